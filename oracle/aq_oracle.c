@@ -1,0 +1,100 @@
+/*
+ * C restatement of the integer core of the AlignQuant mixed W4/W8-A8 linear
+ * layer.  TEST INFRASTRUCTURE ONLY: it is the checker for the CUDA kernels and
+ * the timed CPU baseline of the benchmark; the shipped library never links it.
+ *
+ * Inputs are the *logical* operands: int8 activations xq[M][K], float32
+ * activation scales a[M][n_k] (already broadcast per row), int8 weight tiles
+ * w[n_j][n_k][64 out][64 in] (W4 tiles hold values in [-8, 7]) and float32 tile
+ * scales ws[n_j][n_k].  The arithmetic follows the reference kernels:
+ *   - per (row, N64 tile, K64 tile) exact int32 dot product of 64 terms
+ *     (alignquant/kernels/cuda/linear.cu:664-686, 941-950);
+ *   - FP32 path: acc = acc + float(int) * (a * ws), float multiply and add
+ *     rounded separately, K tiles in increasing order, split-K planes summed in
+ *     split order (linear.cu:956-963, 1237-1238, 1296-1301, 1339-1343);
+ *   - FP64 path: the reference's CPU dequantize-and-matmul
+ *     (alignquant/quantization/exact.py:277-285 and
+ *     alignquant/quantization/calibration.py:566-567), identity output transform.
+ *
+ * Build: gcc -O3 -march=x86-64-v3 -ffp-contract=off -fopenmp -shared -fPIC aq_oracle.c -o libaq_oracle.so
+ * (-ffp-contract=off keeps every multiply and add separately rounded, as the
+ * FP32 contract requires.)
+ */
+#include <stdint.h>
+#include <stddef.h>
+
+#define TILE 64
+
+static inline int32_t dot64(const int8_t* a, const int8_t* b) {
+  int32_t s = 0;
+  for (int i = 0; i < TILE; ++i) s += (int32_t)a[i] * (int32_t)b[i];
+  return s;
+}
+
+/* out[M][n_j][n_k][64] */
+void aqo_tile_accumulators(const int8_t* xq, const int8_t* w, int32_t* out,
+                           int64_t M, int64_t n_j, int64_t n_k) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    for (int64_t j = 0; j < n_j; ++j) {
+      for (int64_t k = 0; k < n_k; ++k) {
+        const int8_t* a = xq + (m * n_k + k) * TILE;
+        const int8_t* t = w + ((j * n_k + k) * TILE) * TILE;
+        int32_t* o = out + ((m * n_j + j) * n_k + k) * TILE;
+        for (int c = 0; c < TILE; ++c) o[c] = dot64(a, t + c * TILE);
+      }
+    }
+  }
+}
+
+/* out[M][n_j*64] float32, kernel operation order */
+void aqo_linear_fp32(const int8_t* xq, const float* a, const int8_t* w, const float* ws,
+                     float* out, int64_t M, int64_t n_j, int64_t n_k, int64_t split_k) {
+  if (split_k < 1) split_k = 1;
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t j = 0; j < n_j; ++j) {
+    for (int64_t m = 0; m < M; ++m) {
+      float total[TILE];
+      for (int64_t s = 0; s < split_k; ++s) {
+        float part[TILE];
+        for (int c = 0; c < TILE; ++c) part[c] = 0.0f;
+        const int64_t k0 = n_k * s / split_k, k1 = n_k * (s + 1) / split_k;
+        for (int64_t k = k0; k < k1; ++k) {
+          const float scale = a[m * n_k + k] * ws[j * n_k + k];
+          const int8_t* x = xq + (m * n_k + k) * TILE;
+          const int8_t* t = w + ((j * n_k + k) * TILE) * TILE;
+          for (int c = 0; c < TILE; ++c) {
+            const float scaled = (float)dot64(x, t + c * TILE) * scale;
+            part[c] = part[c] + scaled;
+          }
+        }
+        for (int c = 0; c < TILE; ++c) total[c] = (s == 0) ? part[c] : total[c] + part[c];
+      }
+      for (int c = 0; c < TILE; ++c) out[m * n_j * TILE + j * TILE + c] = total[c];
+    }
+  }
+}
+
+/* out[M][n_j*64] float64: sum_k (xq*a) . (w*ws), all products and sums in FP64 */
+void aqo_linear_fp64(const int8_t* xq, const float* a, const int8_t* w, const float* ws,
+                     double* out, int64_t M, int64_t n_j, int64_t n_k) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int64_t j = 0; j < n_j; ++j) {
+    for (int64_t m = 0; m < M; ++m) {
+      double acc[TILE];
+      for (int c = 0; c < TILE; ++c) acc[c] = 0.0;
+      for (int64_t k = 0; k < n_k; ++k) {
+        const double sa = (double)a[m * n_k + k];
+        const double sw = (double)ws[j * n_k + k];
+        const int8_t* x = xq + (m * n_k + k) * TILE;
+        const int8_t* t = w + ((j * n_k + k) * TILE) * TILE;
+        for (int c = 0; c < TILE; ++c) {
+          double s = 0.0;
+          for (int i = 0; i < TILE; ++i) s += ((double)x[i] * sa) * ((double)t[c * TILE + i] * sw);
+          acc[c] += s;
+        }
+      }
+      for (int c = 0; c < TILE; ++c) out[m * n_j * TILE + j * TILE + c] = acc[c];
+    }
+  }
+}
