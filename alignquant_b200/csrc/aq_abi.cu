@@ -1,0 +1,197 @@
+// extern "C" entry points of libalignquant_b200.so: argument validation and dispatch.
+// The checks mirror the argument contract of the reference host functions
+// (alignquant/kernels/cuda/linear.cu:1520-1533, 1578-1672) in terms of raw pointers.
+#include <mutex>
+
+#include "aq_common.cuh"
+
+namespace aq {
+
+std::string& last_error_storage() {
+  thread_local std::string text;
+  return text;
+}
+
+int fail(int code, const char* format, ...) {
+  char buffer[512];
+  va_list args;
+  va_start(args, format);
+  vsnprintf(buffer, sizeof(buffer), format, args);
+  va_end(args);
+  last_error_storage() = buffer;
+  return code;
+}
+
+int check_cuda(cudaError_t status, const char* what) {
+  if (status == cudaSuccess) return AQ_OK;
+  return fail(AQ_ERR_CUDA, "%s: %s", what, cudaGetErrorString(status));
+}
+
+int num_sms() {
+  // cached per device; the library may be used from several devices of one process
+  static std::mutex mutex;
+  static int cached[64] = {0};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 148;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (cached[device] == 0) {
+    int value = 0;
+    if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        value <= 0) {
+      value = 148;
+    }
+    cached[device] = value;
+  }
+  return cached[device];
+}
+
+namespace {
+
+constexpr int64_t kStreamMaxRows = 128;  // above this the automatic schedule uses the GEMM
+
+bool valid_split(int s) { return s == 0 || s == 1 || s == 2 || s == 4 || s == 8 || s == 16; }
+
+// 0 = streaming kernel, 1 = tensor-memory GEMM
+int choose_kernel(int64_t m, int schedule) {
+  if (schedule == AQ_SCHEDULE_DECODE || schedule == AQ_SCHEDULE_PREFILL) return 0;
+  if (schedule == AQ_SCHEDULE_PREFILL_M64) return 1;
+  return m <= kStreamMaxRows ? 0 : 1;
+}
+
+}  // namespace
+}  // namespace aq
+
+using namespace aq;
+
+extern "C" {
+
+int aq_version(void) { return 100; }
+
+const char* aq_last_error(void) { return last_error_storage().c_str(); }
+
+int aq_quantize_act(const void* x, int x_dtype, int64_t m, int64_t k, const int32_t* v_metadata,
+                    int scale_mode, int8_t* q, float* scales, void* stream) {
+  AQ_REQUIRE(x != nullptr && q != nullptr && scales != nullptr, "x, q and scales must not be NULL");
+  AQ_REQUIRE(m >= 1, "x must have at least one row, got m=%lld", static_cast<long long>(m));
+  AQ_REQUIRE(k >= kTile && k % kTile == 0, "K must be a positive multiple of 64, got %lld",
+             static_cast<long long>(k));
+  AQ_REQUIRE(k <= (1 << 24), "K too large");
+  AQ_REQUIRE(scale_mode == AQ_SCALE_TILE || scale_mode == AQ_SCALE_TOKEN,
+             "scale_mode must be AQ_SCALE_TILE or AQ_SCALE_TOKEN, got %d", scale_mode);
+  AQ_REQUIRE(scale_mode == AQ_SCALE_TILE || v_metadata == nullptr,
+             "the structured V transform is only defined for AQ_SCALE_TILE");
+  AQ_REQUIRE(aligned(x, 16) && aligned(q, 16), "x and q must be 16-byte aligned for 128-bit access");
+  AQ_REQUIRE(aligned(scales, 4) && aligned(v_metadata, 4), "scales and v_metadata must be 4-byte aligned");
+  return launch_quantize(x, x_dtype, m, k, v_metadata, scale_mode, q, scales,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int64_t aq_prepared_bytes(int32_t n_j, int32_t n_k, int64_t t4, int64_t t8) {
+  if (n_j <= 0 || n_k <= 0 || t4 < 0 || t8 < 0 || t4 + t8 != static_cast<int64_t>(n_j) * n_k) {
+    fail(AQ_ERR_INVALID, "aq_prepared_bytes: need n_j, n_k > 0 and t4 + t8 == n_j * n_k");
+    return AQ_ERR_INVALID;
+  }
+  return records_bytes(t4 + t8) + t4 * kW4TileBytes + t8 * kW8TileBytes;
+}
+
+int aq_repack(const uint8_t* state_bits, const uint8_t* w4_payload, const float* w4_scales,
+              const int8_t* w8_payload, const float* w8_scales, const int32_t* w4_row_offsets,
+              const int32_t* w8_row_offsets, int32_t n_j, int32_t n_k, int64_t t4, int64_t t8,
+              void* prepared, int64_t prepared_bytes, void* stream) {
+  AQ_REQUIRE(n_j > 0 && n_k > 0, "N and K must contain at least one 64-wide tile");
+  AQ_REQUIRE(t4 >= 0 && t8 >= 0 && t4 + t8 == static_cast<int64_t>(n_j) * n_k,
+             "selected payload count mismatch: t4 + t8 must equal n_j * n_k");
+  AQ_REQUIRE(state_bits != nullptr && w4_row_offsets != nullptr && w8_row_offsets != nullptr,
+             "state_bits and row offsets must not be NULL");
+  AQ_REQUIRE(t4 == 0 || (w4_payload != nullptr && w4_scales != nullptr), "W4 arena missing");
+  AQ_REQUIRE(t8 == 0 || (w8_payload != nullptr && w8_scales != nullptr), "W8 arena missing");
+  AQ_REQUIRE(aligned(w4_payload, 8), "w4_payload must be 8-byte aligned");
+  AQ_REQUIRE(aligned(w8_payload, 16), "w8_payload must be 16-byte aligned");
+  AQ_REQUIRE(prepared != nullptr && aligned(prepared, 256), "prepared image must be 256-byte aligned");
+  const int64_t need = aq_prepared_bytes(n_j, n_k, t4, t8);
+  if (prepared_bytes < need) {
+    return fail(AQ_ERR_WORKSPACE, "prepared image needs %lld bytes, got %lld",
+                static_cast<long long>(need), static_cast<long long>(prepared_bytes));
+  }
+  AQ_REQUIRE(need / kW4TileBytes < (1LL << 31), "layer too large for 31-bit tile offsets");
+  return launch_repack(state_bits, w4_payload, w4_scales, w8_payload, w8_scales, w4_row_offsets,
+                       w8_row_offsets, n_j, n_k, prepared, static_cast<cudaStream_t>(stream));
+}
+
+int64_t aq_linear_workspace_bytes(int64_t m, int32_t n_j, int32_t n_k, int schedule,
+                                  int decode_splits) {
+  (void)decode_splits;
+  if (m < 1 || n_j <= 0 || n_k <= 0 || schedule < 0 || schedule > 3) {
+    fail(AQ_ERR_INVALID, "aq_linear_workspace_bytes: invalid problem");
+    return AQ_ERR_INVALID;
+  }
+  if (choose_kernel(m, schedule) == 0) return 0;
+  return tmem_gemm_workspace_bytes(m, n_j, n_k);
+}
+
+int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
+              const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
+              int schedule, int decode_splits, int out_dtype, void* out, void* workspace,
+              int64_t workspace_bytes, int32_t* acc_dump, void* stream) {
+  AQ_REQUIRE(xq != nullptr && act_scales != nullptr && prepared != nullptr && out != nullptr,
+             "xq, act_scales, prepared and out must not be NULL");
+  AQ_REQUIRE(m >= 1, "x_int8 must have at least one row");
+  AQ_REQUIRE(n_j > 0, "N must contain at least one 64-column tile");
+  AQ_REQUIRE(n_k > 0, "K must contain at least one 64-column tile");
+  AQ_REQUIRE(scale_mode == AQ_SCALE_TILE || scale_mode == AQ_SCALE_TOKEN,
+             "scale_mode must be AQ_SCALE_TILE or AQ_SCALE_TOKEN, got %d", scale_mode);
+  AQ_REQUIRE(schedule >= 0 && schedule <= 3,
+             "schedule must be 0 (auto), 1 (decode), 2 (prefill), or 3 (prefill_m64)");
+  AQ_REQUIRE(schedule != AQ_SCHEDULE_DECODE || m == 1,
+             "forced decode schedule requires exactly one row");
+  AQ_REQUIRE(schedule != AQ_SCHEDULE_PREFILL || m > 1,
+             "forced prefill schedule requires more than one row");
+  AQ_REQUIRE(schedule != AQ_SCHEDULE_PREFILL_M64 || m > 1,
+             "forced M64 prefill schedule requires more than one row");
+  AQ_REQUIRE(valid_split(decode_splits), "split override must be 0 (automatic), 1, 2, 4, 8, or 16");
+  AQ_REQUIRE(decode_splits == 0 || schedule != AQ_SCHEDULE_PREFILL_M64,
+             "split override is not available on the forced M64 prefill schedule");
+  AQ_REQUIRE(decode_splits == 0 || decode_splits <= n_k, "decode_splits may not exceed K/64");
+  AQ_REQUIRE(out_dtype == AQ_F32 || out_dtype == AQ_BF16 || out_dtype == AQ_F16,
+             "out_dtype must be AQ_F32, AQ_BF16 or AQ_F16");
+  AQ_REQUIRE(aligned(xq, 16), "x_int8 must be 16-byte aligned for 128-bit access");
+  AQ_REQUIRE(aligned(prepared, 256), "prepared image must be 256-byte aligned");
+  AQ_REQUIRE(aligned(out, 16), "out must be 16-byte aligned");
+  AQ_REQUIRE(aligned(act_scales, 4) && aligned(u_metadata, 4) && aligned(acc_dump, 4),
+             "act_scales, u_metadata and acc_dump must be 4-byte aligned");
+
+  const int64_t tiles = static_cast<int64_t>(n_j) * n_k;
+  LinearArgs a;
+  a.xq = xq;
+  a.act_scales = act_scales;
+  a.scale_mode = scale_mode;
+  a.m = m;
+  a.records = static_cast<const TileRecord*>(prepared);
+  a.payload = static_cast<const uint8_t*>(prepared) + records_bytes(tiles);
+  a.n_j = n_j;
+  a.n_k = n_k;
+  a.u_metadata = u_metadata;
+  a.out_dtype = out_dtype;
+  a.out = out;
+  a.acc_dump = acc_dump;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  if (choose_kernel(m, schedule) == 0) {
+    AQ_REQUIRE(decode_splits == 0 || m <= kStreamMaxRows,
+               "split override requires at most 128 rows");
+    const int split = decode_splits != 0 ? decode_splits : stream_auto_split(m, n_j, n_k);
+    return launch_stream_linear(a, split, s);
+  }
+  const int64_t need = tmem_gemm_workspace_bytes(m, n_j, n_k);
+  if (need > 0 && (workspace == nullptr || workspace_bytes < need || !aligned(workspace, 256))) {
+    return fail(AQ_ERR_WORKSPACE, "aq_linear needs a 256-byte aligned workspace of %lld bytes",
+                static_cast<long long>(need));
+  }
+  return launch_tmem_gemm(a, s);
+}
+
+int aq_device_status(void* stream) { return read_device_status(static_cast<cudaStream_t>(stream)); }
+
+}  // extern "C"

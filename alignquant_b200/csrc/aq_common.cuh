@@ -1,0 +1,145 @@
+// Shared declarations of the alignquant_b200 CUDA library (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "../../include/alignquant_b200.h"
+
+namespace aq {
+
+constexpr int kTile = 64;
+constexpr int kW4TileBytes = 2048;
+constexpr int kW8TileBytes = 4096;
+constexpr uint32_t kW4Flag = 0x80000000u;
+
+// One 8-byte record per weight tile of the prepared image.
+struct __align__(8) TileRecord {
+  uint32_t offset_flag;  // payload offset / 2048, bit 31 set for W4
+  float scale;           // W8: tile scale; W4: tile scale / 16 (kernels feed 16*w to the MMA)
+};
+
+inline int64_t records_bytes(int64_t tiles) {
+  const int64_t raw = tiles * static_cast<int64_t>(sizeof(TileRecord));
+  return (raw + kW4TileBytes - 1) / kW4TileBytes * kW4TileBytes;
+}
+
+// ---- error reporting -------------------------------------------------------
+std::string& last_error_storage();
+int fail(int code, const char* format, ...);
+int check_cuda(cudaError_t status, const char* what);
+
+#define AQ_REQUIRE(cond, ...)                         \
+  do {                                                \
+    if (!(cond)) return ::aq::fail(AQ_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+inline bool aligned(const void* p, size_t a) {
+  return (reinterpret_cast<uintptr_t>(p) % a) == 0;
+}
+
+int num_sms();
+
+// ---- kernel launchers (one per translation unit) ----------------------------
+int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, const int32_t* v_metadata,
+                    int scale_mode, int8_t* q, float* scales, cudaStream_t stream);
+
+int launch_repack(const uint8_t* state_bits, const uint8_t* w4_payload, const float* w4_scales,
+                  const int8_t* w8_payload, const float* w8_scales, const int32_t* w4_row_offsets,
+                  const int32_t* w8_row_offsets, int n_j, int n_k, void* prepared,
+                  cudaStream_t stream);
+
+struct LinearArgs {
+  const int8_t* xq;
+  const float* act_scales;
+  int scale_mode;
+  int64_t m;
+  const TileRecord* records;
+  const uint8_t* payload;
+  int n_j;
+  int n_k;
+  const int32_t* u_metadata;
+  int out_dtype;
+  void* out;
+  int32_t* acc_dump;
+  void* workspace;
+  int64_t workspace_bytes;
+};
+
+// Streaming kernel for small m (mma.sync, split-K reduced through cluster shared memory).
+int launch_stream_linear(const LinearArgs& a, int split_k, cudaStream_t stream);
+int stream_auto_split(int64_t m, int n_j, int n_k);
+
+// Tensor-memory GEMM (tcgen05) for large m.
+int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream);
+int64_t tmem_gemm_workspace_bytes(int64_t m, int n_j, int n_k);
+// Synchronises the stream and reports (then clears) a device-side wait time-out.
+int read_device_status(cudaStream_t stream);
+
+// ---- device helpers -----------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_float(float v) { return v; }
+
+template <typename T>
+__device__ __forceinline__ void store_out(T* out, int64_t index, float value);
+template <>
+__device__ __forceinline__ void store_out<float>(float* out, int64_t index, float value) {
+  out[index] = value;
+}
+template <>
+__device__ __forceinline__ void store_out<__half>(__half* out, int64_t index, float value) {
+  out[index] = __float2half_rn(value);
+}
+template <>
+__device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* out, int64_t index,
+                                                         float value) {
+  out[index] = __float2bfloat16_rn(value);
+}
+
+// 64-point unnormalised Walsh-Hadamard transform of one row held by a warp:
+// lane l owns elements l (low) and l + 32 (high).
+__device__ __forceinline__ void fwht64_warp(double& low, double& high, int lane) {
+#pragma unroll
+  for (int stride = 1; stride < 32; stride <<= 1) {
+    const double low_peer = __shfl_xor_sync(0xffffffffu, low, stride);
+    const double high_peer = __shfl_xor_sync(0xffffffffu, high, stride);
+    low = (lane & stride) ? low_peer - low : low + low_peer;
+    high = (lane & stride) ? high_peer - high : high + high_peer;
+  }
+  const double a = low, b = high;
+  low = a + b;
+  high = a - b;
+}
+
+// Inverse output transform of one 64-column row held by a warp (lane l owns columns
+// l and l + 32): out[r] = left[r] * ((acc * right) H)[perm[r]] / 8, evaluated in FP64
+// (alignquant/kernels/cuda/linear.cu:404-430, 1003-1036).  `meta` points at the
+// [4][64] int32 rows (mode, permutation, left sign, right sign) of the tile.
+__device__ __forceinline__ void inverse_u_row(float& lo, float& hi, const int32_t* meta, int lane) {
+  double dl = static_cast<double>(lo) * static_cast<double>(meta[3 * kTile + lane]);
+  double dh = static_cast<double>(hi) * static_cast<double>(meta[3 * kTile + lane + 32]);
+  fwht64_warp(dl, dh, lane);
+  const int t_lo = meta[kTile + lane];
+  const int t_hi = meta[kTile + lane + 32];
+  const double lo_from_l = __shfl_sync(0xffffffffu, dl, t_lo & 31);
+  const double lo_from_h = __shfl_sync(0xffffffffu, dh, t_lo & 31);
+  const double hi_from_l = __shfl_sync(0xffffffffu, dl, t_hi & 31);
+  const double hi_from_h = __shfl_sync(0xffffffffu, dh, t_hi & 31);
+  lo = static_cast<float>((t_lo < 32 ? lo_from_l : lo_from_h) *
+                          static_cast<double>(meta[2 * kTile + lane]) * 0.125);
+  hi = static_cast<float>((t_hi < 32 ? hi_from_l : hi_from_h) *
+                          static_cast<double>(meta[2 * kTile + lane + 32]) * 0.125);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace aq

@@ -1,0 +1,276 @@
+// Activation quantizer kernels: fp16/bf16/fp32 rows -> int8 plus float32 scales.
+//
+// Two contracts (see include/alignquant_b200.h):
+//   AQ_SCALE_TILE  one scale per 16-row x 64-column tile, endpoint rule and FP64
+//                  rounding of the reference kernel
+//                  (alignquant/kernels/cuda/linear.cu:453-603), optional structured
+//                  64-point transform of every 64-column block first;
+//   AQ_SCALE_TOKEN one scale per row, IEEE float32 arithmetic.
+// Both are bandwidth-bound: 128-bit loads and stores, warp-shuffle reductions.
+#include "aq_common.cuh"
+
+namespace aq {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, float (&v)[16]);
+
+template <>
+__device__ __forceinline__ void load16<__half>(const __half* p, float (&v)[16]) {
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+    const float2 f = __half22float2(h);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[16]) {
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint4 b = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+template <>
+__device__ __forceinline__ void load16<float>(const float* p, float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 f = __ldg(reinterpret_cast<const float4*>(p) + i);
+    v[4 * i] = f.x;
+    v[4 * i + 1] = f.y;
+    v[4 * i + 2] = f.z;
+    v[4 * i + 3] = f.w;
+  }
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+  return (static_cast<uint32_t>(a) & 0xffu) | ((static_cast<uint32_t>(b) & 0xffu) << 8) |
+         ((static_cast<uint32_t>(c) & 0xffu) << 16) | ((static_cast<uint32_t>(d) & 0xffu) << 24);
+}
+
+// ---------------------------------------------------------------------------
+// AQ_SCALE_TOKEN: one CTA walks rows; pass 1 finds the row absmax, pass 2 (the row
+// is still in L1/L2) divides and rounds.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_token_kernel(const T* __restrict__ x,
+                                                             int8_t* __restrict__ q,
+                                                             float* __restrict__ scales,
+                                                             int64_t m, int k) {
+  __shared__ float warp_max[8];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int chunks = k / 16;
+  for (int64_t row = blockIdx.x; row < m; row += gridDim.x) {
+    const T* xr = x + row * k;
+    float amax = 0.0f;
+    for (int c = threadIdx.x; c < chunks; c += 256) {
+      float v[16];
+      load16(xr + c * 16, v);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) warp_max[warp] = amax;
+    __syncthreads();
+    float block_max = warp_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) block_max = fmaxf(block_max, warp_max[w]);
+    const float scale = fmaxf(__fdiv_rn(block_max, 127.0f), 1.0e-12f);
+    if (threadIdx.x == 0) scales[row] = scale;
+    int8_t* qr = q + row * k;
+    for (int c = threadIdx.x; c < chunks; c += 256) {
+      float v[16];
+      load16(xr + c * 16, v);
+      int r[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        r[i] = __float2int_rn(__fdiv_rn(v[i], scale));
+        r[i] = max(-127, min(127, r[i]));
+      }
+      uint4 o;
+      o.x = pack4(r[0], r[1], r[2], r[3]);
+      o.y = pack4(r[4], r[5], r[6], r[7]);
+      o.z = pack4(r[8], r[9], r[10], r[11]);
+      o.w = pack4(r[12], r[13], r[14], r[15]);
+      *reinterpret_cast<uint4*>(qr + c * 16) = o;
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// AQ_SCALE_TILE: one warp per (16-row group, 64-column block).
+// ---------------------------------------------------------------------------
+
+// rint(v / scale) with the reference's FP64 semantics.  v * (1/scale) differs from
+// the correctly rounded quotient by < 1e-13 for |v/scale| <= 129, so it rounds to the
+// same integer unless it lies within 1e-9 of a rounding boundary; only then is the
+// exact division evaluated.
+__device__ __forceinline__ int quantize_fp64(double v, double scale, double inv_scale) {
+  const double t = v * inv_scale;
+  int r = __double2int_rn(t);
+  if (fabs(t - static_cast<double>(r)) > 0.5 - 1.0e-9) r = __double2int_rn(__ddiv_rn(v, scale));
+  return max(-128, min(127, r));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_tile_kernel(const T* __restrict__ x,
+                                                            const int32_t* __restrict__ v_metadata,
+                                                            int8_t* __restrict__ q,
+                                                            float* __restrict__ scales,
+                                                            int64_t m, int n_k) {
+  __shared__ float stage[8][kTile];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int64_t m_tiles = (m + 15) / 16;
+  const int64_t tile = static_cast<int64_t>(blockIdx.x) * 8 + warp;
+  if (tile >= m_tiles * n_k) return;  // whole warps leave; only warp-level syncs below
+  const int64_t mt = tile / n_k;
+  const int kt = static_cast<int>(tile % n_k);
+  const int64_t k = static_cast<int64_t>(n_k) * kTile;
+  const int32_t* meta = v_metadata ? v_metadata + static_cast<int64_t>(kt) * 4 * kTile : nullptr;
+  const bool identity = meta == nullptr || meta[0] == 0;
+
+  if (identity) {
+    // lane -> rows (lane/4, lane/4 + 8), 16 consecutive columns starting at 16*(lane%4)
+    const int r0 = lane >> 2;
+    const int c0 = (lane & 3) * 16;
+    float v[2][16];
+    float pos = 0.0f, neg = 0.0f;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int64_t row = mt * 16 + r0 + 8 * h;
+      if (row < m) {
+        load16(x + row * k + kt * kTile + c0, v[h]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[h][i] = 0.0f;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        pos = fmaxf(pos, v[h][i]);
+        neg = fmaxf(neg, -v[h][i]);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      pos = fmaxf(pos, __shfl_xor_sync(0xffffffffu, pos, o));
+      neg = fmaxf(neg, __shfl_xor_sync(0xffffffffu, neg, o));
+    }
+    const double scale =
+        fmax(fmax(static_cast<double>(pos) / 127.0, static_cast<double>(neg) / 128.0), 1.0e-12);
+    const double inv_scale = 1.0 / scale;
+    if (lane == 0) scales[mt * n_k + kt] = static_cast<float>(scale);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int64_t row = mt * 16 + r0 + 8 * h;
+      if (row < m) {
+        int r[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = quantize_fp64(static_cast<double>(v[h][i]), scale, inv_scale);
+        uint4 o;
+        o.x = pack4(r[0], r[1], r[2], r[3]);
+        o.y = pack4(r[4], r[5], r[6], r[7]);
+        o.z = pack4(r[8], r[9], r[10], r[11]);
+        o.w = pack4(r[12], r[13], r[14], r[15]);
+        *reinterpret_cast<uint4*>(q + row * k + kt * kTile + c0) = o;
+      }
+    }
+    return;
+  }
+
+  // Structured transform V = diag(left) * H[perm, :] * diag(right) / 8 applied to each
+  // row: scatter x[r]*left[r] to position perm[r], 64-point Walsh-Hadamard butterfly,
+  // multiply by right and 1/8 -- all in FP64 like the reference.
+  const int perm_lo = meta[kTile + lane];
+  const int perm_hi = meta[kTile + lane + 32];
+  const float left_lo = static_cast<float>(meta[2 * kTile + lane]);
+  const float left_hi = static_cast<float>(meta[2 * kTile + lane + 32]);
+  const double right_lo = static_cast<double>(meta[3 * kTile + lane]) * 0.125;
+  const double right_hi = static_cast<double>(meta[3 * kTile + lane + 32]) * 0.125;
+  double lo[16], hi[16];
+  double pos = 0.0, neg = 0.0;
+#pragma unroll
+  for (int r = 0; r < 16; ++r) {
+    const int64_t row = mt * 16 + r;
+    float a = 0.0f, b = 0.0f;
+    if (row < m) {
+      a = to_float(x[row * k + kt * kTile + lane]);
+      b = to_float(x[row * k + kt * kTile + lane + 32]);
+    }
+    __syncwarp();
+    stage[warp][perm_lo] = a * left_lo;
+    stage[warp][perm_hi] = b * left_hi;
+    __syncwarp();
+    double l = static_cast<double>(stage[warp][lane]);
+    double h = static_cast<double>(stage[warp][lane + 32]);
+    fwht64_warp(l, h, lane);
+    lo[r] = l * right_lo;
+    hi[r] = h * right_hi;
+    pos = fmax(pos, fmax(lo[r], hi[r]));
+    neg = fmax(neg, fmax(-lo[r], -hi[r]));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    pos = fmax(pos, __shfl_xor_sync(0xffffffffu, pos, o));
+    neg = fmax(neg, __shfl_xor_sync(0xffffffffu, neg, o));
+  }
+  const double scale = fmax(fmax(pos / 127.0, neg / 128.0), 1.0e-12);
+  const double inv_scale = 1.0 / scale;
+  if (lane == 0) scales[mt * n_k + kt] = static_cast<float>(scale);
+#pragma unroll
+  for (int r = 0; r < 16; ++r) {
+    const int64_t row = mt * 16 + r;
+    if (row < m) {
+      q[row * k + kt * kTile + lane] = static_cast<int8_t>(quantize_fp64(lo[r], scale, inv_scale));
+      q[row * k + kt * kTile + lane + 32] = static_cast<int8_t>(quantize_fp64(hi[r], scale, inv_scale));
+    }
+  }
+}
+
+template <typename T>
+int launch_typed(const void* x, int64_t m, int64_t k, const int32_t* v_metadata, int scale_mode,
+                 int8_t* q, float* scales, cudaStream_t stream) {
+  const T* xt = static_cast<const T*>(x);
+  if (scale_mode == AQ_SCALE_TOKEN) {
+    const int64_t grid = m < 148 * 16 ? m : 148 * 16;
+    quantize_token_kernel<T><<<static_cast<unsigned>(grid), 256, 0, stream>>>(xt, q, scales, m,
+                                                                             static_cast<int>(k));
+  } else {
+    const int64_t tiles = (m + 15) / 16 * (k / kTile);
+    const int64_t grid = (tiles + 7) / 8;
+    quantize_tile_kernel<T><<<static_cast<unsigned>(grid), 256, 0, stream>>>(
+        xt, v_metadata, q, scales, m, static_cast<int>(k / kTile));
+  }
+  return check_cuda(cudaGetLastError(), "activation quantizer launch");
+}
+
+}  // namespace
+
+int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, const int32_t* v_metadata,
+                    int scale_mode, int8_t* q, float* scales, cudaStream_t stream) {
+  switch (x_dtype) {
+    case AQ_F16:
+      return launch_typed<__half>(x, m, k, v_metadata, scale_mode, q, scales, stream);
+    case AQ_BF16:
+      return launch_typed<__nv_bfloat16>(x, m, k, v_metadata, scale_mode, q, scales, stream);
+    case AQ_F32:
+      return launch_typed<float>(x, m, k, v_metadata, scale_mode, q, scales, stream);
+    default:
+      return fail(AQ_ERR_INVALID, "x_dtype must be AQ_F16, AQ_BF16 or AQ_F32, got %d", x_dtype);
+  }
+}
+
+}  // namespace aq

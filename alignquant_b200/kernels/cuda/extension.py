@@ -1,0 +1,360 @@
+"""Python operator API of the native W4/W8-A8 path.
+
+Same callables as the reference's ``alignquant/kernels/cuda/extension.py:254-319``
+(``load_extension``, ``alignquant_activation_quantize_cuda``,
+``alignquant_linear_cuda``), backed by ``libalignquant_b200.so`` through ctypes.
+Tensors are passed to the C ABI as raw device pointers together with the current
+CUDA stream; outputs are allocated here with torch's caching allocator.
+
+Additions over the reference API: ``scale_mode`` ("tile" = the reference's
+16x64-tile scales, the default; "token" = one scale per row), fp16 output, row
+counts that are not multiples of 16, and ``prepare_weights`` /
+``alignquant_linear_prepared`` for callers that keep the re-laid-out weight image.
+"""
+
+from __future__ import annotations
+
+import weakref
+from dataclasses import dataclass
+
+import torch
+
+from alignquant_b200 import _lib
+
+_DTYPE_CODES = {torch.float16: _lib.AQ_F16, torch.bfloat16: _lib.AQ_BF16, torch.float32: _lib.AQ_F32}
+_SCALE_MODES = {"tile": _lib.AQ_SCALE_TILE, "token": _lib.AQ_SCALE_TOKEN}
+
+
+def load_extension() -> None:
+    """Load the native library before a timed region (extension.py:254-257 of the reference)."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("The W4/W8A8 extension requires a visible CUDA device.")
+    capability = torch.cuda.get_device_capability()
+    if capability[0] != 10:
+        raise RuntimeError(f"The W4/W8A8 extension requires SM100 (B200), got {capability}.")
+    _lib.load()
+
+
+def _stream(device: torch.device) -> int:
+    return int(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _ptr(tensor: torch.Tensor | None) -> int | None:
+    if tensor is None or tensor.numel() == 0:
+        return None
+    return int(tensor.data_ptr())
+
+
+def _require_cuda(tensor: torch.Tensor, name: str) -> None:
+    if not tensor.is_cuda:
+        raise RuntimeError(f"{name} must be CUDA")
+
+
+def _scale_mode_code(scale_mode: str) -> int:
+    try:
+        return _SCALE_MODES[str(scale_mode)]
+    except KeyError as error:
+        raise ValueError(f"Unknown scale_mode {scale_mode!r}; expected {tuple(_SCALE_MODES)}.") from error
+
+
+def alignquant_activation_quantize_cuda(
+    activation: torch.Tensor,
+    v_metadata: torch.Tensor | None,
+    *,
+    tile_major: bool = False,
+    scale_mode: str = "tile",
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Quantize ``[M, K]`` activations to int8; returns ``(int8, float32 scales)``.
+
+    ``scale_mode="tile"``: scales are ``[ceil(M/16), K/64]`` (``[K/64]`` when M <= 16,
+    as in the reference, linear.cu:1539-1542) after the structured V transform.
+    ``scale_mode="token"``: scales are ``[M]``; ``v_metadata`` must be None or identity.
+    ``tile_major=True`` returns the reference's ``[M/16, K/64, 16, 64]`` arrangement; it
+    exists for API compatibility only (the kernels here read row-major activations).
+    """
+    mode = _scale_mode_code(scale_mode)
+    _require_cuda(activation, "x")
+    if activation.dtype not in _DTYPE_CODES:
+        raise RuntimeError("x must be bf16, fp16, or fp32")
+    if activation.dim() != 2 or activation.size(0) < 1:
+        raise RuntimeError("x must be [M,K] with positive M")
+    x = activation.contiguous()
+    m, k = int(x.size(0)), int(x.size(1))
+    if k % 64:
+        raise RuntimeError("K must be a multiple of 64")
+    n_k = k // 64
+    if tile_major and (m < 128 or m % 16):
+        raise RuntimeError("tile-major A8 output requires at least 128 rows (a multiple of 16)")
+    meta = None
+    if v_metadata is not None:
+        _require_cuda(v_metadata, "v_metadata")
+        if v_metadata.dtype != torch.int32:
+            raise RuntimeError("v_metadata must be int32")
+        if tuple(v_metadata.shape) != (n_k, 4, 64):
+            raise RuntimeError("v_metadata must be [K/64,4,64]")
+        if v_metadata.device != x.device:
+            raise RuntimeError("x and v_metadata must share one device")
+        meta = v_metadata.contiguous()
+        if mode == _lib.AQ_SCALE_TOKEN:
+            if bool((meta[:, 0, 0] != 0).any()):
+                raise RuntimeError("per-token scales do not support a non-identity V transform")
+            meta = None
+    with torch.cuda.device(x.device):
+        q = torch.empty((m, k), dtype=torch.int8, device=x.device)
+        if mode == _lib.AQ_SCALE_TOKEN:
+            scales = torch.empty((m,), dtype=torch.float32, device=x.device)
+        else:
+            n_m = (m + 15) // 16
+            scales = torch.empty((n_k,) if n_m == 1 else (n_m, n_k), dtype=torch.float32, device=x.device)
+        _lib.check(
+            _lib.load().aq_quantize_act(
+                _ptr(x), _DTYPE_CODES[x.dtype], m, k, _ptr(meta), mode, _ptr(q), _ptr(scales), _stream(x.device)
+            )
+        )
+    if tile_major:
+        q = q.view(m // 16, 16, n_k, 64).permute(0, 2, 1, 3).contiguous()
+    return q, scales
+
+
+@dataclass
+class PreparedWeights:
+    """A layer's weights re-laid-out once for the B200 kernels (see ``aq_repack``)."""
+
+    image: torch.Tensor
+    n_j: int
+    n_k: int
+    t4: int
+    t8: int
+
+    @property
+    def device(self) -> torch.device:
+        return self.image.device
+
+    def payload_bytes(self) -> int:
+        return self.t4 * 2048 + self.t8 * 4096
+
+    def algorithmic_bytes(self) -> int:
+        """Weight-side bytes a kernel must read: tiles plus one 8-byte record per tile."""
+        return self.payload_bytes() + 8 * (self.t4 + self.t8)
+
+
+def prepare_weights(
+    state_bits: torch.Tensor,
+    w4_payload: torch.Tensor,
+    w4_scales: torch.Tensor,
+    w8_payload: torch.Tensor,
+    w8_scales: torch.Tensor,
+    w4_row_offsets: torch.Tensor,
+    w8_row_offsets: torch.Tensor,
+    *,
+    n_k: int,
+) -> PreparedWeights:
+    """Validate the seven artifact tensors of a layer and build its prepared image.
+
+    The checks are those of the reference's host function (linear.cu:1594-1639).
+    """
+    tensors = {
+        "state_bits": (state_bits, torch.uint8),
+        "w4_payload": (w4_payload, torch.uint8),
+        "w4_scales": (w4_scales, torch.float32),
+        "w8_payload": (w8_payload, torch.int8),
+        "w8_scales": (w8_scales, torch.float32),
+        "w4_row_offsets": (w4_row_offsets, torch.int32),
+        "w8_row_offsets": (w8_row_offsets, torch.int32),
+    }
+    device = state_bits.device
+    for name, (tensor, dtype) in tensors.items():
+        _require_cuda(tensor, name)
+        if tensor.dtype != dtype:
+            raise RuntimeError(f"{name} must be {str(dtype).replace('torch.', '')}")
+        if tensor.device != device:
+            raise RuntimeError("all inputs must share one CUDA device")
+    if w4_payload.dim() != 3 or tuple(w4_payload.shape[1:]) != (64, 32):
+        raise RuntimeError("w4_payload must be [tiles,64,32]")
+    if w8_payload.dim() != 3 or tuple(w8_payload.shape[1:]) != (64, 64):
+        raise RuntimeError("w8_payload must be [tiles,64,64]")
+    t4, t8 = int(w4_payload.size(0)), int(w8_payload.size(0))
+    if t4 != w4_scales.numel():
+        raise RuntimeError("W4 payload/scale count mismatch")
+    if t8 != w8_scales.numel():
+        raise RuntimeError("W8 payload/scale count mismatch")
+    if w4_row_offsets.dim() != 1 or w8_row_offsets.dim() != 1:
+        raise RuntimeError("row offsets must be rank 1")
+    if w4_row_offsets.numel() != w8_row_offsets.numel():
+        raise RuntimeError("row offset sizes differ")
+    n_j = int(w4_row_offsets.numel()) - 1
+    if n_j <= 0:
+        raise RuntimeError("N must contain at least one 64-column tile")
+    if state_bits.numel() != (n_j * n_k + 7) // 8:
+        raise RuntimeError("state_bits byte count mismatch")
+    if t4 + t8 != n_j * n_k:
+        raise RuntimeError("selected payload count mismatch")
+    lib = _lib.load()
+    size = int(lib.aq_prepared_bytes(n_j, n_k, t4, t8))
+    if size < 0:
+        _lib.check(size)
+    with torch.cuda.device(device):
+        image = torch.empty((size,), dtype=torch.uint8, device=device)
+        keep = [t.contiguous() for t, _ in tensors.values()]
+        _lib.check(
+            lib.aq_repack(
+                _ptr(keep[0]), _ptr(keep[1]), _ptr(keep[2]), _ptr(keep[3]), _ptr(keep[4]), _ptr(keep[5]),
+                _ptr(keep[6]), n_j, n_k, t4, t8, _ptr(image), size, _stream(device),
+            )
+        )
+    return PreparedWeights(image=image, n_j=n_j, n_k=n_k, t4=t4, t8=t8)
+
+
+def alignquant_linear_prepared(
+    activation: torch.Tensor,
+    activation_scales: torch.Tensor,
+    weights: PreparedWeights,
+    u_metadata: torch.Tensor | None,
+    *,
+    schedule: str = "auto",
+    decode_splits: int = 0,
+    output_dtype: torch.dtype = torch.float32,
+    scale_mode: str = "tile",
+    acc_dump: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Run one packed projection on a prepared weight image; returns ``[M, N]``."""
+    try:
+        schedule_code = _lib.SCHEDULE_CODES[str(schedule)]
+    except KeyError as error:
+        raise ValueError(
+            f"Unknown W4/W8A8 schedule {schedule!r}; expected {tuple(_lib.SCHEDULE_CODES)}."
+        ) from error
+    if output_dtype not in _DTYPE_CODES:
+        raise ValueError("Projection output_dtype must be torch.float32, torch.bfloat16 or torch.float16.")
+    mode = _scale_mode_code(scale_mode)
+    _require_cuda(activation, "x_int8")
+    _require_cuda(activation_scales, "activation_scales")
+    if activation.dtype != torch.int8:
+        raise RuntimeError("x_int8 must be int8")
+    if activation_scales.dtype != torch.float32:
+        raise RuntimeError("activation_scales must be float32")
+    n_j, n_k = weights.n_j, weights.n_k
+    x = activation
+    if x.dim() == 4:  # the reference's tile-major arrangement [M/16, K/64, 16, 64]
+        if x.size(2) != 16 or x.size(3) != 64:
+            raise RuntimeError("tile-major x_int8 must be [M/16,K/64,16,64] with M>=128")
+        x = x.permute(0, 2, 1, 3).reshape(x.size(0) * 16, x.size(1) * 64)
+    if x.dim() != 2:
+        raise RuntimeError("x_int8 must be [M,K] or tile-major [M/16,K/64,16,64]")
+    x = x.contiguous()
+    m = int(x.size(0))
+    if int(x.size(1)) != n_k * 64:
+        raise RuntimeError(f"K mismatch: activation has {int(x.size(1))}, weights have {n_k * 64}")
+    scales = activation_scales.contiguous()
+    expected = m if mode == _lib.AQ_SCALE_TOKEN else ((m + 15) // 16) * n_k
+    if scales.numel() != expected:
+        raise RuntimeError(
+            "activation_scales must contain one scalar per M16x64 tile"
+            if mode == _lib.AQ_SCALE_TILE
+            else "activation_scales must contain one scalar per row"
+        )
+    device = x.device
+    if scales.device != device or weights.device != device:
+        raise RuntimeError("all inputs must share one CUDA device")
+    meta = None
+    if u_metadata is not None:
+        _require_cuda(u_metadata, "u_metadata")
+        if u_metadata.dtype != torch.int32:
+            raise RuntimeError("u_metadata must be int32")
+        if tuple(u_metadata.shape) != (n_j, 4, 64):
+            raise RuntimeError("u_metadata must be [N/64,4,64]")
+        if u_metadata.device != device:
+            raise RuntimeError("all inputs must share one CUDA device")
+        meta = u_metadata.contiguous()
+    if acc_dump is not None:
+        if acc_dump.dtype != torch.int32 or tuple(acc_dump.shape) != (m, n_j, n_k, 64) or not acc_dump.is_contiguous():
+            raise RuntimeError("acc_dump must be a contiguous int32 [M,N/64,K/64,64] tensor")
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        if out is None:
+            out = torch.empty((m, n_j * 64), dtype=output_dtype, device=device)
+        elif out.dtype != output_dtype or tuple(out.shape) != (m, n_j * 64) or not out.is_contiguous():
+            raise RuntimeError("out must be a contiguous [M,N] tensor of output_dtype")
+        ws_bytes = int(lib.aq_linear_workspace_bytes(m, n_j, n_k, schedule_code, int(decode_splits)))
+        if ws_bytes < 0:
+            _lib.check(ws_bytes)
+        workspace = torch.empty((ws_bytes,), dtype=torch.uint8, device=device) if ws_bytes else None
+        _lib.check(
+            lib.aq_linear(
+                _ptr(x), _ptr(scales), mode, m, _ptr(weights.image), n_j, n_k, _ptr(meta), schedule_code,
+                int(decode_splits), _DTYPE_CODES[output_dtype], _ptr(out), _ptr(workspace), ws_bytes,
+                _ptr(acc_dump), _stream(device),
+            )
+        )
+    return out
+
+
+_PREPARED_CACHE: dict[tuple, PreparedWeights] = {}
+
+
+def _cached_prepared(tensors: tuple[torch.Tensor, ...], n_k: int) -> PreparedWeights:
+    key = tuple((int(t.data_ptr()), tuple(t.shape), int(t._version)) for t in tensors) + (n_k, str(tensors[0].device))
+    hit = _PREPARED_CACHE.get(key)
+    if hit is None:
+        hit = prepare_weights(*tensors, n_k=n_k)
+        _PREPARED_CACHE[key] = hit
+        for tensor in tensors:  # the image is only valid while the source tensors are alive
+            weakref.finalize(tensor, _PREPARED_CACHE.pop, key, None)
+    return hit
+
+
+def alignquant_linear_cuda(
+    activation: torch.Tensor,
+    activation_scales: torch.Tensor,
+    state_bits: torch.Tensor,
+    w4_payload: torch.Tensor,
+    w4_scales: torch.Tensor,
+    w8_payload: torch.Tensor,
+    w8_scales: torch.Tensor,
+    w4_row_offsets: torch.Tensor,
+    w8_row_offsets: torch.Tensor,
+    u_metadata: torch.Tensor,
+    *,
+    schedule: str = "auto",
+    decode_splits: int = 0,
+    output_dtype: torch.dtype = torch.float32,
+    scale_mode: str = "tile",
+) -> torch.Tensor:
+    """Run one packed projection from the raw artifact tensors (reference signature).
+
+    The weight arenas are re-laid-out on first use and the image is cached for as long
+    as the seven tensors stay alive; callers that own the weights should call
+    ``prepare_weights`` once and ``alignquant_linear_prepared`` per step instead.
+    """
+    if activation.dim() == 4:
+        n_k = int(activation.size(1))
+    else:
+        n_k = int(activation.size(-1)) // 64
+    tensors = tuple(
+        t.contiguous()
+        for t in (state_bits, w4_payload, w4_scales, w8_payload, w8_scales, w4_row_offsets, w8_row_offsets)
+    )
+    weights = _cached_prepared(tensors, n_k)
+    return alignquant_linear_prepared(
+        activation, activation_scales, weights, u_metadata,
+        schedule=schedule, decode_splits=decode_splits, output_dtype=output_dtype, scale_mode=scale_mode,
+    )
+
+
+def device_status(device: torch.device | str | None = None) -> None:
+    """Synchronise the current stream and raise if a kernel gave up a device-side wait."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().aq_device_status(_stream(dev)))
+
+
+__all__ = [
+    "load_extension",
+    "alignquant_activation_quantize_cuda",
+    "alignquant_linear_cuda",
+    "alignquant_linear_prepared",
+    "prepare_weights",
+    "PreparedWeights",
+    "device_status",
+]

@@ -1,0 +1,148 @@
+/*
+ * alignquant_b200 -- C ABI of the B200 (sm_100a) mixed W4/W8-A8 linear-layer path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed
+ * as void*, i.e. a cudaStream_t; NULL is the legacy default stream).  The caller
+ * owns every buffer: inputs, outputs, the prepared weight image and the optional
+ * workspace.  Calls are asynchronous on the given stream, never synchronise and
+ * never allocate.  They return AQ_OK (0) or a negative AQ_ERR_* code; the text of
+ * the last error of the calling thread is returned by aq_last_error().  No C++
+ * exception crosses this boundary.
+ *
+ * The functions replace the two host entry points of the reference extension
+ * (alignquant/kernels/cuda/linear.cu:1516 and :1564, exported to Python by
+ * alignquant/kernels/cuda/bindings.cu:27-52) and the kernels behind them.
+ */
+#ifndef ALIGNQUANT_B200_H_
+#define ALIGNQUANT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define AQ_API __attribute__((visibility("default")))
+#else
+#define AQ_API
+#endif
+
+#define AQ_OK 0
+#define AQ_ERR_INVALID (-1)   /* an argument violates the documented contract        */
+#define AQ_ERR_CUDA (-2)      /* a CUDA runtime call or kernel launch failed          */
+#define AQ_ERR_WORKSPACE (-3) /* workspace or image buffer smaller than required      */
+#define AQ_ERR_DEVICE (-4)    /* a kernel reported a device-side time-out             */
+
+/* element types of activations and outputs */
+#define AQ_F16 0
+#define AQ_BF16 1
+#define AQ_F32 2
+
+/* activation scale granularity */
+#define AQ_SCALE_TILE 0  /* one scale per 16-row x 64-column activation tile (reference
+                            contract, alignquant/kernels/cuda/linear.cu:546-584)      */
+#define AQ_SCALE_TOKEN 1 /* one scale per activation row (benchmark-config contract) */
+
+/* schedule codes, same numbering as alignquant/kernels/cuda/extension.py:290-295 */
+#define AQ_SCHEDULE_AUTO 0
+#define AQ_SCHEDULE_DECODE 1      /* streaming kernel, requires m == 1                */
+#define AQ_SCHEDULE_PREFILL 2     /* streaming kernel, requires m > 1                 */
+#define AQ_SCHEDULE_PREFILL_M64 3 /* tensor-memory GEMM kernel, requires m > 1        */
+
+/* Library version: major * 10000 + minor * 100 + patch. */
+AQ_API int aq_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+AQ_API const char* aq_last_error(void);
+
+/*
+ * Activation quantizer: x[m][k] (AQ_F16 / AQ_BF16 / AQ_F32, row-major) -> q[m][k]
+ * int8 plus float32 scales.  Replaces alignquant_activation_quantize_cuda,
+ * alignquant/kernels/cuda/linear.cu:1516-1562 (kernel :502-603).
+ *
+ *   v_metadata  int32 [k/64][4][64]: rows (mode, permutation, left sign, right sign)
+ *               of the structured 64-point transform applied to every 64-column
+ *               block before quantisation; mode 0 = identity.  May be NULL
+ *               (all identity).  Only used with AQ_SCALE_TILE.
+ *   scale_mode  AQ_SCALE_TILE : scales[ceil(m/16)][k/64]; scale =
+ *                               max(max(+v)/127, max(-v)/128, 1e-12) over the tile,
+ *                               q = rint(v/scale) in FP64, clamp [-128,127].
+ *               AQ_SCALE_TOKEN: scales[m]; scale = max(absmax(row)/127, 1e-12),
+ *                               q = rint(x/scale) in IEEE float32, clamp [-127,127].
+ *   Requirements: m >= 1, k % 64 == 0, x/q 16-byte aligned.
+ */
+AQ_API int aq_quantize_act(const void* x, int x_dtype, int64_t m, int64_t k,
+                    const int32_t* v_metadata, int scale_mode,
+                    int8_t* q, float* scales, void* stream);
+
+/*
+ * Size in bytes of the prepared weight image of a layer with n_j x n_k tiles of
+ * which t4 are W4 and t8 are W8 (t4 + t8 == n_j * n_k).
+ */
+AQ_API int64_t aq_prepared_bytes(int32_t n_j, int32_t n_k, int64_t t4, int64_t t8);
+
+/*
+ * One-time re-layout of the seven artifact tensors of a layer (device pointers,
+ * formats of alignquant/quantization/artifact.py:23-31,131-199: Layout-B tiles,
+ * low-nibble-first W4, LSB-first state bitmap with 1 = W4, per-precision arenas
+ * with row-offset prefixes) into the image the kernels stream.  Replaces the
+ * per-call work of expand_mixed_payload_to_w8_kernel and the per-thread bitmap
+ * scans (alignquant/kernels/cuda/linear.cu:166-220, 1242-1256).
+ *
+ * Image: n_j*n_k 8-byte tile records {uint32 offset/2048 | W4 flag in bit 31,
+ * float32 scale (W4: scale/16)}, padded to 2048 bytes, followed by the tiles in
+ * (j, k) order: W8 tile = 4096 B as [k/16][n/8][n%8][k%16]; W4 tile = 2048 B as
+ * [k/32][n/8][n%8][16 B], byte i = (w[n][32h+i] & 15) | (w[n][32h+16+i] << 4).
+ * `prepared` must be 256-byte aligned and at least aq_prepared_bytes() long.
+ */
+AQ_API int aq_repack(const uint8_t* state_bits, const uint8_t* w4_payload, const float* w4_scales,
+              const int8_t* w8_payload, const float* w8_scales,
+              const int32_t* w4_row_offsets, const int32_t* w8_row_offsets,
+              int32_t n_j, int32_t n_k, int64_t t4, int64_t t8,
+              void* prepared, int64_t prepared_bytes, void* stream);
+
+/*
+ * Bytes of workspace aq_linear needs for this problem (0 when none is needed).
+ */
+AQ_API int64_t aq_linear_workspace_bytes(int64_t m, int32_t n_j, int32_t n_k, int schedule,
+                                  int decode_splits);
+
+/*
+ * out[m][64*n_j] = sum over K64 tiles of float(int32 tile dot product) *
+ * (activation scale * tile scale), accumulated in FP32 in increasing k, followed
+ * by the structured inverse output transform.  Replaces alignquant_linear_cuda,
+ * alignquant/kernels/cuda/linear.cu:1564-1778, and the kernels it dispatches
+ * (:617-698, :700-793, :798-1047, :1053-1210, :1216-1354).
+ *
+ *   xq            int8 [m][64*n_k] row-major, 16-byte aligned
+ *   act_scales    float32, AQ_SCALE_TILE: [ceil(m/16)][n_k]; AQ_SCALE_TOKEN: [m]
+ *   prepared      image written by aq_repack
+ *   u_metadata    int32 [n_j][4][64] inverse-output-transform rows, or NULL (identity)
+ *   schedule      AQ_SCHEDULE_*; decode_splits 0 (automatic) or 1, 2, 4, 8, 16
+ *                 (only with AQ_SCHEDULE_AUTO/DECODE/PREFILL and m <= 128;
+ *                 values above 8 run as 8)
+ *   out_dtype     AQ_F32, AQ_BF16 or AQ_F16; out is [m][64*n_j], 16-byte aligned
+ *   workspace     at least aq_linear_workspace_bytes() bytes, 256-byte aligned, or
+ *                 NULL when that is 0
+ *   acc_dump      NULL, or int32 [m][n_j][n_k][64]: receives every per-tile integer
+ *                 dot product (debug/verification aid; slows the call down)
+ */
+AQ_API int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
+              const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
+              int schedule, int decode_splits, int out_dtype, void* out,
+              void* workspace, int64_t workspace_bytes, int32_t* acc_dump, void* stream);
+
+/*
+ * Synchronises `stream`, then returns AQ_ERR_DEVICE if a kernel of this library gave
+ * up a bounded device-side wait since the last call (the outputs of that launch are
+ * invalid), clearing the condition; AQ_OK otherwise.  The reference has no such
+ * state: its kernels contain no device-side waits.
+ */
+AQ_API int aq_device_status(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALIGNQUANT_B200_H_ */

@@ -1,0 +1,202 @@
+"""GPU parity of the quantizer, the weight re-layout and the streaming (small-M) kernel
+against the CPU oracle, through the Python operator API and the C ABI behind it."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import alignquant_oracle as oc
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+REL, ABS = 1e-3, 1e-2  # contract tolerance of fp outputs against the FP64 dequantize-and-matmul
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from alignquant_b200.kernels.cuda import extension
+
+    extension.load_extension()
+    return extension
+
+
+@pytest.mark.parametrize("fraction", [0.6, 0.0, 1.0])
+@pytest.mark.parametrize("n,k", [(64, 64), (128, 192), (192, 320)])
+def test_repack_image_is_exact(ext, n, k, fraction):
+    packed, states, tiles, scales = helpers.forced_layer(n, k, seed=n + k, fraction=fraction)
+    weights, _ = helpers.prepare_layer(packed, k // 64)
+    image = weights.image.cpu().numpy()
+    word, rec_scale, payload = helpers.expected_image(states, tiles, scales)
+    n_tiles = states.size
+    rec = image[: n_tiles * 8].view(np.uint32).reshape(n_tiles, 2)
+    assert np.array_equal(rec[:, 0], word)
+    assert np.array_equal(rec[:, 1].view(np.float32), rec_scale)
+    start = -(-n_tiles * 8 // 2048) * 2048
+    assert np.array_equal(image[start : start + payload.size], payload)
+    assert image.size == start + payload.size
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,k", [(1, 64), (5, 192), (16, 3072), (130, 256)])
+def test_token_quantizer_bit_exact(ext, m, k, dtype):
+    x = oc.synthetic_activation(m, k, seed=m * 7 + k, dtype="bfloat16" if dtype == torch.bfloat16 else np.float16)
+    x = x.astype(np.float32)
+    if m > 2:
+        x[2] = 0.0  # all-zero row takes the scale floor
+    xt = helpers.torch_activation(x, dtype)
+    q, s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode="token")
+    q_ref, s_ref = oc.a8_token_quantize(xt.float().cpu().numpy())
+    assert np.array_equal(s.cpu().numpy(), s_ref)
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,k", [(1, 64), (4, 192), (16, 3072), (17, 128), (130, 256)])
+def test_tile_quantizer_bit_exact_identity(ext, m, k, dtype):
+    x = oc.synthetic_activation(m, k, seed=m * 11 + k, dtype="bfloat16" if dtype == torch.bfloat16 else np.float16)
+    xt = helpers.torch_activation(x, dtype)
+    meta = torch.from_numpy(oc.identity_metadata(k // 64)).cuda()
+    q, s = ext.alignquant_activation_quantize_cuda(xt, meta)
+    rows = 1 if m == 1 else 16 * ((m + 15) // 16)
+    xp = np.zeros((rows, k), dtype=np.float64)
+    xp[:m] = xt.float().cpu().numpy()
+    q_ref, s_ref = oc.a8_tile_quantize(xp)
+    assert np.array_equal(s.cpu().numpy().reshape(s_ref.shape), s_ref)
+    assert np.array_equal(q.cpu().numpy(), q_ref[:m])
+
+
+def test_tile_quantizer_matches_reference_fixture_with_transform(ext, golden_dir):
+    g = dict(np.load(golden_dir / "act_quant_mixed.npz"))
+    xt = torch.from_numpy(g["x"]).cuda()
+    meta = torch.from_numpy(g["v_metadata"]).cuda()
+    q, s = ext.alignquant_activation_quantize_cuda(xt, meta)
+    # The kernel evaluates the 64-point butterfly in FP64, the reference's CPU path one
+    # FP64 matmul: values agree to rounding noise, so scales agree to float32 rounding
+    # and int8 codes may differ by one step on a vanishing fraction of elements.
+    assert np.allclose(s.cpu().numpy(), g["scales"], rtol=1e-6, atol=0)
+    diff = np.abs(q.cpu().numpy().astype(np.int32) - g["q"].astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
+
+
+def _run_linear(ext, xq, a_s, weights, u_meta, m, n_j, n_k, **kw):
+    dump = torch.full((m, n_j, n_k, 64), -7, dtype=torch.int32, device="cuda")
+    out = ext.alignquant_linear_prepared(xq, a_s, weights, u_meta, acc_dump=dump, **kw)
+    ext.device_status()
+    return out, dump
+
+
+@pytest.mark.parametrize("scale_mode", ["tile", "token"])
+@pytest.mark.parametrize("m", [1, 4, 16, 17, 64, 128])
+@pytest.mark.parametrize("n,k", [(64, 64), (128, 192), (192, 512)])
+def test_stream_linear_matches_oracle(ext, n, k, m, scale_mode):
+    n_j, n_k = n // 64, k // 64
+    packed, states, tiles, scales = oc.synthetic_layer(n, k, seed=n * 3 + k)
+    weights, _ = helpers.prepare_layer(packed, n_k)
+    x = oc.synthetic_activation(m, k, seed=m + n + k)
+    xt = helpers.torch_activation(x, torch.float16)
+    xq, a_s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode=scale_mode)
+    xq_np = xq.cpu().numpy()
+    if scale_mode == "token":
+        a_mk = oc.expand_act_scales(a_s.cpu().numpy(), m, n_k, "token")
+    else:
+        a_mk = np.repeat(a_s.cpu().numpy().reshape(-1, n_k), 16, axis=0)[:m]
+    acc_ref = oc.tile_accumulators_c(xq_np, tiles)
+    y64 = oc.dequant_matmul_fp64(xq_np, a_mk, tiles, scales)
+    schedule = "forced_decode" if m == 1 else "forced_prefill"
+    for split in (1, 2, 0):
+        if split > n_k:
+            continue
+        out, dump = _run_linear(ext, xq, a_s, weights, None, m, n_j, n_k,
+                                schedule=schedule, decode_splits=split, scale_mode=scale_mode)
+        assert np.array_equal(dump.cpu().numpy(), acc_ref), f"int32 tile accumulators differ (split {split})"
+        got = out.cpu().numpy()
+        if split:
+            want = oc.linear_fp32_c(xq_np, a_mk, tiles, scales, split)
+            assert np.array_equal(got, want), f"fp32 result not in reference operation order (split {split})"
+        assert np.allclose(got, y64, rtol=REL, atol=ABS)
+
+
+@pytest.mark.parametrize("fraction", [0.0, 1.0])
+def test_stream_linear_uniform_precision_layers(ext, fraction):
+    n, k, m = 128, 256, 8
+    packed, states, tiles, scales = helpers.forced_layer(n, k, seed=5, fraction=fraction)
+    weights, _ = helpers.prepare_layer(packed, k // 64)
+    xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=9), torch.float16)
+    xq, a_s = ext.alignquant_activation_quantize_cuda(xt, None)
+    out, dump = _run_linear(ext, xq, a_s, weights, None, m, n // 64, k // 64, decode_splits=1)
+    xq_np = xq.cpu().numpy()
+    a_mk = np.repeat(a_s.cpu().numpy().reshape(-1, k // 64), 16, axis=0)[:m]
+    assert np.array_equal(dump.cpu().numpy(), oc.tile_accumulators_c(xq_np, tiles))
+    assert np.array_equal(out.cpu().numpy(), oc.linear_fp32_c(xq_np, a_mk, tiles, scales, 1))
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+def test_stream_linear_half_outputs_and_bounds(ext, out_dtype):
+    n, k, m = 192, 320, 13
+    n_j, n_k = n // 64, k // 64
+    packed, states, tiles, scales = oc.synthetic_layer(n, k, seed=77)
+    weights, _ = helpers.prepare_layer(packed, n_k)
+    xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=1), torch.float16)
+    xq, a_s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode="token")
+    canvas = torch.full((m + 2, n), 123.0, dtype=out_dtype, device="cuda")  # canary rows around the output
+    out = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token",
+                                         output_dtype=out_dtype, out=canvas[1 : m + 1])
+    ext.device_status()
+    assert bool((canvas[0] == 123.0).all()) and bool((canvas[m + 1] == 123.0).all())
+    a_mk = oc.expand_act_scales(a_s.cpu().numpy(), m, n_k, "token")
+    y64 = oc.dequant_matmul_fp64(xq.cpu().numpy(), a_mk, tiles, scales)
+    assert np.allclose(out.float().cpu().numpy(), y64, rtol=1e-2 if out_dtype == torch.bfloat16 else REL, atol=ABS)
+
+
+@pytest.mark.parametrize("name", ["linear_identity", "linear_m1", "linear_transformed"])
+def test_reference_fixture_end_to_end(ext, golden_dir, name):
+    """Raw artifact tensors from the reference's packer -> quantize -> linear -> y of the
+    reference's CPU dequantize-and-matmul, through the reference-signature call."""
+    g = dict(np.load(golden_dir / f"{name}.npz"))
+    m, k = g["x"].shape
+    n_j, n_k = g["states"].shape
+    t = helpers.to_cuda({key[len("packed_"):]: v for key, v in g.items() if key.startswith("packed_")})
+    xt = torch.from_numpy(g["x"]).cuda()
+    v_meta = torch.from_numpy(g["v_metadata"]).cuda()
+    u_meta = torch.from_numpy(g["u_metadata"]).cuda()
+    xq, a_s = ext.alignquant_activation_quantize_cuda(xt, v_meta)
+    if name != "linear_transformed":
+        assert np.array_equal(xq.cpu().numpy(), g["xq"])
+        assert np.array_equal(a_s.cpu().numpy().reshape(-1, n_k), g["act_scales"][: (m + 15) // 16])
+    out = ext.alignquant_linear_cuda(
+        xq, a_s, t["state_bits"], t["w4_payload"], t["w4_scales"], t["w8_payload"], t["w8_scales"],
+        t["w4_row_offsets"], t["w8_row_offsets"], u_meta,
+    )
+    ext.device_status()
+    assert tuple(out.shape) == (m, n_j * 64) and out.dtype == torch.float32
+    assert np.allclose(out.cpu().numpy(), g["y"], rtol=REL, atol=ABS)
+    # with the fixture's own int8 activations the integer tile sums are exact
+    xq_fix = torch.from_numpy(g["xq"]).cuda()
+    a_fix = torch.from_numpy(np.ascontiguousarray(g["act_scales"][: (m + 15) // 16])).cuda()
+    weights, _ = helpers.prepare_layer({key[len("packed_"):]: v for key, v in g.items() if key.startswith("packed_")}, n_k)
+    out2, dump = _run_linear(ext, xq_fix, a_fix, weights, u_meta, m, n_j, n_k)
+    assert np.array_equal(dump.cpu().numpy(), g["acc"])
+    assert np.allclose(out2.cpu().numpy(), g["y"], rtol=REL, atol=ABS)
+
+
+def test_argument_errors_raise(ext):
+    packed, *_ = oc.synthetic_layer(64, 64, seed=1)
+    weights, t = helpers.prepare_layer(packed, 1)
+    xq = torch.zeros((2, 64), dtype=torch.int8, device="cuda")
+    s = torch.ones((1,), dtype=torch.float32, device="cuda")
+    with pytest.raises(ValueError):
+        ext.alignquant_linear_prepared(xq, s, weights, None, schedule="fastest")
+    with pytest.raises(RuntimeError, match="forced decode schedule requires exactly one row"):
+        ext.alignquant_linear_prepared(xq, s, weights, None, schedule="forced_decode")
+    with pytest.raises(RuntimeError, match="decode_splits may not exceed"):
+        ext.alignquant_linear_prepared(xq, s, weights, None, decode_splits=2)
+    with pytest.raises(RuntimeError, match="one scalar per M16x64 tile"):
+        ext.alignquant_linear_prepared(xq, torch.ones(3, device="cuda"), weights, None)
+    with pytest.raises(RuntimeError, match="K must be a multiple of 64"):
+        ext.alignquant_activation_quantize_cuda(torch.zeros((2, 65), device="cuda", dtype=torch.float16), None)
+    with pytest.raises(RuntimeError, match="selected payload count mismatch"):
+        ext.prepare_weights(t["state_bits"], t["w4_payload"], t["w4_scales"], t["w8_payload"], t["w8_scales"],
+                            t["w4_row_offsets"], t["w8_row_offsets"], n_k=2)

@@ -1,0 +1,99 @@
+"""GPU parity of the tensor-memory (tcgen05) GEMM against the CPU oracle."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import alignquant_oracle as oc
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+REL, ABS = 1e-3, 1e-2
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from alignquant_b200.kernels.cuda import extension
+
+    extension.load_extension()
+    return extension
+
+
+def _case(ext, m, n, k, scale_mode, seed, fraction=0.6, act_dtype=torch.bfloat16):
+    n_j, n_k = n // 64, k // 64
+    packed, states, tiles, scales = oc.synthetic_layer(n, k, seed=seed, w4_fraction=fraction)
+    weights, _ = helpers.prepare_layer(packed, n_k)
+    x = oc.synthetic_activation(m, k, seed=seed + 1, dtype="bfloat16" if act_dtype == torch.bfloat16 else np.float16)
+    xt = helpers.torch_activation(x, act_dtype)
+    xq, a_s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode=scale_mode)
+    if scale_mode == "token":
+        a_mk = oc.expand_act_scales(a_s.cpu().numpy(), m, n_k, "token")
+    else:
+        a_mk = np.repeat(a_s.cpu().numpy().reshape(-1, n_k), 16, axis=0)[:m]
+    return weights, tiles, scales, xq, a_s, a_mk
+
+
+@pytest.mark.parametrize("scale_mode", ["tile", "token"])
+@pytest.mark.parametrize("m", [2, 64, 128, 130, 300])
+@pytest.mark.parametrize("n,k", [(64, 64), (192, 192), (256, 1024), (320, 128)])
+def test_gemm_matches_oracle(ext, n, k, m, scale_mode):
+    n_j, n_k = n // 64, k // 64
+    weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, scale_mode, seed=n + k + m)
+    dump = torch.full((m, n_j, n_k, 64), -7, dtype=torch.int32, device="cuda")
+    out = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill_m64",
+                                         scale_mode=scale_mode, acc_dump=dump)
+    ext.device_status()
+    xq_np = xq.cpu().numpy()
+    assert np.array_equal(dump.cpu().numpy(), oc.tile_accumulators_c(xq_np, tiles)), "int32 tile accumulators differ"
+    got = out.cpu().numpy()
+    assert np.array_equal(got, oc.linear_fp32_c(xq_np, a_mk, tiles, scales, 1)), "fp32 not in reference operation order"
+    assert np.allclose(got, oc.dequant_matmul_fp64(xq_np, a_mk, tiles, scales), rtol=REL, atol=ABS)
+
+
+@pytest.mark.parametrize("fraction", [0.0, 1.0])
+def test_gemm_uniform_precision_layers(ext, fraction):
+    m, n, k = 256, 256, 256
+    weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "token", seed=3, fraction=fraction)
+    out = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill_m64", scale_mode="token")
+    ext.device_status()
+    assert np.array_equal(out.cpu().numpy(), oc.linear_fp32_c(xq.cpu().numpy(), a_mk, tiles, scales, 1))
+
+
+def test_gemm_auto_schedule_bf16_output_and_bounds(ext):
+    m, n, k = 200, 384, 512
+    weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "token", seed=21)
+    canvas = torch.full((m + 2, n), 77.0, dtype=torch.bfloat16, device="cuda")
+    out = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token",
+                                         output_dtype=torch.bfloat16, out=canvas[1 : m + 1])
+    ext.device_status()
+    assert bool((canvas[0] == 77.0).all()) and bool((canvas[m + 1] == 77.0).all())
+    want = torch.from_numpy(oc.linear_fp32_c(xq.cpu().numpy(), a_mk, tiles, scales, 1)).to(torch.bfloat16)
+    assert torch.equal(out.cpu(), want)
+
+
+def test_gemm_reference_fixture_with_output_transform(ext, golden_dir):
+    g = dict(np.load(golden_dir / "linear_transformed.npz"))
+    m, k = g["x"].shape
+    n_j, n_k = g["states"].shape
+    packed = {key[len("packed_"):]: v for key, v in g.items() if key.startswith("packed_")}
+    weights, _ = helpers.prepare_layer(packed, n_k)
+    xq = torch.from_numpy(g["xq"]).cuda()
+    a_s = torch.from_numpy(np.ascontiguousarray(g["act_scales"])).cuda()
+    u_meta = torch.from_numpy(g["u_metadata"]).cuda()
+    dump = torch.zeros((m, n_j, n_k, 64), dtype=torch.int32, device="cuda")
+    out = ext.alignquant_linear_prepared(xq, a_s, weights, u_meta, schedule="forced_prefill_m64", acc_dump=dump)
+    ext.device_status()
+    assert np.array_equal(dump.cpu().numpy(), g["acc"])
+    assert np.allclose(out.cpu().numpy(), g["y"], rtol=REL, atol=ABS)
+
+
+def test_gemm_agrees_with_streaming_kernel_bit_for_bit(ext):
+    m, n, k = 96, 256, 384
+    weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "tile", seed=8)
+    a = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill_m64")
+    b = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill", decode_splits=1)
+    ext.device_status()
+    assert torch.equal(a, b)
