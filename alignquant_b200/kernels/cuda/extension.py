@@ -63,6 +63,7 @@ def alignquant_activation_quantize_cuda(
     *,
     tile_major: bool = False,
     scale_mode: str = "tile",
+    out: tuple[torch.Tensor, torch.Tensor] | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Quantize ``[M, K]`` activations to int8; returns ``(int8, float32 scales)``.
 
@@ -71,6 +72,7 @@ def alignquant_activation_quantize_cuda(
     ``scale_mode="token"``: scales are ``[M]``; ``v_metadata`` must be None or identity.
     ``tile_major=True`` returns the reference's ``[M/16, K/64, 16, 64]`` arrangement; it
     exists for API compatibility only (the kernels here read row-major activations).
+    ``out=(int8, scales)`` reuses caller-owned contiguous buffers of the right size.
     """
     mode = _scale_mode_code(scale_mode)
     _require_cuda(activation, "x")
@@ -99,13 +101,20 @@ def alignquant_activation_quantize_cuda(
             if bool((meta[:, 0, 0] != 0).any()):
                 raise RuntimeError("per-token scales do not support a non-identity V transform")
             meta = None
+    n_m = (m + 15) // 16
+    scale_shape = (m,) if mode == _lib.AQ_SCALE_TOKEN else ((n_k,) if n_m == 1 else (n_m, n_k))
     with torch.cuda.device(x.device):
-        q = torch.empty((m, k), dtype=torch.int8, device=x.device)
-        if mode == _lib.AQ_SCALE_TOKEN:
-            scales = torch.empty((m,), dtype=torch.float32, device=x.device)
+        if out is not None:
+            q, scales = out
+            if (q.dtype != torch.int8 or tuple(q.shape) != (m, k) or not q.is_contiguous()
+                    or scales.dtype != torch.float32 or tuple(scales.shape) != scale_shape
+                    or not scales.is_contiguous() or q.device != x.device or scales.device != x.device):
+                raise RuntimeError("out must be (contiguous int8 [M,K], contiguous float32 scales) on x's device")
+            if tile_major:
+                raise RuntimeError("out= is not available with tile_major=True")
         else:
-            n_m = (m + 15) // 16
-            scales = torch.empty((n_k,) if n_m == 1 else (n_m, n_k), dtype=torch.float32, device=x.device)
+            q = torch.empty((m, k), dtype=torch.int8, device=x.device)
+            scales = torch.empty(scale_shape, dtype=torch.float32, device=x.device)
         _lib.check(
             _lib.load().aq_quantize_act(
                 _ptr(x), _DTYPE_CODES[x.dtype], m, k, _ptr(meta), mode, _ptr(q), _ptr(scales), _stream(x.device)

@@ -1,0 +1,391 @@
+"""Benchmark of the mixed W4/W8-A8 linear hot path on B200.
+
+Workload (one "step"): the decode sweep over every quantized linear of a random-init
+Llama-3.2-3B-shaped decoder -- 28 layers x {qkv 3072->5120, o 3072->3072,
+gate_up 3072->16384, down 8192->3072}, row counts M in {1, 4, 8, 16}, 60 % W4 tiles,
+per-token INT8 activations -- i.e. 448 (activation quantizer -> packed GEMV) pairs
+over ~2 GB of distinct weights (larger than L2, so no flush is needed between steps).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
+
+With N > 1 (launched under torch.distributed.run) every layer is sharded
+tensor-parallel: column shards of qkv/gate_up, row shards of o/down followed by an
+NCCL all-reduce of the [M, 3072] partial; total work is fixed ("strong" scaling).
+
+Rank 0 prints one JSON line.  `value` is algorithmic bytes per second with every
+input resident in HBM (CUDA-graph replay, CUDA-event timing, max over ranks); `e2e`
+is the same sweep through the public Python API from pinned host buffers, host<->device
+copies included; `roofline` times the packed-GEMV kernel alone; `cpu_baseline` times
+the CPU oracle (the reference's dequantize-and-matmul recipe) on a bounded sample.
+`--impl reference` runs only that CPU arm.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+HIDDEN, INTER, LAYERS = 3072, 8192, 28
+ROW_COUNTS = (1, 4, 8, 16)
+# name -> (N, K, tensor-parallel split axis)
+GROUPS = {
+    "qkv": (5120, HIDDEN, "n"),
+    "o": (HIDDEN, HIDDEN, "k"),
+    "gate_up": (2 * INTER, HIDDEN, "n"),
+    "down": (HIDDEN, INTER, "k"),
+}
+WORKLOAD = "llama-3.2-3b decode sweep: 28 layers x (qkv, o, gate_up, down), M in {1,4,8,16}, 60% W4, per-token A8"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("native", "reference"), default="native")
+    return ap.parse_args()
+
+
+def hbm_peak():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = (
+        "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+        "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        self.index = index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return False
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, max_clocks, reasons = [], [], set()
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clocks.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, value in zip(self.NAMES, parts[2:]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        if clocks:
+            self.result = {
+                "sm_mhz": statistics.median(clocks), "sm_max_mhz": max(max_clocks),
+                "reasons": sorted(reasons), "samples": len(clocks),
+            }
+        return False
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle's restatement of the reference's dequantize-and-matmul
+# ---------------------------------------------------------------------------
+
+
+def artifact_bytes(n_j: int, n_k: int, w4_tiles: int) -> int:
+    """Weight-side algorithmic bytes of a layer in the artifact format."""
+    tiles = n_j * n_k
+    return w4_tiles * 2048 + (tiles - w4_tiles) * 4096 + 4 * tiles + (tiles + 7) // 8 + 8 * (n_j + 1)
+
+
+def call_bytes(m: int, n: int, k: int, weight_bytes: int) -> int:
+    """Algorithmic bytes of one quantize -> linear pair (fp16 in, fp32 out, per-token scales)."""
+    quantizer = m * k * 2 + m * k + 4 * m
+    linear = weight_bytes + m * k + 4 * m + m * n * 4
+    return quantizer + linear
+
+
+class CpuSample:
+    """One decoder layer's four projection groups at M in {1,4,8,16} on the host cores."""
+
+    description = "1 of 28 layers: (qkv, o, gate_up, down) x M in {1,4,8,16}, FP64 dequantize-and-matmul (numpy/BLAS)"
+
+    def __init__(self):
+        import numpy as np
+
+        from oracle import alignquant_oracle as oc
+
+        self.oc, self.np = oc, np
+        self.cases = []
+        self.bytes = 0
+        for index, (name, (n, k, _)) in enumerate(GROUPS.items()):
+            _, states, tiles, scales = oc.synthetic_layer(n, k, seed=100 + index, pack=False)
+            w_bytes = artifact_bytes(n // 64, k // 64, int((states == oc.P4).sum()))
+            for m in ROW_COUNTS:
+                x = oc.synthetic_activation(m, k, seed=7 * m + index)
+                self.cases.append((x, tiles, scales, k // 64))
+                self.bytes += call_bytes(m, n, k, w_bytes)
+
+    def run(self) -> float:
+        oc = self.oc
+        start = time.perf_counter()
+        for x, tiles, scales, n_k in self.cases:
+            xq, a_s = oc.a8_token_quantize(x)
+            a_mk = oc.expand_act_scales(a_s, x.shape[0], n_k, "token")
+            oc.dequant_matmul_fp64(xq, a_mk, tiles, scales)
+        return time.perf_counter() - start
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    sample = CpuSample()
+    for _ in range(min(args.warmup, 1)):
+        sample.run()
+    times = [sample.run()]
+    budget_steps = max(1, int(120.0 / max(times[0], 1e-3)))  # keep the whole arm within a few minutes
+    while len(times) < min(max(1, args.steps), budget_steps):
+        times.append(sample.run())
+    per_step = sum(times) / len(times)
+    value = sample.bytes / per_step / 1e9
+    line = {
+        "metric": "decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "impl": "reference",
+        "n_gpus": args.gpus, "steps": len(times), "warmup": min(args.warmup, 1), "ms_per_step": per_step * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "step": CpuSample.description},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": CpuSample.description},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+
+
+def run_native(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from alignquant_b200.kernels.cuda import extension as ext
+    from alignquant_b200.synthetic import algorithmic_weight_bytes, synthetic_activation, synthetic_module_tensors
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    ext.load_extension()
+
+    # ---- build the sharded model: prepared weight images only (raw arenas are freed)
+    layers = []
+    weight_bytes = {}
+    for layer in range(LAYERS):
+        entry = {}
+        for index, (name, (n, k, axis)) in enumerate(GROUPS.items()):
+            n_local = n // world if axis == "n" else n
+            k_local = k // world if axis == "k" else k
+            tensors = synthetic_module_tensors(n_local, k_local, seed=((layer * 8 + index) * 64 + rank), device=device)
+            weight_bytes[(layer, name)] = algorithmic_weight_bytes(tensors)
+            entry[name] = ext.prepare_weights(
+                tensors["state_bits"], tensors["w4_payload"], tensors["w4_scales"], tensors["w8_payload"],
+                tensors["w8_scales"], tensors["w4_row_offsets"], tensors["w8_row_offsets"], n_k=k_local // 64,
+            )
+            del tensors
+        layers.append(entry)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+
+    local_shape = {
+        name: (n // world if axis == "n" else n, k // world if axis == "k" else k) for name, (n, k, axis) in GROUPS.items()
+    }
+    acts = {(m, name): synthetic_activation(m, local_shape[name][1], seed=m * 16 + i, device=device)
+            for m in ROW_COUNTS for i, name in enumerate(GROUPS)}
+    qbuf = {key: (torch.empty(x.shape, dtype=torch.int8, device=device), torch.empty((x.shape[0],), dtype=torch.float32, device=device))
+            for key, x in acts.items()}
+    outs = {(m, name): torch.empty((m, local_shape[name][0]), dtype=torch.float32, device=device)
+            for m in ROW_COUNTS for name in GROUPS}
+
+    step_bytes = 0
+    linear_bytes = 0
+    for m in ROW_COUNTS:
+        for layer in range(LAYERS):
+            for name in GROUPS:
+                n, k = local_shape[name]
+                step_bytes += call_bytes(m, n, k, weight_bytes[(layer, name)])
+                linear_bytes += weight_bytes[(layer, name)] + m * k + 4 * m + m * n * 4
+    pairs_per_step = len(ROW_COUNTS) * LAYERS * len(GROUPS)
+
+    def sweep(with_quantizer: bool, with_allreduce: bool) -> None:
+        for m in ROW_COUNTS:
+            for entry in layers:
+                for name, (_, _, axis) in GROUPS.items():
+                    if with_quantizer:
+                        ext.alignquant_activation_quantize_cuda(acts[(m, name)], None, scale_mode="token", out=qbuf[(m, name)])
+                    xq, a_s = qbuf[(m, name)]
+                    ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", out=outs[(m, name)])
+                    if with_allreduce and world > 1 and axis == "k":
+                        dist.all_reduce(outs[(m, name)])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps: int, warmup: int) -> float:
+        """Seconds per step: CUDA events around `steps` calls, max over ranks."""
+        for _ in range(warmup):
+            fn()
+        barrier()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(steps):
+            fn()
+        end.record()
+        barrier()
+        seconds = begin.elapsed_time(end) / 1e3 / steps
+        if world > 1:
+            t = torch.tensor([seconds], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            seconds = float(t.item())
+        return seconds
+
+    # ---- device-resident step: CUDA graph on one GPU, eager with NCCL otherwise
+    sweep(True, True)
+    barrier()
+    if world == 1:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            sweep(True, False)
+        step = graph.replay
+    else:
+        step = lambda: sweep(True, True)  # noqa: E731
+    with ClockSampler(local_rank) as clocks:
+        seconds = timed(step, args.steps, max(args.warmup, 3))
+    ext.device_status(device)
+
+    # ---- the packed-GEMV kernel alone (roofline of the dominant kernel)
+    kernel_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(kernel_graph):
+        sweep(False, False)
+    kernel_seconds = timed(kernel_graph.replay, args.steps, 3) / pairs_per_step
+    peak, peak_source = hbm_peak()
+    achieved = linear_bytes / pairs_per_step / kernel_seconds / 1e9
+
+    # ---- end to end through the public API from pinned host buffers
+    host_x = {key: x.cpu().pin_memory() for key, x in acts.items()}
+    host_out = {key: torch.empty(o.shape, dtype=o.dtype).pin_memory() for key, o in outs.items()}
+    h2d = sum(host_x[(m, name)].numel() * 2 for m in ROW_COUNTS for name in GROUPS) * LAYERS
+    d2h = sum(host_out[(m, name)].numel() * 4 for m in ROW_COUNTS for name in GROUPS) * LAYERS
+
+    def e2e_step() -> None:
+        for m in ROW_COUNTS:
+            for entry in layers:
+                for name, (_, _, axis) in GROUPS.items():
+                    x = host_x[(m, name)].to(device, non_blocking=True)
+                    xq, a_s = ext.alignquant_activation_quantize_cuda(x, None, scale_mode="token")
+                    y = ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token")
+                    if world > 1 and axis == "k":
+                        dist.all_reduce(y)
+                    host_out[(m, name)].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    e2e_seconds = timed(e2e_step, max(1, min(args.steps, 5)), 1)
+
+    total_bytes = step_bytes * world  # every rank streams its own shard
+    line = {
+        "metric": "decode_gemv_hbm_gbs",
+        "value": total_bytes / seconds / 1e9,
+        "unit": "GB/s",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": seconds * 1e3,
+        "higher_is_better": True,
+        "scaling": "strong",
+        "vs_baseline": None,
+        "dtype": "int8",
+        "data": "synthetic",
+        "config": {
+            "workload": WORKLOAD,
+            "l2": "2 GB of distinct weights per step exceed the 126 MB L2; no flush between steps",
+            "parallelism": f"tp{world}",
+            "launch": "cuda graph replay" if world == 1 else "eager + NCCL all-reduce",
+        },
+        "clocks": clocks.result,
+        "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": 2 * pairs_per_step * args.steps,
+        "roofline": {
+            "kernel": "stream_linear_kernel (packed W4/W8 GEMV, M<=16)", "bound": "hbm",
+            "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "peak_source": f"{peak_source} HBM copy bandwidth", "traffic": None,
+            "bytes_per_launch": linear_bytes / pairs_per_step, "us_per_launch": kernel_seconds * 1e6,
+        },
+    }
+    if rank == 0 and world == 1:
+        sample = CpuSample()
+        sample.run()
+        cpu_seconds = min(sample.run() for _ in range(2))
+        line["cpu_baseline"] = {
+            "value": sample.bytes / cpu_seconds / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1,
+            "kind": "port", "sample": CpuSample.description,
+        }
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()
