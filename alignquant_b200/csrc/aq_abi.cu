@@ -1,6 +1,8 @@
 // extern "C" entry points of libalignquant_b200.so: argument validation and dispatch.
 // The checks mirror the argument contract of the reference host functions
 // (alignquant/kernels/cuda/linear.cu:1520-1533, 1578-1672) in terms of raw pointers.
+#include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 #include "aq_common.cuh"
@@ -43,6 +45,14 @@ int num_sms() {
     cached[device] = value;
   }
   return cached[device];
+}
+
+bool use_dependent_launch() {
+  static const bool enabled = [] {
+    const char* value = std::getenv("ALIGNQUANT_B200_PDL");
+    return value == nullptr || std::strcmp(value, "0") != 0;
+  }();
+  return enabled;
 }
 
 namespace {
@@ -192,6 +202,17 @@ int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t
   return launch_tmem_gemm(a, s);
 }
 
-int aq_device_status(void* stream) { return read_device_status(static_cast<cudaStream_t>(stream)); }
+int aq_device_status(void* stream) {
+  const int rc = check_cuda(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "cudaStreamSynchronize");
+  if (rc != AQ_OK) return rc;
+  const int stream_status = take_stream_status();
+  const int gemm_status = take_gemm_status();
+  if (stream_status < 0 || gemm_status < 0) return fail(AQ_ERR_CUDA, "could not read the device status words");
+  if (stream_status != 0 || gemm_status != 0) {
+    return fail(AQ_ERR_DEVICE, "a kernel wait timed out on the device (streaming kernel wait id %d, GEMM wait id %d)",
+                stream_status, gemm_status);
+  }
+  return AQ_OK;
+}
 
 }  // extern "C"

@@ -79,8 +79,13 @@ int stream_auto_split(int64_t m, int n_j, int n_k);
 // Tensor-memory GEMM (tcgen05) for large m.
 int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream);
 int64_t tmem_gemm_workspace_bytes(int64_t m, int n_j, int n_k);
-// Synchronises the stream and reports (then clears) a device-side wait time-out.
-int read_device_status(cudaStream_t stream);
+// Read and clear the device-side time-out word of each kernel family (0 = none,
+// -1 = the word could not be read).
+int take_stream_status();
+int take_gemm_status();
+// Whether kernels are launched with programmatic stream serialization (dependent
+// launch); on by default, ALIGNQUANT_B200_PDL=0 turns it off.
+bool use_dependent_launch();
 
 // ---- device helpers -----------------------------------------------------------
 #ifdef __CUDACC__

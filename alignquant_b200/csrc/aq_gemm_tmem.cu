@@ -25,10 +25,11 @@
 #include <mutex>
 
 #include "aq_common.cuh"
+#include "aq_ptx.cuh"
 
 namespace aq {
 
-__device__ int g_device_status = 0;
+__device__ int g_gemm_status = 0;
 
 namespace {
 
@@ -45,7 +46,6 @@ constexpr int kRecBytes = kTilesN * kMaxNk * static_cast<int>(sizeof(TileRecord)
 constexpr int kNumBars = 4 * kStages + 5;
 constexpr int kSmemBytes = kStages * kStageBytes + kRecBytes + 512;
 constexpr int kThreads = 384;
-constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr int kEpiRowFloats = 65;
 
 struct GemmParams {
@@ -63,51 +63,6 @@ struct GemmParams {
   int out_dtype;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Bounded wait.  Returns false when the CTA is aborting (this wait or another one
-// ran out of polls); `code` identifies the waiting role in the status word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *abort_flag != 0) return false;
-  }
-  *abort_flag = 1;
-  atomicCAS(&g_device_status, 0, code);
-  return false;
-}
-
-__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-      "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
                : "memory");
@@ -116,9 +71,6 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -215,7 +167,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
     }
     mbar_init(final_bar, 1);
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
     fence_proxy_async();
   }
   for (int i = threadIdx.x; i < tiles_here * n_k; i += kThreads) {
@@ -242,7 +194,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
       for (int kt = 0; kt < n_k; ++kt) {
         const int s = kt % kStages;
         const uint32_t ph = (kt / kStages) & 1;
-        if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, 1)) break;
+        if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, &g_gemm_status, 1)) break;
         uint8_t* a_s = stages + s * kStageBytes;
         const uint32_t a_addr = smem_u32(a_s);
         const uint32_t b_addr = a_addr + kABytes;
@@ -304,9 +256,9 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
           const uint32_t ph = (kt / kStages) & 1;
           const int b = kt & 1;
           const uint32_t pha = (kt >> 1) & 1;
-          ok = mbar_wait(raw_full(s), ph, abort_flag, 2) && mbar_wait(a_full(s), ph, abort_flag, 3) &&
-               mbar_wait(unpacked(s), ph, abort_flag, 4) &&
-               mbar_wait(acc_empty(b), pha ^ 1u, abort_flag, 5);
+          ok = mbar_wait(raw_full(s), ph, abort_flag, &g_gemm_status, 2) && mbar_wait(a_full(s), ph, abort_flag, &g_gemm_status, 3) &&
+               mbar_wait(unpacked(s), ph, abort_flag, &g_gemm_status, 4) &&
+               mbar_wait(acc_empty(b), pha ^ 1u, abort_flag, &g_gemm_status, 5);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(stages + s * kStageBytes);
@@ -331,7 +283,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
       for (int kt = 0; kt < n_k; ++kt) {
         const int s = kt % kStages;
         const uint32_t ph = (kt / kStages) & 1;
-        if (!mbar_wait(raw_full(s), ph, abort_flag, 6)) break;
+        if (!mbar_wait(raw_full(s), ph, abort_flag, &g_gemm_status, 6)) break;
         uint8_t* b_s = stages + s * kStageBytes + kABytes;
         const uint8_t* p_s = b_s + kBBytes;
         for (int t = 0; t < tiles_here; ++t) {
@@ -377,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
     for (int kt = 0; kt < n_k; ++kt) {
       const int b = kt & 1;
       const uint32_t pha = (kt >> 1) & 1;
-      if (!mbar_wait(acc_full(b), pha, abort_flag, 7)) {
+      if (!mbar_wait(acc_full(b), pha, abort_flag, &g_gemm_status, 7)) {
         ok = false;
         break;
       }
@@ -499,18 +451,14 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   return check_cuda(cudaGetLastError(), "tensor-memory GEMM launch");
 }
 
-int read_device_status(cudaStream_t stream) {
-  int rc = check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
-  if (rc != AQ_OK) return rc;
+int take_gemm_status() {
   int status = 0;
-  rc = check_cuda(cudaMemcpyFromSymbol(&status, g_device_status, sizeof(int)), "read device status");
-  if (rc != AQ_OK) return rc;
+  if (cudaMemcpyFromSymbol(&status, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
   if (status != 0) {
     const int zero = 0;
-    cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
-    return fail(AQ_ERR_DEVICE, "a kernel wait timed out on the device (wait id %d)", status);
+    cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
   }
-  return AQ_OK;
+  return status;
 }
 
 }  // namespace aq

@@ -8,6 +8,7 @@
 //   AQ_SCALE_TOKEN one scale per row, IEEE float32 arithmetic.
 // Both are bandwidth-bound: 128-bit loads and stores, warp-shuffle reductions.
 #include "aq_common.cuh"
+#include "aq_ptx.cuh"
 
 namespace aq {
 namespace {
@@ -68,6 +69,8 @@ __global__ void __launch_bounds__(256) quantize_token_kernel(const T* __restrict
                                                              float* __restrict__ scales,
                                                              int64_t m, int k) {
   __shared__ float warp_max[8];
+  grid_launch_dependents();  // the consumer of q may start fetching its weights now
+  grid_dependency_wait();    // x comes from the preceding kernel
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int chunks = k / 16;
@@ -132,6 +135,8 @@ __global__ void __launch_bounds__(256) quantize_tile_kernel(const T* __restrict_
                                                             float* __restrict__ scales,
                                                             int64_t m, int n_k) {
   __shared__ float stage[8][kTile];
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int64_t m_tiles = (m + 15) / 16;
@@ -244,17 +249,26 @@ template <typename T>
 int launch_typed(const void* x, int64_t m, int64_t k, const int32_t* v_metadata, int scale_mode,
                  int8_t* q, float* scales, cudaStream_t stream) {
   const T* xt = static_cast<const T*>(x);
+  cudaLaunchConfig_t config = {};
+  config.blockDim = dim3(256, 1, 1);
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = use_dependent_launch() ? 1 : 0;
+  cudaError_t status;
   if (scale_mode == AQ_SCALE_TOKEN) {
     const int64_t grid = m < 148 * 16 ? m : 148 * 16;
-    quantize_token_kernel<T><<<static_cast<unsigned>(grid), 256, 0, stream>>>(xt, q, scales, m,
-                                                                             static_cast<int>(k));
+    config.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+    status = cudaLaunchKernelEx(&config, quantize_token_kernel<T>, xt, q, scales, m, static_cast<int>(k));
   } else {
     const int64_t tiles = (m + 15) / 16 * (k / kTile);
-    const int64_t grid = (tiles + 7) / 8;
-    quantize_tile_kernel<T><<<static_cast<unsigned>(grid), 256, 0, stream>>>(
-        xt, v_metadata, q, scales, m, static_cast<int>(k / kTile));
+    config.gridDim = dim3(static_cast<unsigned>((tiles + 7) / 8), 1, 1);
+    status = cudaLaunchKernelEx(&config, quantize_tile_kernel<T>, xt, v_metadata, q, scales, m,
+                                static_cast<int>(k / kTile));
   }
-  return check_cuda(cudaGetLastError(), "activation quantizer launch");
+  return check_cuda(status, "activation quantizer launch");
 }
 
 }  // namespace
