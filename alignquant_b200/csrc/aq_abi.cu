@@ -58,14 +58,15 @@ bool use_dependent_launch() {
 namespace {
 
 constexpr int64_t kStreamMaxRows = 128;  // above this the automatic schedule uses the GEMM
+constexpr int64_t kDecodeMaxRows = 32;   // the persistent decode kernel handles up to this many rows
 
 bool valid_split(int s) { return s == 0 || s == 1 || s == 2 || s == 4 || s == 8 || s == 16; }
 
-// 0 = streaming kernel, 1 = tensor-memory GEMM
-int choose_kernel(int64_t m, int schedule) {
-  if (schedule == AQ_SCHEDULE_DECODE || schedule == AQ_SCHEDULE_PREFILL) return 0;
+// 0 = cluster streaming kernel, 1 = tensor-memory GEMM, 2 = persistent decode kernel
+int choose_kernel(int64_t m, int schedule, int decode_splits) {
   if (schedule == AQ_SCHEDULE_PREFILL_M64) return 1;
-  return m <= kStreamMaxRows ? 0 : 1;
+  if (schedule == AQ_SCHEDULE_AUTO && m > kStreamMaxRows) return 1;
+  return (decode_splits == 0 && m <= kDecodeMaxRows) ? 2 : 0;
 }
 
 }  // namespace
@@ -130,13 +131,18 @@ int aq_repack(const uint8_t* state_bits, const uint8_t* w4_payload, const float*
 
 int64_t aq_linear_workspace_bytes(int64_t m, int32_t n_j, int32_t n_k, int schedule,
                                   int decode_splits) {
-  (void)decode_splits;
   if (m < 1 || n_j <= 0 || n_k <= 0 || schedule < 0 || schedule > 3) {
     fail(AQ_ERR_INVALID, "aq_linear_workspace_bytes: invalid problem");
     return AQ_ERR_INVALID;
   }
-  if (choose_kernel(m, schedule) == 0) return 0;
-  return tmem_gemm_workspace_bytes(m, n_j, n_k);
+  switch (choose_kernel(m, schedule, decode_splits)) {
+    case 0:
+      return 0;
+    case 2:
+      return decode_workspace_bytes(m, n_j, n_k);
+    default:
+      return tmem_gemm_workspace_bytes(m, n_j, n_k);
+  }
 }
 
 int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
@@ -188,18 +194,24 @@ int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t
   a.workspace_bytes = workspace_bytes;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  if (choose_kernel(m, schedule) == 0) {
+  const int kernel = choose_kernel(m, schedule, decode_splits);
+  if (kernel == 0) {
     AQ_REQUIRE(decode_splits == 0 || m <= kStreamMaxRows,
                "split override requires at most 128 rows");
     const int split = decode_splits != 0 ? decode_splits : stream_auto_split(m, n_j, n_k);
     return launch_stream_linear(a, split, s);
   }
-  const int64_t need = tmem_gemm_workspace_bytes(m, n_j, n_k);
+  const int64_t need = kernel == 2 ? decode_workspace_bytes(m, n_j, n_k) : tmem_gemm_workspace_bytes(m, n_j, n_k);
   if (need > 0 && (workspace == nullptr || workspace_bytes < need || !aligned(workspace, 256))) {
     return fail(AQ_ERR_WORKSPACE, "aq_linear needs a 256-byte aligned workspace of %lld bytes",
                 static_cast<long long>(need));
   }
-  return launch_tmem_gemm(a, s);
+  return kernel == 2 ? launch_decode_linear(a, s) : launch_tmem_gemm(a, s);
+}
+
+int aq_decode_ctas(int32_t n_j, int32_t n_k) {
+  if (n_j <= 0 || n_k <= 0) return fail(AQ_ERR_INVALID, "aq_decode_ctas: n_j and n_k must be positive");
+  return decode_ctas(n_j, n_k);
 }
 
 int aq_device_status(void* stream) {
@@ -207,10 +219,15 @@ int aq_device_status(void* stream) {
   if (rc != AQ_OK) return rc;
   const int stream_status = take_stream_status();
   const int gemm_status = take_gemm_status();
-  if (stream_status < 0 || gemm_status < 0) return fail(AQ_ERR_CUDA, "could not read the device status words");
-  if (stream_status != 0 || gemm_status != 0) {
-    return fail(AQ_ERR_DEVICE, "a kernel wait timed out on the device (streaming kernel wait id %d, GEMM wait id %d)",
-                stream_status, gemm_status);
+  const int decode_status = take_decode_status();
+  if (stream_status < 0 || gemm_status < 0 || decode_status < 0) {
+    return fail(AQ_ERR_CUDA, "could not read the device status words");
+  }
+  if (stream_status != 0 || gemm_status != 0 || decode_status != 0) {
+    return fail(AQ_ERR_DEVICE,
+                "a kernel wait timed out on the device (wait ids: cluster kernel %d, GEMM %d, decode kernel %d); "
+                "outputs of that launch are invalid and any workspace must be zeroed again",
+                stream_status, gemm_status, decode_status);
   }
   return AQ_OK;
 }

@@ -76,6 +76,12 @@ struct LinearArgs {
 int launch_stream_linear(const LinearArgs& a, int split_k, cudaStream_t stream);
 int stream_auto_split(int64_t m, int n_j, int n_k);
 
+// Persistent stream-K kernel for m <= 32 (needs a zeroed, self-cleaning workspace).
+int launch_decode_linear(const LinearArgs& a, cudaStream_t stream);
+int64_t decode_workspace_bytes(int64_t m, int n_j, int n_k);
+int decode_ctas(int n_j, int n_k);
+int take_decode_status();
+
 // Tensor-memory GEMM (tcgen05) for large m.
 int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream);
 int64_t tmem_gemm_workspace_bytes(int64_t m, int n_j, int n_k);

@@ -288,7 +288,7 @@ def alignquant_linear_prepared(
         ws_bytes = int(lib.aq_linear_workspace_bytes(m, n_j, n_k, schedule_code, int(decode_splits)))
         if ws_bytes < 0:
             _lib.check(ws_bytes)
-        workspace = torch.empty((ws_bytes,), dtype=torch.uint8, device=device) if ws_bytes else None
+        workspace = _workspace(device, ws_bytes) if ws_bytes else None
         _lib.check(
             lib.aq_linear(
                 _ptr(x), _ptr(scales), mode, m, _ptr(weights.image), n_j, n_k, _ptr(meta), schedule_code,
@@ -297,6 +297,23 @@ def alignquant_linear_prepared(
             )
         )
     return out
+
+
+_WORKSPACES: dict[tuple, torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, size: int) -> torch.Tensor:
+    """Zeroed scratch for split-K partials, one per (device, stream).
+
+    The kernels leave the workspace zeroed, and calls on one stream run in order, so a
+    single buffer per stream is reused by every call; it only grows.
+    """
+    key = (device.index, _stream(device))
+    buffer = _WORKSPACES.get(key)
+    if buffer is None or buffer.numel() < size:
+        buffer = torch.zeros((max(size, 1 << 21),), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buffer
+    return buffer
 
 
 _PREPARED_CACHE: dict[tuple, PreparedWeights] = {}
@@ -355,7 +372,18 @@ def device_status(device: torch.device | str | None = None) -> None:
     """Synchronise the current stream and raise if a kernel gave up a device-side wait."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().aq_device_status(_stream(dev)))
+        status = _lib.load().aq_device_status(_stream(dev))
+        if status != _lib.AQ_OK:
+            _WORKSPACES.clear()  # arrival counters may be left non-zero by an aborted kernel
+        _lib.check(status)
+
+
+def decode_ctas(n_j: int, n_k: int) -> int:
+    """Number of tile ranges the persistent decode kernel uses for an n_j x n_k layer."""
+    value = int(_lib.load().aq_decode_ctas(int(n_j), int(n_k)))
+    if value < 0:
+        _lib.check(value)
+    return value
 
 
 __all__ = [
@@ -366,4 +394,5 @@ __all__ = [
     "prepare_weights",
     "PreparedWeights",
     "device_status",
+    "decode_ctas",
 ]

@@ -104,7 +104,13 @@ AQ_API int aq_repack(const uint8_t* state_bits, const uint8_t* w4_payload, const
               void* prepared, int64_t prepared_bytes, void* stream);
 
 /*
- * Bytes of workspace aq_linear needs for this problem (0 when none is needed).
+ * Bytes of workspace aq_linear needs for this problem (0 when none is needed).  The
+ * workspace holds split-K partial tiles and per-row arrival counters.  Its owner must
+ * zero it once before the first call; every call leaves it zeroed again, so it can be
+ * reused by later calls on the same stream.  Calls that may run concurrently (other
+ * streams) need separate workspaces.  After an AQ_ERR_DEVICE report zero it again.
+ * Replaces the per-call torch::empty of partial planes in the reference
+ * (alignquant/kernels/cuda/linear.cu:1692-1695).
  */
 AQ_API int64_t aq_linear_workspace_bytes(int64_t m, int32_t n_j, int32_t n_k, int schedule,
                                   int decode_splits);
@@ -124,8 +130,8 @@ AQ_API int64_t aq_linear_workspace_bytes(int64_t m, int32_t n_j, int32_t n_k, in
  *                 (only with AQ_SCHEDULE_AUTO/DECODE/PREFILL and m <= 128;
  *                 values above 8 run as 8)
  *   out_dtype     AQ_F32, AQ_BF16 or AQ_F16; out is [m][64*n_j], 16-byte aligned
- *   workspace     at least aq_linear_workspace_bytes() bytes, 256-byte aligned, or
- *                 NULL when that is 0
+ *   workspace     at least aq_linear_workspace_bytes() bytes, 256-byte aligned and
+ *                 zeroed by its owner (see above), or NULL when that is 0
  *   acc_dump      NULL, or int32 [m][n_j][n_k][64]: receives every per-tile integer
  *                 dot product (debug/verification aid; slows the call down)
  */
@@ -133,6 +139,16 @@ AQ_API int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, 
               const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
               int schedule, int decode_splits, int out_dtype, void* out,
               void* workspace, int64_t workspace_bytes, int32_t* acc_dump, void* stream);
+
+/*
+ * Number of contiguous tile ranges (CTAs) the persistent decode kernel cuts an
+ * n_j x n_k layer into on the current device.  Range i covers tiles
+ * [i*T/G, (i+1)*T/G) of the (j, k)-ordered tile sequence (T = n_j*n_k, G = result);
+ * partial sums of ranges that share a tile row are added in range order.  Exposed so
+ * that callers can reproduce the floating-point summation order; the reference's
+ * counterpart is its split-K heuristic (alignquant/kernels/cuda/linear.cu:1679-1691).
+ */
+AQ_API int aq_decode_ctas(int32_t n_j, int32_t n_k);
 
 /*
  * Synchronises `stream`, then returns AQ_ERR_DEVICE if a kernel of this library gave

@@ -116,7 +116,37 @@ def test_stream_linear_matches_oracle(ext, n, k, m, scale_mode):
         if split:
             want = oc.linear_fp32_c(xq_np, a_mk, tiles, scales, split)
             assert np.array_equal(got, want), f"fp32 result not in reference operation order (split {split})"
+        elif m <= 32:  # automatic schedule: persistent decode kernel, partial sums cut at its range borders
+            want = oc.linear_fp32_ranges_c(xq_np, a_mk, tiles, scales, ext.decode_ctas(n_j, n_k))
+            assert np.array_equal(got, want), "fp32 result differs from the range-ordered emulation"
         assert np.allclose(got, y64, rtol=REL, atol=ABS)
+
+
+@pytest.mark.parametrize("m", [1, 7, 16, 32])
+@pytest.mark.parametrize("n,k", [(3072, 3072), (1024, 8192), (5120, 256)])
+def test_decode_kernel_many_ranges(ext, n, k, m):
+    """Layers with more tiles than SMs: ranges start and end inside tile rows, rows are
+    finished by whichever CTA arrives last, and repeated calls reuse the workspace."""
+    n_j, n_k = n // 64, k // 64
+    packed, states, tiles, scales = oc.synthetic_layer(n, k, seed=n + k)
+    weights, _ = helpers.prepare_layer(packed, n_k)
+    xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=m), torch.float16)
+    for scale_mode in ("token", "tile"):
+        xq, a_s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode=scale_mode)
+        xq_np = xq.cpu().numpy()
+        if scale_mode == "token":
+            a_mk = oc.expand_act_scales(a_s.cpu().numpy(), m, n_k, "token")
+        else:
+            a_mk = np.repeat(a_s.cpu().numpy().reshape(-1, n_k), 16, axis=0)[:m]
+        want = oc.linear_fp32_ranges_c(xq_np, a_mk, tiles, scales, ext.decode_ctas(n_j, n_k))
+        for _ in range(3):
+            out = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode=scale_mode)
+            ext.device_status()
+            assert np.array_equal(out.cpu().numpy(), want)
+    dump = torch.zeros((m, n_j, n_k, 64), dtype=torch.int32, device="cuda")
+    ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="tile", acc_dump=dump)
+    ext.device_status()
+    assert np.array_equal(dump.cpu().numpy(), oc.tile_accumulators_c(xq_np, tiles))
 
 
 @pytest.mark.parametrize("fraction", [0.0, 1.0])
