@@ -61,6 +61,8 @@ constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kXRowStride = 80;  // 64 activation bytes + 16 bytes of bank-spreading pad
 constexpr int kMaxRecords = 1024;
 constexpr int kNumBars = 2 * kStages;
+constexpr int kMaxCounterRows = 16384;  // counters occupy a fixed region so that one workspace serves any layer
+constexpr int64_t kCounterBytes = static_cast<int64_t>(kMaxCounterRows) * 4;
 
 __host__ __device__ constexpr int stage_bytes(int mt) { return kW8TileBytes + 16 * mt * kXRowStride; }
 
@@ -379,11 +381,13 @@ int decode_ctas(int n_j, int n_k) {
 
 int64_t decode_workspace_bytes(int64_t m, int n_j, int n_k) {
   const int mt = m <= 16 ? 1 : 2;
-  const int64_t counters = (static_cast<int64_t>(n_j) * 4 + 255) / 256 * 256;
-  return counters + partial_bytes(decode_ctas(n_j, n_k), mt);
+  return kCounterBytes + partial_bytes(decode_ctas(n_j, n_k), mt);
 }
 
 int launch_decode_linear(const LinearArgs& a, cudaStream_t stream) {
+  if (a.n_j > kMaxCounterRows) {
+    return fail(AQ_ERR_INVALID, "the decode kernel supports N up to %d, got %d", kMaxCounterRows * kTile, a.n_j * kTile);
+  }
   DecodeParams p;
   p.xq = a.xq;
   p.act_scales = a.act_scales;
@@ -393,8 +397,7 @@ int launch_decode_linear(const LinearArgs& a, cudaStream_t stream) {
   p.out = a.out;
   p.acc_dump = a.acc_dump;
   p.counters = static_cast<int32_t*>(a.workspace);
-  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) +
-                                        (static_cast<int64_t>(a.n_j) * 4 + 255) / 256 * 256);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + kCounterBytes);
   p.m = a.m;
   p.total_tiles = static_cast<int64_t>(a.n_j) * a.n_k;
   p.n_j = a.n_j;

@@ -105,9 +105,10 @@ AQ_API int aq_repack(const uint8_t* state_bits, const uint8_t* w4_payload, const
 
 /*
  * Bytes of workspace aq_linear needs for this problem (0 when none is needed).  The
- * workspace holds split-K partial tiles and per-row arrival counters.  Its owner must
- * zero it once before the first call; every call leaves it zeroed again, so it can be
- * reused by later calls on the same stream.  Calls that may run concurrently (other
+ * workspace holds per-row arrival counters (its first 64 KiB) followed by split-K
+ * partial tiles.  Its owner must zero it once before the first call; every call
+ * returns the counters to zero, so one buffer can be reused by later calls on the same
+ * stream, for any layer.  Calls that may run concurrently (other
  * streams) need separate workspaces.  After an AQ_ERR_DEVICE report zero it again.
  * Replaces the per-call torch::empty of partial planes in the reference
  * (alignquant/kernels/cuda/linear.cu:1692-1695).
