@@ -10,7 +10,9 @@
 // first ring fill are issued before the grid dependency is resolved, so under
 // programmatic dependent launch they overlap the tail of the preceding kernel.
 // Eight consumer warps (8 output columns each) run the integer dot products on
-// mma.sync.m16n8k32.s8 exactly as in the cluster kernel (aq_stream.cu).
+// mma.sync.m16n8k32.s8 (aq_tile_math.cuh), several tiles per loop trip so that the
+// waits, shared-memory loads and MMAs of neighbouring tiles overlap; the FP32
+// accumulation still visits the tiles in increasing k.
 //
 // A CTA range may start and end in the middle of a tile row.  A row that lies entirely
 // inside one range is finished by that CTA.  Otherwise each CTA writes its partial
@@ -28,6 +30,7 @@
 
 #include "aq_common.cuh"
 #include "aq_ptx.cuh"
+#include "aq_tile_math.cuh"
 
 namespace aq {
 
@@ -58,7 +61,7 @@ constexpr int kStages = 16;
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
-constexpr int kXRowStride = 80;  // 64 activation bytes + 16 bytes of bank-spreading pad
+constexpr int kXRowStride = 64;  // one K64 block of one activation row
 constexpr int kMaxRecords = 1024;
 constexpr int kNumBars = 2 * kStages;
 constexpr int kMaxCounterRows = 16384;  // counters occupy a fixed region so that one workspace serves any layer
@@ -66,26 +69,7 @@ constexpr int64_t kCounterBytes = static_cast<int64_t>(kMaxCounterRows) * 4;
 
 __host__ __device__ constexpr int stage_bytes(int mt) { return kW8TileBytes + 16 * mt * kXRowStride; }
 
-__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                       uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-
-__device__ __forceinline__ void store_any(void* out, int dtype, int64_t index, float value) {
-  if (dtype == AQ_F32) {
-    static_cast<float*>(out)[index] = value;
-  } else if (dtype == AQ_BF16) {
-    static_cast<__nv_bfloat16*>(out)[index] = __float2bfloat16_rn(value);
-  } else {
-    static_cast<__half*>(out)[index] = __float2half_rn(value);
-  }
-}
 
 // first tile of CTA i, and the CTA that owns tile t, for T tiles cut into G ranges
 __device__ __forceinline__ int64_t range_begin(int64_t i, int64_t total, int ctas) { return i * total / ctas; }
@@ -178,7 +162,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Decode
   // ---- consumers: warp w owns output columns 8w .. 8w+7 --------------------------------
   const int g = lane >> 2;
   const int c = lane & 3;
-  const uint32_t lane_word = static_cast<uint32_t>(warp * 128 + g * 16 + c * 4);
+  const int n = warp * 8 + g;
+  constexpr int kUnroll = MT == 1 ? 4 : 2;
   float token_scale[MT][2];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
@@ -197,6 +182,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Decode
     const int64_t row_end = static_cast<int64_t>(j + 1) * n_k;
     const int seg_tiles = static_cast<int>((row_end < t1 ? row_end : t1) - t_first);
     const bool whole_row = k_lo == 0 && seg_tiles == n_k;
+    const int seg_begin = i;
 
     float acc[MT][4];
 #pragma unroll
@@ -204,76 +190,79 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Decode
 #pragma unroll
       for (int q = 0; q < 4; ++q) acc[mt][q] = 0.0f;
     }
-    for (int e = i + seg_tiles; i < e; ++i) {
-      const int s = i % kStages;
-      const int kt = k_lo + (i - static_cast<int>(t_first - t0));
-      if (!mbar_wait(full(s), (i / kStages) & 1, abort_flag, &g_decode_status, 22)) {
-        ok = false;
-        break;
+    const int seg_end = i + seg_tiles;
+    while (i < seg_end && ok) {
+      const int batch = seg_end - i < kUnroll ? seg_end - i : kUnroll;
+      TileRecord rec[kUnroll];
+      int d[kUnroll][MT][4];
+      // waits first, then every load, then every MMA: independent chains the scheduler can overlap
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (u < batch && ok) {
+          ok = mbar_wait(full((i + u) % kStages), ((i + u) / kStages) & 1, abort_flag, &g_decode_status, 22);
+        }
       }
-      const TileRecord r = recs[i];
-      const bool is_w4 = (r.offset_flag & kW4Flag) != 0;
-      const uint8_t* stage = ring + s * kStage;
-      const uint8_t* wptr = stage + lane_word;
-      uint32_t b[4];
-      if (is_w4) {
-        const uint32_t p0 = *reinterpret_cast<const uint32_t*>(wptr);
-        const uint32_t p1 = *reinterpret_cast<const uint32_t*>(wptr + 1024);
-        b[0] = (p0 << 4) & 0xf0f0f0f0u;
-        b[1] = p0 & 0xf0f0f0f0u;
-        b[2] = (p1 << 4) & 0xf0f0f0f0u;
-        b[3] = p1 & 0xf0f0f0f0u;
-      } else {
+      if (!ok) break;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const uint32_t*>(wptr + q * 1024);
-      }
+      for (int u = 0; u < kUnroll; ++u) {
+        if (u < batch) {
+          rec[u] = recs[i + u];
+          const uint8_t* stage = ring + ((i + u) % kStages) * kStage;
+          const uint4 w = load_weight_vector(stage, (rec[u].offset_flag & kW4Flag) != 0, n, c);
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        const int r_lo = mt * 16 + g;
-        const int r_hi = r_lo + 8;
-        uint32_t a_lo[4] = {0, 0, 0, 0}, a_hi[4] = {0, 0, 0, 0};
-        const uint8_t* x_lo = stage + kW8TileBytes + r_lo * kXRowStride + c * 4;
-        if (r_lo < rows) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) a_lo[q] = *reinterpret_cast<const uint32_t*>(x_lo + q * 16);
-        }
-        if (r_hi < rows) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) a_hi[q] = *reinterpret_cast<const uint32_t*>(x_lo + 8 * kXRowStride + q * 16);
-        }
-        int d[4] = {0, 0, 0, 0};
-        mma_s8(d, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[0], b[1]);
-        mma_s8(d, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[2], b[3]);
-        float s_lo, s_hi;
-        if (p.scale_mode == AQ_SCALE_TOKEN) {
-          s_lo = __fmul_rn(token_scale[mt][0], r.scale);
-          s_hi = __fmul_rn(token_scale[mt][1], r.scale);
-        } else {
-          const float a_s = (mt * 16 < rows) ? p.act_scales[static_cast<int64_t>(mt) * n_k + kt] : 0.0f;
-          s_lo = s_hi = __fmul_rn(a_s, r.scale);
-        }
-        acc[mt][0] = __fadd_rn(acc[mt][0], __fmul_rn(static_cast<float>(d[0]), s_lo));
-        acc[mt][1] = __fadd_rn(acc[mt][1], __fmul_rn(static_cast<float>(d[1]), s_lo));
-        acc[mt][2] = __fadd_rn(acc[mt][2], __fmul_rn(static_cast<float>(d[2]), s_hi));
-        acc[mt][3] = __fadd_rn(acc[mt][3], __fmul_rn(static_cast<float>(d[3]), s_hi));
-        if (p.acc_dump != nullptr) {
-          const int shift = is_w4 ? 4 : 0;
-          const int col_out = warp * 8 + 2 * c;
-          if (r_lo < rows) {
-            int32_t* o = p.acc_dump + ((static_cast<int64_t>(r_lo) * p.n_j + j) * n_k + kt) * kTile + col_out;
-            o[0] = d[0] >> shift;
-            o[1] = d[1] >> shift;
-          }
-          if (r_hi < rows) {
-            int32_t* o = p.acc_dump + ((static_cast<int64_t>(r_hi) * p.n_j + j) * n_k + kt) * kTile + col_out;
-            o[0] = d[2] >> shift;
-            o[1] = d[3] >> shift;
+          for (int mt = 0; mt < MT; ++mt) {
+            const int r_lo = mt * 16 + g;
+            uint4 x_lo = make_uint4(0, 0, 0, 0), x_hi = make_uint4(0, 0, 0, 0);
+            const uint8_t* xp = stage + kW8TileBytes + r_lo * kXRowStride + c * 16;
+            if (r_lo < rows) x_lo = *reinterpret_cast<const uint4*>(xp);
+            if (r_lo + 8 < rows) x_hi = *reinterpret_cast<const uint4*>(xp + 8 * kXRowStride);
+            tile_dot(d[u][mt], x_lo, x_hi, w);
           }
         }
       }
-      // every lane's operand words have been consumed by the warp-wide MMAs above
+      // every lane's operands have been consumed by the warp-wide MMAs above
       __syncwarp();
-      if (lane == 0 && i + kStages < count) mbar_arrive(empty(s));
+      if (lane == 0) {
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          if (u < batch && i + u + kStages < count) mbar_arrive(empty((i + u) % kStages));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (u < batch) {
+          const int kt = k_lo + (i + u - seg_begin);
+          const bool is_w4 = (rec[u].offset_flag & kW4Flag) != 0;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            float s_lo, s_hi;
+            if (p.scale_mode == AQ_SCALE_TOKEN) {
+              s_lo = __fmul_rn(token_scale[mt][0], rec[u].scale);
+              s_hi = __fmul_rn(token_scale[mt][1], rec[u].scale);
+            } else {
+              const float a_s = (mt * 16 < rows) ? p.act_scales[static_cast<int64_t>(mt) * n_k + kt] : 0.0f;
+              s_lo = s_hi = __fmul_rn(a_s, rec[u].scale);
+            }
+            tile_accumulate(acc[mt], d[u][mt], s_lo, s_hi);
+            if (p.acc_dump != nullptr) {
+              const int shift = is_w4 ? 4 : 0;
+              const int col_out = warp * 8 + 2 * c;
+              const int r_lo = mt * 16 + g;
+              if (r_lo < rows) {
+                int32_t* o = p.acc_dump + ((static_cast<int64_t>(r_lo) * p.n_j + j) * n_k + kt) * kTile + col_out;
+                o[0] = d[u][mt][0] >> shift;
+                o[1] = d[u][mt][1] >> shift;
+              }
+              if (r_lo + 8 < rows) {
+                int32_t* o = p.acc_dump + ((static_cast<int64_t>(r_lo + 8) * p.n_j + j) * n_k + kt) * kTile + col_out;
+                o[0] = d[u][mt][2] >> shift;
+                o[1] = d[u][mt][3] >> shift;
+              }
+            }
+          }
+        }
+      }
+      i += batch;
     }
     if (!ok) break;
 
@@ -291,7 +280,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Decode
     bool finish = whole_row;
     if (!whole_row) {
       // partial: publish to the workspace; the last arriver of the row finishes it
-      const int slot = 2 * blockIdx.x + (i == seg_tiles ? 0 : 1);  // 0: first segment of this CTA
+      const int slot = 2 * blockIdx.x + (seg_begin == 0 ? 0 : 1);  // 0: first segment of this CTA
       float* dst = p.partials + static_cast<int64_t>(slot) * kRows * kTile;
       for (int e = threadIdx.x; e < rows * kTile; e += kConsumerThreads) __stcg(dst + e, tile[e]);
       __threadfence();

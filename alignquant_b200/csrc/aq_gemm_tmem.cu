@@ -4,8 +4,8 @@
 // rows) and walks K in 64-wide steps.  Per step:
 //   * one elected thread streams the step's weight tiles from the prepared image into
 //     shared memory with bulk asynchronous copies (cp.async.bulk, completion counted
-//     on an mbarrier); W8 tiles land directly in the operand layout, W4 tiles land
-//     packed in a staging area;
+//     on an mbarrier); a W8 tile is already in the 64-byte-swizzled K-major operand
+//     layout and lands in place with one copy, W4 tiles land packed in a staging area;
 //   * the producer warp copies the 128 x 64 int8 activation block with 16-byte
 //     cp.async into the same K-major "core matrix" layout (8 rows x 16 bytes);
 //   * two warps widen staged W4 tiles to int8 (value 16*w: one shift, one mask) into
@@ -26,6 +26,7 @@
 
 #include "aq_common.cuh"
 #include "aq_ptx.cuh"
+#include "aq_tile_math.cuh"
 
 namespace aq {
 
@@ -106,27 +107,22 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, int (&v)[32]) {
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// K-major, no swizzle: 8-row x 16-byte core matrices; LBO = byte step between the two
-// 16-byte K chunks of one MMA, SBO = byte step between 8-row groups.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+// K-major shared-memory operand descriptor.  Without swizzle the operand is made of
+// 8-row x 16-byte core matrices: LBO = byte step between the two 16-byte K chunks of one
+// MMA, SBO = byte step between 8-row groups.  With the 64-byte swizzle a row is 64
+// contiguous bytes whose 16-byte chunks are XOR-ed with address bits 7-8, SBO is the
+// step between 8-row groups (512 B) and LBO is not used (encoded as 16 B).
+constexpr uint32_t kSwizzle64 = 4;
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
   return static_cast<uint64_t>((addr & 0x3ffffu) >> 4) |
          (static_cast<uint64_t>((lbo >> 4) & 0x3fffu) << 16) |
-         (static_cast<uint64_t>((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
+         (static_cast<uint64_t>((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46) |
+         (static_cast<uint64_t>(layout) << 61);
 }
 // kind::i8: D = S32 (2), A = B = signed 8-bit (1), both K-major, M = 128.
 __device__ __forceinline__ uint32_t instr_desc_i8(int n) {
   return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(kBM >> 4) << 24);
-}
-
-__device__ __forceinline__ void store_any(void* out, int dtype, int64_t index, float value) {
-  if (dtype == AQ_F32) {
-    static_cast<float*>(out)[index] = value;
-  } else if (dtype == AQ_BF16) {
-    static_cast<__nv_bfloat16*>(out)[index] = __float2bfloat16_rn(value);
-  } else {
-    static_cast<__half*>(out)[index] = __float2half_rn(value);
-  }
 }
 
 __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams p) {
@@ -211,10 +207,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
             if (of & kW4Flag) {
               bulk_copy(p_addr + t * kW4TileBytes, src, kW4TileBytes, raw_full(s));
             } else {
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                bulk_copy(b_addr + c * 4096 + t * 1024, src + c * 1024, 1024, raw_full(s));
-              }
+              bulk_copy(b_addr + t * kW8TileBytes, src, kW8TileBytes, raw_full(s));
             }
           }
         }
@@ -264,8 +257,11 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
           const uint32_t a_addr = smem_u32(stages + s * kStageBytes);
           const uint32_t b_addr = a_addr + kABytes;
           const uint32_t d = tmem_base + static_cast<uint32_t>(b) * 256u;
-          tc_mma_i8(d, smem_desc(a_addr, 2048, 128), smem_desc(b_addr, 4096, 128), idesc, 0u);
-          tc_mma_i8(d, smem_desc(a_addr + 4096, 2048, 128), smem_desc(b_addr + 8192, 4096, 128), idesc, 1u);
+          // A: no swizzle, 16-byte K chunks 2048 B apart, 8-row groups 128 B apart.
+          // B: 64-byte swizzle, rows of 64 B, 8-row groups 512 B apart; the second K32
+          // half of a row starts 32 B further on.
+          tc_mma_i8(d, smem_desc(a_addr, 2048, 128, 0), smem_desc(b_addr, 16, 512, kSwizzle64), idesc, 0u);
+          tc_mma_i8(d, smem_desc(a_addr + 4096, 2048, 128, 0), smem_desc(b_addr + 32, 16, 512, kSwizzle64), idesc, 1u);
           tc_commit(empty(s));
           tc_commit(acc_full(b));
         }
@@ -289,8 +285,11 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
         for (int t = 0; t < tiles_here; ++t) {
           if (rec_smem[t * kMaxNk + kt].offset_flag & kW4Flag) {
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const uint4 pk = *reinterpret_cast<const uint4*>(p_s + t * kW4TileBytes + (h * 64 + u) * 16);
+            for (int rep = 0; rep < 2; ++rep) {
+              // packed chunk q = 2*n + h: low nibbles are k16 block 2h of row n, high nibbles 2h+1
+              const int q = rep * 64 + u;
+              const int n = q >> 1, h = q & 1;
+              const uint4 pk = *reinterpret_cast<const uint4*>(p_s + t * kW4TileBytes + q * 16);
               uint4 lo, hi;
               lo.x = (pk.x << 4) & 0xf0f0f0f0u;
               lo.y = (pk.y << 4) & 0xf0f0f0f0u;
@@ -300,9 +299,10 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
               hi.y = pk.y & 0xf0f0f0f0u;
               hi.z = pk.z & 0xf0f0f0f0u;
               hi.w = pk.w & 0xf0f0f0f0u;
-              uint8_t* dst = b_s + (2 * h) * 4096 + t * 1024 + u * 16;
-              *reinterpret_cast<uint4*>(dst) = lo;
-              *reinterpret_cast<uint4*>(dst + 4096) = hi;
+              uint8_t* row = b_s + t * kW8TileBytes + n * 64;
+              const int swz = (n >> 1) & 3;
+              *reinterpret_cast<uint4*>(row + (((2 * h) ^ swz) << 4)) = lo;
+              *reinterpret_cast<uint4*>(row + (((2 * h + 1) ^ swz) << 4)) = hi;
             }
           }
         }

@@ -8,10 +8,12 @@
 // W4 tiles store the same order two values per byte, low nibble first.
 //
 // Destination (include/alignquant_b200.h): tiles in (j, k) order behind an array of
-// 8-byte records; a W8 tile is [k/16][n/8][n%8][k%16] (the K-major "core matrix"
-// order tcgen05.mma reads without swizzle: 8 rows x 16 bytes contiguous), a W4 tile
-// is [k/32][n/8][n%8][16 B] with the two 16-k halves of a 32-k block in the low and
-// high nibbles of the same bytes, so one shift-and-mask widens a word.
+// 8-byte records.  A W8 tile is 64 rows (output columns n) of 64 bytes (k), the
+// 16-byte chunk c = k/16 of row n stored at slot c ^ ((n/2) % 4): the K-major
+// 64-byte-swizzle operand layout of tcgen05.mma, which also makes the small-M
+// kernels' 16-byte shared-memory reads conflict free.  A W4 tile is 64 rows of 32
+// bytes: chunk h = k/32 holds k%32 < 16 in the low nibbles and k%32 >= 16 in the high
+// nibbles of the same bytes, so one shift-and-mask widens a word.
 #include "aq_common.cuh"
 
 namespace aq {
@@ -65,17 +67,16 @@ __global__ void __launch_bounds__(256) repack_kernel(
   }
 
   if (!is_w4) {
-    // destination row r = (k16*8 + n8)*8 + g  <-  Layout-B vector of (n = 8*n8+g, k16)
+    // destination chunk r = 4*n + slot  <-  Layout-B vector of (n, k16 = slot ^ ((n/2)%4))
     const uint4* src = reinterpret_cast<const uint4*>(w8_payload + index8 * kW8TileBytes);
     const int r = threadIdx.x;
-    const int g = r & 7, n8 = (r >> 3) & 7, k16 = r >> 6;
-    reinterpret_cast<uint4*>(dst)[r] = src[layout_b_vector(8 * n8 + g, k16)];
+    const int n = r >> 2, slot = r & 3;
+    reinterpret_cast<uint4*>(dst)[r] = src[layout_b_vector(n, slot ^ ((n >> 1) & 3))];
   } else if (threadIdx.x < 128) {
-    // destination chunk c = (h*8 + n8)*8 + g; a source vector of 16 int4 is 8 bytes
+    // destination chunk u = 2*n + h; a source vector of 16 int4 is 8 bytes
     const uint2* src = reinterpret_cast<const uint2*>(w4_payload + index4 * kW4TileBytes);
-    const int c = threadIdx.x;
-    const int g = c & 7, n8 = (c >> 3) & 7, h = c >> 6;
-    const int n = 8 * n8 + g;
+    const int u = threadIdx.x;
+    const int n = u >> 1, h = u & 1;
     const uint2 a = src[layout_b_vector(n, 2 * h)];      // k%32 in [0,16): nibble i = k offset i
     const uint2 b = src[layout_b_vector(n, 2 * h + 1)];  // k%32 in [16,32)
     const uint64_t av = (static_cast<uint64_t>(a.y) << 32) | a.x;
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(256) repack_kernel(
       }
       out[w] = word;
     }
-    reinterpret_cast<uint4*>(dst)[c] = make_uint4(out[0], out[1], out[2], out[3]);
+    reinterpret_cast<uint4*>(dst)[u] = make_uint4(out[0], out[1], out[2], out[3]);
   }
 }
 

@@ -6,11 +6,10 @@
 // prepared image into a shared-memory ring with one bulk asynchronous copy per tile
 // (cp.async.bulk, completion counted on an mbarrier) and stages the CTA's slice of
 // the int8 activations once.  Eight consumer warps, one per 8 output columns, read
-// their 32-bit operand words from shared memory without bank conflicts and run the
-// integer dot products on mma.sync.m16n8k32.s8, so 1..16 rows cost the same; W4
-// nibbles are widened with one shift and one mask to 16*w (the factor 1/16 is folded
-// into the tile scale, which is exact).  The contraction index of the MMA is a
-// permutation of the real k; it is the same permutation for both operands.
+// their operands with conflict-free 16-byte shared-memory loads and run the integer
+// dot products on mma.sync.m16n8k32.s8, so 1..16 rows cost the same (aq_tile_math.cuh);
+// W4 nibbles are widened with one shift and one mask to 16*w (the factor 1/16 is
+// folded into the tile scale, which is exact).
 //
 // Each K64 tile's int32 result is converted to FP32, multiplied by
 // (activation scale * tile scale) and added to an FP32 accumulator with separately
@@ -26,6 +25,7 @@
 
 #include "aq_common.cuh"
 #include "aq_ptx.cuh"
+#include "aq_tile_math.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -48,7 +48,7 @@ struct StreamParams {
   int n_k;
   int scale_mode;
   int out_dtype;
-  int x_stride;  // bytes between staged activation rows: 64 * k_count + 16
+  int x_stride;  // bytes between staged activation rows, congruent to 64 modulo 128
 };
 
 constexpr int kStages = 8;
@@ -58,25 +58,6 @@ constexpr int kMaxCount = 512;             // tiles of one CTA's K range
 constexpr int kMaxXBytes = 96 * 1024;      // staged activation slice
 constexpr int kNumBars = 2 * kStages + 1;  // full[], empty[], x_full
 constexpr int kBarRegionBytes = (kNumBars + 3) * 8;  // barriers, abort flag, padding to 16 bytes
-
-__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
-                                       uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ void store_any(void* out, int dtype, int64_t index, float value) {
-  if (dtype == AQ_F32) {
-    static_cast<float*>(out)[index] = value;
-  } else if (dtype == AQ_BF16) {
-    static_cast<__nv_bfloat16*>(out)[index] = __float2bfloat16_rn(value);
-  } else {
-    static_cast<__half*>(out)[index] = __float2half_rn(value);
-  }
-}
 
 // Shared memory: [ring kStages x 4096][tile MT*16 x 64 f32][records k_count x 8]
 //                [barriers][abort flag][activation slice rows x x_stride]
@@ -173,7 +154,7 @@ __global__ void __launch_bounds__(kThreads) stream_linear_kernel(const StreamPar
     // ---- consumers: warp w owns output columns 8w .. 8w+7 ---------------------------
     const int g = lane >> 2;
     const int c = lane & 3;
-    const uint32_t lane_word = static_cast<uint32_t>(warp * 128 + g * 16 + c * 4);
+    const int n = warp * 8 + g;
     float token_scale[MT][2];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
@@ -189,37 +170,17 @@ __global__ void __launch_bounds__(kThreads) stream_linear_kernel(const StreamPar
       if (!mbar_wait(full(s), (i / kStages) & 1, abort_flag, &g_stream_status, 13)) break;
       const TileRecord r = recs[i];
       const bool is_w4 = (r.offset_flag & kW4Flag) != 0;
-      const uint8_t* stage = ring + s * kW8TileBytes + lane_word;
-      uint32_t b[4];
-      if (is_w4) {
-        const uint32_t p0 = *reinterpret_cast<const uint32_t*>(stage);
-        const uint32_t p1 = *reinterpret_cast<const uint32_t*>(stage + 1024);
-        b[0] = (p0 << 4) & 0xf0f0f0f0u;
-        b[1] = p0 & 0xf0f0f0f0u;
-        b[2] = (p1 << 4) & 0xf0f0f0f0u;
-        b[3] = p1 & 0xf0f0f0f0u;
-      } else {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) b[q] = *reinterpret_cast<const uint32_t*>(stage + q * 1024);
-      }
+      const uint4 w = load_weight_vector(ring + s * kW8TileBytes, is_w4, n, c);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const int r_lo = mt * 16 + g;
         const int r_hi = r_lo + 8;
-        uint32_t a_lo[4] = {0, 0, 0, 0}, a_hi[4] = {0, 0, 0, 0};
-        const uint8_t* x_lo = xs + r_lo * p.x_stride + i * kTile + c * 4;
-        const uint8_t* x_hi = x_lo + 8 * p.x_stride;
-        if (r_lo < rows) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) a_lo[q] = *reinterpret_cast<const uint32_t*>(x_lo + q * 16);
-        }
-        if (r_hi < rows) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) a_hi[q] = *reinterpret_cast<const uint32_t*>(x_hi + q * 16);
-        }
-        int d[4] = {0, 0, 0, 0};
-        mma_s8(d, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[0], b[1]);
-        mma_s8(d, a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[2], b[3]);
+        uint4 x_lo = make_uint4(0, 0, 0, 0), x_hi = make_uint4(0, 0, 0, 0);
+        const uint8_t* xp = xs + r_lo * p.x_stride + i * kTile + c * 16;
+        if (r_lo < rows) x_lo = *reinterpret_cast<const uint4*>(xp);
+        if (r_hi < rows) x_hi = *reinterpret_cast<const uint4*>(xp + 8 * p.x_stride);
+        int d[4];
+        tile_dot(d, x_lo, x_hi, w);
         float s_lo, s_hi;
         if (p.scale_mode == AQ_SCALE_TOKEN) {
           s_lo = __fmul_rn(token_scale[mt][0], r.scale);
@@ -229,10 +190,7 @@ __global__ void __launch_bounds__(kThreads) stream_linear_kernel(const StreamPar
           const float a_s = (mtile * 16 < p.m) ? p.act_scales[mtile * n_k + kt] : 0.0f;
           s_lo = s_hi = __fmul_rn(a_s, r.scale);
         }
-        acc[mt][0] = __fadd_rn(acc[mt][0], __fmul_rn(static_cast<float>(d[0]), s_lo));
-        acc[mt][1] = __fadd_rn(acc[mt][1], __fmul_rn(static_cast<float>(d[1]), s_lo));
-        acc[mt][2] = __fadd_rn(acc[mt][2], __fmul_rn(static_cast<float>(d[2]), s_hi));
-        acc[mt][3] = __fadd_rn(acc[mt][3], __fmul_rn(static_cast<float>(d[3]), s_hi));
+        tile_accumulate(acc[mt], d, s_lo, s_hi);
         if (p.acc_dump != nullptr) {
           const int shift = is_w4 ? 4 : 0;
           const int col_out = warp * 8 + 2 * c;
@@ -285,9 +243,12 @@ __global__ void __launch_bounds__(kThreads) stream_linear_kernel(const StreamPar
   cluster.sync();  // peers may still be reading this CTA's tile
 }
 
+// bytes between staged activation rows: 64 * k_count rounded so that it is 64 modulo 128
+int x_row_stride(int k_count) { return k_count * kTile + ((k_count & 1) ? 0 : kTile); }
+
 int smem_bytes(int mt, int k_count, int rows) {
   return kStages * kW8TileBytes + mt * 16 * kTile * 4 + ((k_count + 1) & ~1) * 8 + kBarRegionBytes +
-         rows * (k_count * kTile + 16);
+         rows * x_row_stride(k_count);
 }
 
 template <int MT>
@@ -345,13 +306,13 @@ int launch_stream_linear(const LinearArgs& a, int split_k, cudaStream_t stream) 
   // rows per CTA: as many as the staged activation slice allows; more splits shorten it
   int rows = rows_per_cta(a.m);
   auto max_count = [&](int s) { return (a.n_k + s - 1) / s; };
-  while (rows > 16 && static_cast<int64_t>(rows) * (max_count(split_k) * kTile + 16) > kMaxXBytes) rows /= 2;
+  while (rows > 16 && static_cast<int64_t>(rows) * x_row_stride(max_count(split_k)) > kMaxXBytes) rows /= 2;
   while (split_k < 8 && split_k * 2 <= a.n_k &&
-         (static_cast<int64_t>(rows) * (max_count(split_k) * kTile + 16) > kMaxXBytes || max_count(split_k) > kMaxCount)) {
+         (static_cast<int64_t>(rows) * x_row_stride(max_count(split_k)) > kMaxXBytes || max_count(split_k) > kMaxCount)) {
     split_k *= 2;
   }
   const int k_count = max_count(split_k);
-  if (k_count > kMaxCount || static_cast<int64_t>(rows) * (k_count * kTile + 16) > kMaxXBytes) {
+  if (k_count > kMaxCount || static_cast<int64_t>(rows) * x_row_stride(k_count) > kMaxXBytes) {
     return fail(AQ_ERR_INVALID, "the streaming kernel supports K up to %d, got %d", 8 * kMaxXBytes / 16,
                 a.n_k * kTile);
   }
@@ -368,7 +329,7 @@ int launch_stream_linear(const LinearArgs& a, int split_k, cudaStream_t stream) 
   p.n_k = a.n_k;
   p.scale_mode = a.scale_mode;
   p.out_dtype = a.out_dtype;
-  p.x_stride = k_count * kTile + 16;
+  p.x_stride = x_row_stride(k_count);
   switch (rows) {
     case 16:
       return launch_mt<1>(p, split_k, k_count, stream);

@@ -93,8 +93,9 @@ AQ_API int64_t aq_prepared_bytes(int32_t n_j, int32_t n_k, int64_t t4, int64_t t
  *
  * Image: n_j*n_k 8-byte tile records {uint32 offset/2048 | W4 flag in bit 31,
  * float32 scale (W4: scale/16)}, padded to 2048 bytes, followed by the tiles in
- * (j, k) order: W8 tile = 4096 B as [k/16][n/8][n%8][k%16]; W4 tile = 2048 B as
- * [k/32][n/8][n%8][16 B], byte i = (w[n][32h+i] & 15) | (w[n][32h+16+i] << 4).
+ * (j, k) order.  W8 tile = 4096 B: 64 rows (output column n) of 64 bytes, the 16-byte
+ * chunk c = k/16 of row n stored at slot c ^ ((n/2) % 4).  W4 tile = 2048 B: 64 rows of
+ * 32 bytes, byte 16h+i of row n = (w[n][32h+i] & 15) | (w[n][32h+16+i] << 4).
  * `prepared` must be 256-byte aligned and at least aq_prepared_bytes() long.
  */
 AQ_API int aq_repack(const uint8_t* state_bits, const uint8_t* w4_payload, const float* w4_scales,

@@ -18,16 +18,20 @@ def expected_image(states: np.ndarray, tiles: np.ndarray, scales: np.ndarray):
         for k in range(n_k):
             t = tiles[j, k]  # [n, kk]
             if states[j, k] == oc.P4:
-                v = t.reshape(8, 8, 2, 2, 16).astype(np.uint8)
-                byte = (v[:, :, :, 0, :] & 15) | ((v[:, :, :, 1, :] & 15) << 4)
-                chunks.append(np.ascontiguousarray(byte.transpose(2, 0, 1, 3)).reshape(-1))
+                v = t.reshape(64, 2, 2, 16).astype(np.uint8)  # [n][h][half][i]
+                byte = (v[:, :, 0, :] & 15) | ((v[:, :, 1, :] & 15) << 4)
+                chunks.append(np.ascontiguousarray(byte).reshape(-1))
                 offsets.append(units)
                 flags.append(1)
                 rec_scales.append(np.float32(scales[j, k]) * np.float32(0.0625))
                 units += 1
             else:
-                v = t.reshape(8, 8, 4, 16)
-                chunks.append(np.ascontiguousarray(v.transpose(2, 0, 1, 3)).reshape(-1).view(np.uint8))
+                v = t.reshape(64, 4, 16)  # [n][c][i]
+                out = np.empty_like(v)
+                n = np.arange(64)
+                for c in range(4):
+                    out[n, c ^ ((n >> 1) & 3)] = v[n, c]
+                chunks.append(out.reshape(-1).view(np.uint8))
                 offsets.append(units)
                 flags.append(0)
                 rec_scales.append(np.float32(scales[j, k]))
