@@ -4,14 +4,14 @@
 // is built to keep one uninterrupted byte stream per SM.  The layer's tiles are
 // stored in (j, k) order in the prepared image; that 1-D sequence of T tiles is cut
 // into G equal contiguous ranges, one per CTA, one CTA per SM ("stream-K").  Each
-// CTA's producer warp streams its range through a deep shared-memory ring with bulk
-// asynchronous copies: one copy per weight tile and one 64-byte copy per activation
-// row of that K64 block, all counted on the stage's mbarrier.  Weight copies of the
-// first ring fill are issued before the grid dependency is resolved, so under
-// programmatic dependent launch they overlap the tail of the preceding kernel.
-// Eight consumer warps (8 output columns each) run the integer dot products on
-// mma.sync.m16n8k32.s8 (aq_tile_math.cuh), several tiles per loop trip so that the
-// waits, shared-memory loads and MMAs of neighbouring tiles overlap; the FP32
+// CTA's producer warp streams its range through a deep shared-memory ring with one
+// bulk asynchronous copy per weight tile; four tiles share a ring slot and one
+// full/empty mbarrier pair.  The copies of the first ring fill are issued before the
+// grid dependency is resolved, so under programmatic dependent launch they overlap the
+// tail of the preceding kernel.  Eight consumer warps (8 output columns each) run the
+// integer dot products on mma.sync.m16n8k32.s8 (aq_tile_math.cuh) a slot at a time as
+// straight-line code: activation vectors come from global memory (a few KiB, L1/L2
+// resident) and are requested before the slot's barrier is waited on; the FP32
 // accumulation still visits the tiles in increasing k.
 //
 // A CTA range may start and end in the middle of a tile row.  A row that lies entirely
@@ -36,6 +36,15 @@ namespace aq {
 
 __device__ int g_decode_status = 0;
 
+#ifdef AQ_TRACE
+// Development aid: timestamps of CTA 0 (consumer warp 0 and the producer), 4096 slots.
+__device__ long long g_trace[4096];
+#define AQ_TRACE_MARK(slot) \
+  do { if (blockIdx.x == 0 && lane == 0 && (slot) < 4096) g_trace[(slot)] = clock64(); } while (0)
+#else
+#define AQ_TRACE_MARK(slot) do { } while (0)
+#endif
+
 namespace {
 
 struct DecodeParams {
@@ -57,19 +66,24 @@ struct DecodeParams {
   int out_dtype;
 };
 
-constexpr int kStages = 16;
+constexpr int kGroupTiles = 4;  // tiles per ring slot: one full/empty barrier pair per slot
+constexpr int kSlots = 5;       // ring depth in slots (20 tiles, 80 KiB)
+constexpr int kSlotBytes = kGroupTiles * kW8TileBytes;
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
-constexpr int kXRowStride = 64;  // one K64 block of one activation row
 constexpr int kMaxRecords = 1024;
-constexpr int kNumBars = 2 * kStages;
+constexpr int kNumBars = 2 * kSlots;
 constexpr int kMaxCounterRows = 16384;  // counters occupy a fixed region so that one workspace serves any layer
 constexpr int64_t kCounterBytes = static_cast<int64_t>(kMaxCounterRows) * 4;
 
-__host__ __device__ constexpr int stage_bytes(int mt) { return kW8TileBytes + 16 * mt * kXRowStride; }
-
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+__device__ __forceinline__ uint4 ldg_x(const int8_t* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 
 // first tile of CTA i, and the CTA that owns tile t, for T tiles cut into G ranges
 __device__ __forceinline__ int64_t range_begin(int64_t i, int64_t total, int ctas) { return i * total / ctas; }
@@ -77,14 +91,17 @@ __device__ __forceinline__ int owner_of(int64_t t, int64_t total, int ctas) {
   return static_cast<int>(((t + 1) * ctas - 1) / total);
 }
 
-// Shared memory: [ring kStages x stage_bytes][tile 16*MT x 64 f32][records][barriers][flags]
+__device__ __forceinline__ uint32_t tile_bytes(const TileRecord& r) {
+  return (r.offset_flag & kW4Flag) ? kW4TileBytes : kW8TileBytes;
+}
+
+// Shared memory: [ring kSlots x kGroupTiles x 4096][tile 16*MT x 64 f32][records][barriers][flags]
 template <int MT>
-__global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, MT == 1 ? 2 : 1) decode_linear_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int kStage = stage_bytes(MT);
   constexpr int kRows = 16 * MT;
   uint8_t* ring = smem;
-  float* tile = reinterpret_cast<float*>(smem + kStages * kStage);
+  float* tile = reinterpret_cast<float*>(smem + kSlots * kSlotBytes);
   TileRecord* recs = reinterpret_cast<TileRecord*>(tile + kRows * kTile);
   uint64_t* bars = reinterpret_cast<uint64_t*>(recs + kMaxRecords);
   volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(bars + kNumBars);
@@ -96,15 +113,17 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Decode
   const int64_t t0 = range_begin(blockIdx.x, p.total_tiles, p.ctas);
   const int64_t t1 = range_begin(blockIdx.x + 1, p.total_tiles, p.ctas);
   const int count = static_cast<int>(t1 - t0);
+  const int groups = (count + kGroupTiles - 1) / kGroupTiles;
   const int rows = p.m < kRows ? static_cast<int>(p.m) : kRows;
 
   const uint32_t bar0 = smem_u32(bars);
   auto full = [&](int s) { return bar0 + 8u * s; };
-  auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto empty = [&](int s) { return bar0 + 8u * (kSlots + s); };
   const uint32_t ring_addr = smem_u32(ring);
 
+  if (warp == 0) AQ_TRACE_MARK(4000);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kSlots; ++s) {
       mbar_init(full(s), 1);
       mbar_init(empty(s), kConsumerWarps);
     }
@@ -116,45 +135,59 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Decode
 
   const TileRecord* my_records = p.records + t0;
   const bool producer = warp == kConsumerWarps;
-  const uint32_t x_bytes = static_cast<uint32_t>(rows) * kTile;
 
-  // First ring fill, weights only: they do not depend on the preceding kernel.
-  if (producer && lane < kStages && lane < count) {
-    const TileRecord r = my_records[lane];
-    const uint32_t bytes = (r.offset_flag & kW4Flag) ? kW4TileBytes : kW8TileBytes;
-    mbar_expect_tx(full(lane), bytes + x_bytes);
-    bulk_copy(ring_addr + lane * kStage,
-              p.payload + static_cast<int64_t>(r.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(lane));
+  // First ring fill: weights do not depend on the preceding kernel, so these copies are
+  // issued before the grid dependency is resolved.  Lane l fetches tile l of the range.
+  if (producer) {
+    constexpr int kFill = kSlots * kGroupTiles;
+    static_assert(kFill <= 32, "the first fill uses one lane per tile");
+    const bool active = lane < kFill && lane < count;
+    TileRecord r = {0u, 0.0f};
+    if (active) r = my_records[lane];
+    uint32_t bytes = active ? tile_bytes(r) : 0u;
+    uint32_t group_bytes = bytes;
+    group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 1);
+    group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 2);
+    if (active && (lane % kGroupTiles) == 0) mbar_expect_tx(full(lane / kGroupTiles), group_bytes);
+    __syncwarp();
+    if (active) {
+      bulk_copy(ring_addr + lane * kW8TileBytes,
+                p.payload + static_cast<int64_t>(r.offset_flag & ~kW4Flag) * kW4TileBytes, bytes,
+                full(lane / kGroupTiles));
+    }
   }
   for (int i = threadIdx.x; i < count; i += kThreads) recs[i] = my_records[i];
   grid_launch_dependents();
   grid_dependency_wait();  // activations, scales, workspace and output belong to earlier kernels
   __syncthreads();
+  if (warp == 0) AQ_TRACE_MARK(4001);
 
   if (producer) {
-    const int64_t k_bytes = static_cast<int64_t>(n_k) * kTile;
-    for (int i = 0; i < count; ++i) {
-      const int s = i % kStages;
+    // ---- refills: one slot (up to four tiles) per trip, lanes 0..3 issue the copies ----
+    for (int gi = kSlots; gi < groups; ++gi) {
+      const int slot = gi % kSlots;
       int ok = 1;
-      if (i >= kStages) {
-        if (lane == 0) {
-          ok = mbar_wait(empty(s), ((i / kStages) - 1) & 1, abort_flag, &g_decode_status, 21) ? 1 : 0;
-          if (ok) {
-            const TileRecord r = recs[i];
-            const uint32_t bytes = (r.offset_flag & kW4Flag) ? kW4TileBytes : kW8TileBytes;
-            mbar_expect_tx(full(s), bytes + x_bytes);
-            bulk_copy(ring_addr + s * kStage,
-                      p.payload + static_cast<int64_t>(r.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(s));
-          }
-        }
-        ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (lane == 0) {
+        ok = mbar_wait(empty(slot), ((gi / kSlots) - 1) & 1, abort_flag, &g_decode_status, 21) ? 1 : 0;
       }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) break;
-      const int kt = static_cast<int>((t0 + i) % n_k);
-      if (lane < rows) {
-        bulk_copy(ring_addr + s * kStage + kW8TileBytes + lane * kXRowStride,
-                  p.xq + lane * k_bytes + static_cast<int64_t>(kt) * kTile, kTile, full(s));
+      AQ_TRACE_MARK(2048 + 2 * gi);
+      const int i = gi * kGroupTiles + lane;
+      const bool active = lane < kGroupTiles && i < count;
+      TileRecord r = {0u, 0.0f};
+      if (active) r = recs[i];
+      const uint32_t bytes = active ? tile_bytes(r) : 0u;
+      uint32_t group_bytes = bytes;
+      group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 1);
+      group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 2);
+      if (lane == 0) mbar_expect_tx(full(slot), group_bytes);
+      __syncwarp();
+      if (active) {
+        bulk_copy(ring_addr + slot * kSlotBytes + lane * kW8TileBytes,
+                  p.payload + static_cast<int64_t>(r.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(slot));
       }
+      AQ_TRACE_MARK(2048 + 2 * gi + 1);
     }
     return;
   }
@@ -163,7 +196,11 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Decode
   const int g = lane >> 2;
   const int c = lane & 3;
   const int n = warp * 8 + g;
-  constexpr int kUnroll = MT == 1 ? 4 : 2;
+  const int64_t k_bytes = static_cast<int64_t>(n_k) * kTile;
+  // byte offsets of this lane's 16-byte weight vector inside a staged W8 / W4 tile
+  const uint32_t w8_off = static_cast<uint32_t>(n * 64 + ((c ^ ((n >> 1) & 3)) << 4));
+  const uint32_t w4_off = static_cast<uint32_t>(n * 32 + (c >> 1) * 16);
+  const int w4_shift = (c & 1) ? 0 : 4;
   float token_scale[MT][2];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
@@ -173,120 +210,43 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Decode
   }
   const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
 
-  int i = 0;
-  bool ok = true;
-  while (i < count && ok) {
-    const int64_t t_first = t0 + i;
-    const int j = static_cast<int>(t_first / n_k);
-    const int k_lo = static_cast<int>(t_first - static_cast<int64_t>(j) * n_k);
-    const int64_t row_end = static_cast<int64_t>(j + 1) * n_k;
-    const int seg_tiles = static_cast<int>((row_end < t1 ? row_end : t1) - t_first);
-    const bool whole_row = k_lo == 0 && seg_tiles == n_k;
-    const int seg_begin = i;
+  // running position inside the (j, k) grid
+  int j = static_cast<int>(t0 / n_k);
+  int kt = static_cast<int>(t0 - static_cast<int64_t>(j) * n_k);
+  bool first_segment = true;
+  int seg_k_lo = kt;
+  float acc[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) acc[mt][q] = 0.0f;
+  }
 
-    float acc[MT][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-      for (int q = 0; q < 4; ++q) acc[mt][q] = 0.0f;
-    }
-    const int seg_end = i + seg_tiles;
-    while (i < seg_end && ok) {
-      const int batch = seg_end - i < kUnroll ? seg_end - i : kUnroll;
-      TileRecord rec[kUnroll];
-      int d[kUnroll][MT][4];
-      // waits first, then every load, then every MMA: independent chains the scheduler can overlap
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (u < batch && ok) {
-          ok = mbar_wait(full((i + u) % kStages), ((i + u) / kStages) & 1, abort_flag, &g_decode_status, 22);
-        }
-      }
-      if (!ok) break;
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (u < batch) {
-          rec[u] = recs[i + u];
-          const uint8_t* stage = ring + ((i + u) % kStages) * kStage;
-          const uint4 w = load_weight_vector(stage, (rec[u].offset_flag & kW4Flag) != 0, n, c);
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            const int r_lo = mt * 16 + g;
-            uint4 x_lo = make_uint4(0, 0, 0, 0), x_hi = make_uint4(0, 0, 0, 0);
-            const uint8_t* xp = stage + kW8TileBytes + r_lo * kXRowStride + c * 16;
-            if (r_lo < rows) x_lo = *reinterpret_cast<const uint4*>(xp);
-            if (r_lo + 8 < rows) x_hi = *reinterpret_cast<const uint4*>(xp + 8 * kXRowStride);
-            tile_dot(d[u][mt], x_lo, x_hi, w);
-          }
-        }
-      }
-      // every lane's operands have been consumed by the warp-wide MMAs above
-      __syncwarp();
-      if (lane == 0) {
-#pragma unroll
-        for (int u = 0; u < kUnroll; ++u) {
-          if (u < batch && i + u + kStages < count) mbar_arrive(empty((i + u) % kStages));
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (u < batch) {
-          const int kt = k_lo + (i + u - seg_begin);
-          const bool is_w4 = (rec[u].offset_flag & kW4Flag) != 0;
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            float s_lo, s_hi;
-            if (p.scale_mode == AQ_SCALE_TOKEN) {
-              s_lo = __fmul_rn(token_scale[mt][0], rec[u].scale);
-              s_hi = __fmul_rn(token_scale[mt][1], rec[u].scale);
-            } else {
-              const float a_s = (mt * 16 < rows) ? p.act_scales[static_cast<int64_t>(mt) * n_k + kt] : 0.0f;
-              s_lo = s_hi = __fmul_rn(a_s, rec[u].scale);
-            }
-            tile_accumulate(acc[mt], d[u][mt], s_lo, s_hi);
-            if (p.acc_dump != nullptr) {
-              const int shift = is_w4 ? 4 : 0;
-              const int col_out = warp * 8 + 2 * c;
-              const int r_lo = mt * 16 + g;
-              if (r_lo < rows) {
-                int32_t* o = p.acc_dump + ((static_cast<int64_t>(r_lo) * p.n_j + j) * n_k + kt) * kTile + col_out;
-                o[0] = d[u][mt][0] >> shift;
-                o[1] = d[u][mt][1] >> shift;
-              }
-              if (r_lo + 8 < rows) {
-                int32_t* o = p.acc_dump + ((static_cast<int64_t>(r_lo + 8) * p.n_j + j) * n_k + kt) * kTile + col_out;
-                o[0] = d[u][mt][2] >> shift;
-                o[1] = d[u][mt][3] >> shift;
-              }
-            }
-          }
-        }
-      }
-      i += batch;
-    }
-    if (!ok) break;
-
-    // ---- finish the segment ------------------------------------------------------------
+  // Finish the segment [seg_k_lo, k_hi) of row j held in `acc`.
+  auto flush = [&](int k_hi) {
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
       const int col = warp * 8 + 2 * c;
       *reinterpret_cast<float2*>(&tile[(mt * 16 + g) * kTile + col]) = make_float2(acc[mt][0], acc[mt][1]);
       *reinterpret_cast<float2*>(&tile[(mt * 16 + g + 8) * kTile + col]) = make_float2(acc[mt][2], acc[mt][3]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) acc[mt][q] = 0.0f;
     }
     consumer_sync();
+    const bool whole_row = seg_k_lo == 0 && k_hi == n_k;
     const int32_t* meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
     const bool has_u = meta != nullptr && meta[0] != 0;
     int first_cta = blockIdx.x, last_cta = blockIdx.x;
     bool finish = whole_row;
     if (!whole_row) {
       // partial: publish to the workspace; the last arriver of the row finishes it
-      const int slot = 2 * blockIdx.x + (seg_begin == 0 ? 0 : 1);  // 0: first segment of this CTA
+      const int slot = 2 * blockIdx.x + (first_segment ? 0 : 1);
       float* dst = p.partials + static_cast<int64_t>(slot) * kRows * kTile;
       for (int e = threadIdx.x; e < rows * kTile; e += kConsumerThreads) __stcg(dst + e, tile[e]);
       __threadfence();
       consumer_sync();
       first_cta = owner_of(static_cast<int64_t>(j) * n_k, p.total_tiles, p.ctas);
-      last_cta = owner_of(row_end - 1, p.total_tiles, p.ctas);
+      last_cta = owner_of(static_cast<int64_t>(j + 1) * n_k - 1, p.total_tiles, p.ctas);
       if (threadIdx.x == 0) {
         const int arrived = atomicAdd(p.counters + j, 1);
         const bool last = arrived == last_cta - first_cta;
@@ -323,11 +283,110 @@ __global__ void __launch_bounds__(kThreads, 2) decode_linear_kernel(const Decode
       }
     }
     consumer_sync();  // the tile and the last-arriver flag are reused by the next segment
+    first_segment = false;
+  };
+
+  for (int gi = 0; gi < groups; ++gi) {
+    const int slot = gi % kSlots;
+    const int base = gi * kGroupTiles;
+    const int batch = count - base < kGroupTiles ? count - base : kGroupTiles;
+
+    // (1) activations of the batch straight from global memory (L1/L2 resident, tiny);
+    //     issued before the wait so that their latency hides behind it
+    uint4 x_lo[kGroupTiles][MT], x_hi[kGroupTiles][MT];
+    {
+      int jj = j, kk = kt;
+#pragma unroll
+      for (int u = 0; u < kGroupTiles; ++u) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          x_lo[u][mt] = make_uint4(0, 0, 0, 0);
+          x_hi[u][mt] = make_uint4(0, 0, 0, 0);
+          const int r_lo = mt * 16 + g;
+          const int8_t* xp = p.xq + r_lo * k_bytes + static_cast<int64_t>(kk) * kTile + c * 16;
+          if (u < batch && r_lo < rows) x_lo[u][mt] = ldg_x(xp);
+          if (u < batch && r_lo + 8 < rows) x_hi[u][mt] = ldg_x(xp + 8 * k_bytes);
+        }
+        if (++kk == n_k) {
+          kk = 0;
+          ++jj;
+        }
+      }
+    }
+    // (2) the slot's weights
+    if (warp == 0) AQ_TRACE_MARK(2 * gi);
+    if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_decode_status, 22)) break;
+    if (warp == 0) AQ_TRACE_MARK(2 * gi + 1);
+    // (3) records and weight vectors of the batch, branch free
+    TileRecord rec[kGroupTiles];
+    uint4 w[kGroupTiles];
+#pragma unroll
+    for (int u = 0; u < kGroupTiles; ++u) rec[u] = recs[base + (u < batch ? u : 0)];
+#pragma unroll
+    for (int u = 0; u < kGroupTiles; ++u) {
+      const bool is_w4 = (rec[u].offset_flag & kW4Flag) != 0;
+      const uint8_t* src = ring + slot * kSlotBytes + u * kW8TileBytes + (is_w4 ? w4_off : w8_off);
+      const uint4 v = *reinterpret_cast<const uint4*>(src);
+      const int shift = is_w4 ? w4_shift : 0;
+      const uint32_t mask = is_w4 ? 0xf0f0f0f0u : 0xffffffffu;
+      w[u] = make_uint4((v.x << shift) & mask, (v.y << shift) & mask, (v.z << shift) & mask, (v.w << shift) & mask);
+    }
+    // (4) integer dot products
+    int d[kGroupTiles][MT][4];
+#pragma unroll
+    for (int u = 0; u < kGroupTiles; ++u) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) tile_dot(d[u][mt], x_lo[u][mt], x_hi[u][mt], w[u]);
+    }
+    // (5) every lane's operands have been consumed by the warp-wide MMAs: release the slot
+    __syncwarp();
+    if (lane == 0 && gi + kSlots < groups) mbar_arrive(empty(slot));
+    // (6) scale and accumulate in increasing k; a row boundary finishes the segment
+#pragma unroll
+    for (int u = 0; u < kGroupTiles; ++u) {
+      if (u < batch) {
+        const bool is_w4 = (rec[u].offset_flag & kW4Flag) != 0;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          float s_lo, s_hi;
+          if (p.scale_mode == AQ_SCALE_TOKEN) {
+            s_lo = __fmul_rn(token_scale[mt][0], rec[u].scale);
+            s_hi = __fmul_rn(token_scale[mt][1], rec[u].scale);
+          } else {
+            const float a_s = (mt * 16 < rows) ? p.act_scales[static_cast<int64_t>(mt) * n_k + kt] : 0.0f;
+            s_lo = s_hi = __fmul_rn(a_s, rec[u].scale);
+          }
+          tile_accumulate(acc[mt], d[u][mt], s_lo, s_hi);
+          if (p.acc_dump != nullptr) {
+            const int shift = is_w4 ? 4 : 0;
+            const int col_out = warp * 8 + 2 * c;
+            const int r_lo = mt * 16 + g;
+            if (r_lo < rows) {
+              int32_t* o = p.acc_dump + ((static_cast<int64_t>(r_lo) * p.n_j + j) * n_k + kt) * kTile + col_out;
+              o[0] = d[u][mt][0] >> shift;
+              o[1] = d[u][mt][1] >> shift;
+            }
+            if (r_lo + 8 < rows) {
+              int32_t* o = p.acc_dump + ((static_cast<int64_t>(r_lo + 8) * p.n_j + j) * n_k + kt) * kTile + col_out;
+              o[0] = d[u][mt][2] >> shift;
+              o[1] = d[u][mt][3] >> shift;
+            }
+          }
+        }
+        if (++kt == n_k) {
+          flush(n_k);
+          kt = 0;
+          seg_k_lo = 0;
+          ++j;
+        }
+      }
+    }
   }
+  if (kt != seg_k_lo && *abort_flag == 0) flush(kt);  // the range ended inside a row
 }
 
 int smem_bytes(int mt) {
-  return kStages * stage_bytes(mt) + 16 * mt * kTile * 4 + kMaxRecords * 8 + kNumBars * 8 + 16;
+  return kSlots * kSlotBytes + 16 * mt * kTile * 4 + kMaxRecords * 8 + kNumBars * 8 + 16;
 }
 
 template <int MT>
@@ -396,6 +455,12 @@ int launch_decode_linear(const LinearArgs& a, cudaStream_t stream) {
   p.out_dtype = a.out_dtype;
   return a.m <= 16 ? launch_mt<1>(p, stream) : launch_mt<2>(p, stream);
 }
+
+#ifdef AQ_TRACE
+extern "C" __attribute__((visibility("default"))) int aq_debug_read_trace(long long* dst) {
+  return static_cast<int>(cudaMemcpyFromSymbol(dst, g_trace, sizeof(long long) * 4096));
+}
+#endif
 
 int take_decode_status() {
   int status = 0;
