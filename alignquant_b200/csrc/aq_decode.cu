@@ -14,6 +14,7 @@
 // resident) and are requested before the slot's barrier is waited on; the FP32
 // accumulation still visits the tiles in increasing k.
 //
+//
 // A CTA range may start and end in the middle of a tile row.  A row that lies entirely
 // inside one range is finished by that CTA.  Otherwise each CTA writes its partial
 // FP32 tile to a workspace slot and bumps the row's counter; the CTA that arrives last
@@ -55,7 +56,7 @@ struct DecodeParams {
   const int32_t* u_metadata;
   void* out;
   int32_t* acc_dump;
-  float* partials;    // [2 * ctas][16 * MT][64]
+  float* partials;    // [2 * ctas][8 * NT][64]
   int32_t* counters;  // [n_j], zero between launches
   int64_t m;
   int64_t total_tiles;
@@ -66,10 +67,10 @@ struct DecodeParams {
   int out_dtype;
 };
 
-constexpr int kGroupTiles = 4;  // tiles per ring slot: one full/empty barrier pair per slot
-constexpr int kSlots = 5;       // ring depth in slots (20 tiles, 80 KiB)
+constexpr int kGroupTiles = 8;  // tiles per ring slot: one full/empty barrier pair per slot
+constexpr int kSlots = 3;       // ring depth in slots (24 tiles, 96 KiB)
 constexpr int kSlotBytes = kGroupTiles * kW8TileBytes;
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = 4;  // 16 output columns each
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kMaxRecords = 1024;
@@ -77,7 +78,7 @@ constexpr int kNumBars = 2 * kSlots;
 constexpr int kMaxCounterRows = 16384;  // counters occupy a fixed region so that one workspace serves any layer
 constexpr int64_t kCounterBytes = static_cast<int64_t>(kMaxCounterRows) * 4;
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ uint4 ldg_x(const int8_t* p) {
   uint4 v;
@@ -95,11 +96,32 @@ __device__ __forceinline__ uint32_t tile_bytes(const TileRecord& r) {
   return (r.offset_flag & kW4Flag) ? kW4TileBytes : kW8TileBytes;
 }
 
-// Shared memory: [ring kSlots x kGroupTiles x 4096][tile 16*MT x 64 f32][records][barriers][flags]
-template <int MT>
-__global__ void __launch_bounds__(kThreads, MT == 1 ? 2 : 1) decode_linear_kernel(const DecodeParams p) {
+// 16-byte weight vector of output column n, k in [16c, 16c+16), from a staged tile
+// (layouts in aq_tile_math.cuh); W4 nibbles are widened to bytes holding 16*w.
+__device__ __forceinline__ uint4 weight_vector(const uint8_t* tile, bool is_w4, uint32_t w8_off, uint32_t w4_off,
+                                               int w4_shift) {
+  uint4 v = *reinterpret_cast<const uint4*>(tile + (is_w4 ? w4_off : w8_off));
+  if (is_w4) {
+    v.x = (v.x << w4_shift) & 0xf0f0f0f0u;
+    v.y = (v.y << w4_shift) & 0xf0f0f0f0u;
+    v.z = (v.z << w4_shift) & 0xf0f0f0f0u;
+    v.w = (v.w << w4_shift) & 0xf0f0f0f0u;
+  }
+  return v;
+}
+
+// In this kernel the weights are the 16-row MMA operand (16 output columns per warp and
+// MMA) and up to eight activation rows ("tokens") are the 8-column operand, so one pair
+// of MMAs covers 16 columns x 8 tokens of a K64 tile.  Lane (g, c) = (lane/4, lane%4)
+// holds the weight vectors of columns 16w+g and 16w+g+8 and the activation vector of
+// token 8*pass+g, all for k in [16c, 16c+16).  Results: d[0], d[1] = column 16w+g,
+// tokens 8*pass+2c, +1; d[2], d[3] = column 16w+g+8, same tokens.
+//
+// Shared memory: [ring kSlots x kGroupTiles x 4096][tile 8*NT x 64 f32][records][barriers][flags]
+template <int NT>
+__global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) decode_linear_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int kRows = 16 * MT;
+  constexpr int kRows = 8 * NT;
   uint8_t* ring = smem;
   float* tile = reinterpret_cast<float*>(smem + kSlots * kSlotBytes);
   TileRecord* recs = reinterpret_cast<TileRecord*>(tile + kRows * kTile);
@@ -140,14 +162,15 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 2 : 1) decode_linear_kerne
   // issued before the grid dependency is resolved.  Lane l fetches tile l of the range.
   if (producer) {
     constexpr int kFill = kSlots * kGroupTiles;
-    static_assert(kFill <= 32, "the first fill uses one lane per tile");
+    static_assert(kFill <= 32 && kGroupTiles == 8, "the first fill uses one lane per tile");
     const bool active = lane < kFill && lane < count;
     TileRecord r = {0u, 0.0f};
     if (active) r = my_records[lane];
-    uint32_t bytes = active ? tile_bytes(r) : 0u;
+    const uint32_t bytes = active ? tile_bytes(r) : 0u;
     uint32_t group_bytes = bytes;
     group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 1);
     group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 2);
+    group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 4);
     if (active && (lane % kGroupTiles) == 0) mbar_expect_tx(full(lane / kGroupTiles), group_bytes);
     __syncwarp();
     if (active) {
@@ -163,7 +186,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 2 : 1) decode_linear_kerne
   if (warp == 0) AQ_TRACE_MARK(4001);
 
   if (producer) {
-    // ---- refills: one slot (up to four tiles) per trip, lanes 0..3 issue the copies ----
+    // ---- refills: one slot (up to eight tiles) per trip, lanes 0..7 issue the copies ----
     for (int gi = kSlots; gi < groups; ++gi) {
       const int slot = gi % kSlots;
       int ok = 1;
@@ -181,6 +204,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 2 : 1) decode_linear_kerne
       uint32_t group_bytes = bytes;
       group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 1);
       group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 2);
+      group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 4);
       if (lane == 0) mbar_expect_tx(full(slot), group_bytes);
       __syncwarp();
       if (active) {
@@ -192,45 +216,51 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 2 : 1) decode_linear_kerne
     return;
   }
 
-  // ---- consumers: warp w owns output columns 8w .. 8w+7 --------------------------------
+  // ---- consumers: warp w owns output columns 16w .. 16w+15 -----------------------------
   const int g = lane >> 2;
   const int c = lane & 3;
-  const int n = warp * 8 + g;
+  const int n_a = warp * 16 + g;  // second column of this lane is n_a + 8
   const int64_t k_bytes = static_cast<int64_t>(n_k) * kTile;
-  // byte offsets of this lane's 16-byte weight vector inside a staged W8 / W4 tile
-  const uint32_t w8_off = static_cast<uint32_t>(n * 64 + ((c ^ ((n >> 1) & 3)) << 4));
-  const uint32_t w4_off = static_cast<uint32_t>(n * 32 + (c >> 1) * 16);
+  // byte offsets of this lane's 16-byte weight vectors inside a staged W8 / W4 tile
+  const uint32_t w8_off = static_cast<uint32_t>(n_a * 64 + ((c ^ ((n_a >> 1) & 3)) << 4));
+  const uint32_t w4_off = static_cast<uint32_t>(n_a * 32 + (c >> 1) * 16);
   const int w4_shift = (c & 1) ? 0 : 4;
-  float token_scale[MT][2];
+  // per-token activation scale of the two tokens this lane's results belong to
+  float token_scale[NT][2];
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
-    const int r_lo = mt * 16 + g;
-    token_scale[mt][0] = (p.scale_mode == AQ_SCALE_TOKEN && r_lo < rows) ? p.act_scales[r_lo] : 0.0f;
-    token_scale[mt][1] = (p.scale_mode == AQ_SCALE_TOKEN && r_lo + 8 < rows) ? p.act_scales[r_lo + 8] : 0.0f;
+  for (int nt = 0; nt < NT; ++nt) {
+    const int tok = nt * 8 + 2 * c;
+    token_scale[nt][0] = (p.scale_mode == AQ_SCALE_TOKEN && tok < rows) ? p.act_scales[tok] : 0.0f;
+    token_scale[nt][1] = (p.scale_mode == AQ_SCALE_TOKEN && tok + 1 < rows) ? p.act_scales[tok + 1] : 0.0f;
   }
   const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
+  const int8_t* x_lane[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) x_lane[nt] = p.xq + static_cast<int64_t>(nt * 8 + g) * k_bytes + c * 16;
 
   // running position inside the (j, k) grid
   int j = static_cast<int>(t0 / n_k);
   int kt = static_cast<int>(t0 - static_cast<int64_t>(j) * n_k);
   bool first_segment = true;
   int seg_k_lo = kt;
-  float acc[MT][4];
+  float acc[NT][4];
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
+  for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) acc[mt][q] = 0.0f;
+    for (int q = 0; q < 4; ++q) acc[nt][q] = 0.0f;
   }
 
   // Finish the segment [seg_k_lo, k_hi) of row j held in `acc`.
   auto flush = [&](int k_hi) {
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      const int col = warp * 8 + 2 * c;
-      *reinterpret_cast<float2*>(&tile[(mt * 16 + g) * kTile + col]) = make_float2(acc[mt][0], acc[mt][1]);
-      *reinterpret_cast<float2*>(&tile[(mt * 16 + g + 8) * kTile + col]) = make_float2(acc[mt][2], acc[mt][3]);
+    for (int nt = 0; nt < NT; ++nt) {
+      const int tok = nt * 8 + 2 * c;
+      tile[tok * kTile + n_a] = acc[nt][0];
+      tile[(tok + 1) * kTile + n_a] = acc[nt][1];
+      tile[tok * kTile + n_a + 8] = acc[nt][2];
+      tile[(tok + 1) * kTile + n_a + 8] = acc[nt][3];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) acc[mt][q] = 0.0f;
+      for (int q = 0; q < 4; ++q) acc[nt][q] = 0.0f;
     }
     consumer_sync();
     const bool whole_row = seg_k_lo == 0 && k_hi == n_k;
@@ -291,52 +321,42 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 2 : 1) decode_linear_kerne
     const int base = gi * kGroupTiles;
     const int batch = count - base < kGroupTiles ? count - base : kGroupTiles;
 
-    // (1) activations of the batch straight from global memory (L1/L2 resident, tiny);
-    //     issued before the wait so that their latency hides behind it
-    uint4 x_lo[kGroupTiles][MT], x_hi[kGroupTiles][MT];
+    // (1) activations of the batch straight from global memory (a few KiB, L1/L2
+    //     resident); requested before the wait so that their latency hides behind it
+    uint4 x[kGroupTiles][NT];
     {
-      int jj = j, kk = kt;
+      int kk = kt;
 #pragma unroll
       for (int u = 0; u < kGroupTiles; ++u) {
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          x_lo[u][mt] = make_uint4(0, 0, 0, 0);
-          x_hi[u][mt] = make_uint4(0, 0, 0, 0);
-          const int r_lo = mt * 16 + g;
-          const int8_t* xp = p.xq + r_lo * k_bytes + static_cast<int64_t>(kk) * kTile + c * 16;
-          if (u < batch && r_lo < rows) x_lo[u][mt] = ldg_x(xp);
-          if (u < batch && r_lo + 8 < rows) x_hi[u][mt] = ldg_x(xp + 8 * k_bytes);
+        for (int nt = 0; nt < NT; ++nt) {
+          x[u][nt] = make_uint4(0, 0, 0, 0);
+          if (u < batch && nt * 8 + g < rows) x[u][nt] = ldg_x(x_lane[nt] + static_cast<int64_t>(kk) * kTile);
         }
-        if (++kk == n_k) {
-          kk = 0;
-          ++jj;
-        }
+        if (++kk == n_k) kk = 0;
       }
     }
     // (2) the slot's weights
     if (warp == 0) AQ_TRACE_MARK(2 * gi);
     if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_decode_status, 22)) break;
     if (warp == 0) AQ_TRACE_MARK(2 * gi + 1);
-    // (3) records and weight vectors of the batch, branch free
+    // (3) + (4) records, weight vectors and integer dot products of the batch
     TileRecord rec[kGroupTiles];
-    uint4 w[kGroupTiles];
 #pragma unroll
     for (int u = 0; u < kGroupTiles; ++u) rec[u] = recs[base + (u < batch ? u : 0)];
+    int d[kGroupTiles][NT][4];
 #pragma unroll
     for (int u = 0; u < kGroupTiles; ++u) {
       const bool is_w4 = (rec[u].offset_flag & kW4Flag) != 0;
-      const uint8_t* src = ring + slot * kSlotBytes + u * kW8TileBytes + (is_w4 ? w4_off : w8_off);
-      const uint4 v = *reinterpret_cast<const uint4*>(src);
-      const int shift = is_w4 ? w4_shift : 0;
-      const uint32_t mask = is_w4 ? 0xf0f0f0f0u : 0xffffffffu;
-      w[u] = make_uint4((v.x << shift) & mask, (v.y << shift) & mask, (v.z << shift) & mask, (v.w << shift) & mask);
-    }
-    // (4) integer dot products
-    int d[kGroupTiles][MT][4];
+      const uint8_t* staged = ring + slot * kSlotBytes + u * kW8TileBytes;
+      const uint4 wa = weight_vector(staged, is_w4, w8_off, w4_off, w4_shift);
+      const uint4 wb = weight_vector(staged + (is_w4 ? 8 * 32 : 8 * 64), is_w4, w8_off, w4_off, w4_shift);
 #pragma unroll
-    for (int u = 0; u < kGroupTiles; ++u) {
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) tile_dot(d[u][mt], x_lo[u][mt], x_hi[u][mt], w[u]);
+      for (int nt = 0; nt < NT; ++nt) {
+        d[u][nt][0] = d[u][nt][1] = d[u][nt][2] = d[u][nt][3] = 0;
+        mma_s8(d[u][nt], wa.x, wb.x, wa.y, wb.y, x[u][nt].x, x[u][nt].y);
+        mma_s8(d[u][nt], wa.z, wb.z, wa.w, wb.w, x[u][nt].z, x[u][nt].w);
+      }
     }
     // (5) every lane's operands have been consumed by the warp-wide MMAs: release the slot
     __syncwarp();
@@ -347,29 +367,30 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 2 : 1) decode_linear_kerne
       if (u < batch) {
         const bool is_w4 = (rec[u].offset_flag & kW4Flag) != 0;
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          float s_lo, s_hi;
+        for (int nt = 0; nt < NT; ++nt) {
+          float s0, s1;
           if (p.scale_mode == AQ_SCALE_TOKEN) {
-            s_lo = __fmul_rn(token_scale[mt][0], rec[u].scale);
-            s_hi = __fmul_rn(token_scale[mt][1], rec[u].scale);
+            s0 = __fmul_rn(token_scale[nt][0], rec[u].scale);
+            s1 = __fmul_rn(token_scale[nt][1], rec[u].scale);
           } else {
-            const float a_s = (mt * 16 < rows) ? p.act_scales[static_cast<int64_t>(mt) * n_k + kt] : 0.0f;
-            s_lo = s_hi = __fmul_rn(a_s, rec[u].scale);
+            // tokens 8*nt .. 8*nt+7 share the scale of their 16-row group
+            const float a_s = (nt * 8 < rows) ? p.act_scales[static_cast<int64_t>(nt >> 1) * n_k + kt] : 0.0f;
+            s0 = s1 = __fmul_rn(a_s, rec[u].scale);
           }
-          tile_accumulate(acc[mt], d[u][mt], s_lo, s_hi);
+          acc[nt][0] = __fadd_rn(acc[nt][0], __fmul_rn(static_cast<float>(d[u][nt][0]), s0));
+          acc[nt][1] = __fadd_rn(acc[nt][1], __fmul_rn(static_cast<float>(d[u][nt][1]), s1));
+          acc[nt][2] = __fadd_rn(acc[nt][2], __fmul_rn(static_cast<float>(d[u][nt][2]), s0));
+          acc[nt][3] = __fadd_rn(acc[nt][3], __fmul_rn(static_cast<float>(d[u][nt][3]), s1));
           if (p.acc_dump != nullptr) {
             const int shift = is_w4 ? 4 : 0;
-            const int col_out = warp * 8 + 2 * c;
-            const int r_lo = mt * 16 + g;
-            if (r_lo < rows) {
-              int32_t* o = p.acc_dump + ((static_cast<int64_t>(r_lo) * p.n_j + j) * n_k + kt) * kTile + col_out;
-              o[0] = d[u][mt][0] >> shift;
-              o[1] = d[u][mt][1] >> shift;
-            }
-            if (r_lo + 8 < rows) {
-              int32_t* o = p.acc_dump + ((static_cast<int64_t>(r_lo + 8) * p.n_j + j) * n_k + kt) * kTile + col_out;
-              o[0] = d[u][mt][2] >> shift;
-              o[1] = d[u][mt][3] >> shift;
+            const int tok = nt * 8 + 2 * c;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int t = tok + (q & 1);
+              const int col = n_a + ((q & 2) ? 8 : 0);
+              if (t < rows) {
+                p.acc_dump[((static_cast<int64_t>(t) * p.n_j + j) * n_k + kt) * kTile + col] = d[u][nt][q] >> shift;
+              }
             }
           }
         }
@@ -386,7 +407,7 @@ __global__ void __launch_bounds__(kThreads, MT == 1 ? 2 : 1) decode_linear_kerne
 }
 
 int smem_bytes(int mt) {
-  return kSlots * kSlotBytes + 16 * mt * kTile * 4 + kMaxRecords * 8 + kNumBars * 8 + 16;
+  return kSlots * kSlotBytes + 8 * mt * kTile * 4 + kMaxRecords * 8 + kNumBars * 8 + 16;
 }
 
 template <int MT>
@@ -415,7 +436,7 @@ int launch_mt(const DecodeParams& p, cudaStream_t stream) {
   return check_cuda(cudaLaunchKernelEx(&config, decode_linear_kernel<MT>, p), "decode linear launch");
 }
 
-int64_t partial_bytes(int ctas, int mt) { return 2LL * ctas * 16 * mt * kTile * 4; }
+int64_t partial_bytes(int ctas, int nt) { return 2LL * ctas * 8 * nt * kTile * 4; }
 
 }  // namespace
 
@@ -428,8 +449,8 @@ int decode_ctas(int n_j, int n_k) {
 }
 
 int64_t decode_workspace_bytes(int64_t m, int n_j, int n_k) {
-  const int mt = m <= 16 ? 1 : 2;
-  return kCounterBytes + partial_bytes(decode_ctas(n_j, n_k), mt);
+  const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
+  return kCounterBytes + partial_bytes(decode_ctas(n_j, n_k), nt);
 }
 
 int launch_decode_linear(const LinearArgs& a, cudaStream_t stream) {
@@ -453,7 +474,7 @@ int launch_decode_linear(const LinearArgs& a, cudaStream_t stream) {
   p.ctas = decode_ctas(a.n_j, a.n_k);
   p.scale_mode = a.scale_mode;
   p.out_dtype = a.out_dtype;
-  return a.m <= 16 ? launch_mt<1>(p, stream) : launch_mt<2>(p, stream);
+  return a.m <= 8 ? launch_mt<1>(p, stream) : (a.m <= 16 ? launch_mt<2>(p, stream) : launch_mt<4>(p, stream));
 }
 
 #ifdef AQ_TRACE
