@@ -58,7 +58,7 @@ bool use_dependent_launch() {
 namespace {
 
 constexpr int64_t kStreamMaxRows = 128;  // above this the automatic schedule uses the GEMM
-constexpr int64_t kDecodeMaxRows = 32;   // the persistent decode kernel handles up to this many rows
+constexpr int64_t kDecodeMaxRows = 16;   // the persistent decode kernel handles up to this many rows
 
 bool valid_split(int s) { return s == 0 || s == 1 || s == 2 || s == 4 || s == 8 || s == 16; }
 

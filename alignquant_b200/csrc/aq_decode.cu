@@ -1,32 +1,34 @@
-// Persistent decode kernel: packed W4/W8 x A8 GEMV/GEMM for at most 32 rows.
+// Persistent decode kernel: packed W4/W8 x A8 GEMV/GEMM for at most 16 rows.
 //
 // At decode sizes a whole layer is a few microseconds of HBM traffic, so the kernel
 // is built to keep one uninterrupted byte stream per SM.  The layer's tiles are
 // stored in (j, k) order in the prepared image; that 1-D sequence of T tiles is cut
-// into G equal contiguous ranges, one per CTA, one CTA per SM ("stream-K").  Each
-// CTA's producer warp streams its range through a deep shared-memory ring with one
-// bulk asynchronous copy per weight tile; four tiles share a ring slot and one
-// full/empty mbarrier pair.  The copies of the first ring fill are issued before the
-// grid dependency is resolved, so under programmatic dependent launch they overlap the
-// tail of the preceding kernel.  Eight consumer warps (8 output columns each) run the
-// integer dot products on mma.sync.m16n8k32.s8 (aq_tile_math.cuh) a slot at a time as
-// straight-line code: activation vectors come from global memory (a few KiB, L1/L2
-// resident) and are requested before the slot's barrier is waited on; the FP32
-// accumulation still visits the tiles in increasing k.
+// into G equal contiguous ranges, one per CTA, one CTA per SM ("stream-K").  A range
+// is contiguous in memory, so the producer warp streams it through a shared-memory
+// ring with ONE bulk asynchronous copy per slot of eight tiles (up to 32 KiB, counted
+// on the slot's mbarrier).  The first ring fill is issued before the grid dependency
+// is resolved, so under programmatic dependent launch it overlaps the preceding kernel.
 //
+// Sixteen consumer warps each take whole tiles (tile i of the range goes to warp
+// i % 16), so sixteen tiles are in progress at once and every warp's waits, loads and
+// MMAs overlap with the others'.  Inside a warp the weights are the 16-row MMA operand
+// (mma.sync.m16n8k32.s8: 16 output columns) and up to eight activation rows
+// ("tokens") the 8-column operand; activation vectors come straight from global
+// memory (a few KiB, L1/L2 resident) and are requested one tile ahead.
+//
+// Summation order (all FP32, separately rounded multiply and add as in
+// alignquant/kernels/cuda/linear.cu:956-963): a warp adds its tiles of a row segment
+// in increasing k; the sixteen warp sums are added in warp order; the partial sums of
+// the ranges that share a tile row are added in range order (the analogue of the
+// reference's split-K reducer, linear.cu:1339-1343).  The order is fixed by the
+// problem shape and the SM count, never by timing.
 //
 // A CTA range may start and end in the middle of a tile row.  A row that lies entirely
 // inside one range is finished by that CTA.  Otherwise each CTA writes its partial
 // FP32 tile to a workspace slot and bumps the row's counter; the CTA that arrives last
-// sums the slots in increasing-k order (so the result does not depend on arrival
-// order), applies the inverse output transform and stores the row.  Counters return to
-// zero, so the workspace only has to be zeroed once by its owner.  Nothing spins on
-// another CTA.
-//
-// Arithmetic contract: per K64 tile, float(int32 dot) * (activation scale * tile
-// scale), separately rounded multiply and add in increasing k inside a range
-// (alignquant/kernels/cuda/linear.cu:956-963, 1296-1301); range partials are added in
-// range order like the reference's split-K reducer (linear.cu:1339-1343).
+// sums the slots, applies the inverse output transform and stores the row.  Counters
+// return to zero, so the workspace only has to be zeroed once by its owner.  Nothing
+// spins on another CTA; every mbarrier wait is bounded (aq_ptx.cuh).
 #include <mutex>
 
 #include "aq_common.cuh"
@@ -67,10 +69,10 @@ struct DecodeParams {
   int out_dtype;
 };
 
-constexpr int kGroupTiles = 8;  // tiles per ring slot: one full/empty barrier pair per slot
-constexpr int kSlots = 3;       // ring depth in slots (24 tiles, 96 KiB)
+constexpr int kGroupTiles = 8;  // tiles per ring slot: one copy and one full/empty barrier pair per slot
+constexpr int kSlots = 4;       // ring depth in slots (32 tiles, 128 KiB)
 constexpr int kSlotBytes = kGroupTiles * kW8TileBytes;
-constexpr int kConsumerWarps = 4;  // 16 output columns each
+constexpr int kConsumerWarps = 16;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 32;
 constexpr int kMaxRecords = 1024;
@@ -78,7 +80,7 @@ constexpr int kNumBars = 2 * kSlots;
 constexpr int kMaxCounterRows = 16384;  // counters occupy a fixed region so that one workspace serves any layer
 constexpr int64_t kCounterBytes = static_cast<int64_t>(kMaxCounterRows) * 4;
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
 __device__ __forceinline__ uint4 ldg_x(const int8_t* p) {
   uint4 v;
@@ -92,8 +94,11 @@ __device__ __forceinline__ int owner_of(int64_t t, int64_t total, int ctas) {
   return static_cast<int>(((t + 1) * ctas - 1) / total);
 }
 
-__device__ __forceinline__ uint32_t tile_bytes(const TileRecord& r) {
-  return (r.offset_flag & kW4Flag) ? kW4TileBytes : kW8TileBytes;
+// payload bytes of tiles [first, last] given their records (tiles are contiguous)
+__device__ __forceinline__ uint32_t span_bytes(const TileRecord& first, const TileRecord& last) {
+  const uint32_t units = (last.offset_flag & ~kW4Flag) + ((last.offset_flag & kW4Flag) ? 1u : 2u) -
+                         (first.offset_flag & ~kW4Flag);
+  return units * kW4TileBytes;
 }
 
 // 16-byte weight vector of output column n, k in [16c, 16c+16), from a staged tile
@@ -110,20 +115,20 @@ __device__ __forceinline__ uint4 weight_vector(const uint8_t* tile, bool is_w4, 
   return v;
 }
 
-// In this kernel the weights are the 16-row MMA operand (16 output columns per warp and
-// MMA) and up to eight activation rows ("tokens") are the 8-column operand, so one pair
-// of MMAs covers 16 columns x 8 tokens of a K64 tile.  Lane (g, c) = (lane/4, lane%4)
-// holds the weight vectors of columns 16w+g and 16w+g+8 and the activation vector of
-// token 8*pass+g, all for k in [16c, 16c+16).  Results: d[0], d[1] = column 16w+g,
-// tokens 8*pass+2c, +1; d[2], d[3] = column 16w+g+8, same tokens.
+// Lane (g, c) = (lane/4, lane%4) of a consumer warp holds, for column group q = 0..3,
+// the weight vectors of columns 16q+g and 16q+g+8 and the activation vector of token
+// 8*pass+g, all for k in [16c, 16c+16).  MMA results: d[0], d[1] = column 16q+g, tokens
+// 8*pass+2c, +1; d[2], d[3] = column 16q+g+8, same tokens.
 //
-// Shared memory: [ring kSlots x kGroupTiles x 4096][tile 8*NT x 64 f32][records][barriers][flags]
+// Shared memory: [ring kSlots x 32 KiB][slabs 16 x (8*NT) x 64 f32][tile (8*NT) x 64 f32]
+//                [records][barriers][flags]
 template <int NT>
-__global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) decode_linear_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const DecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kRows = 8 * NT;
   uint8_t* ring = smem;
-  float* tile = reinterpret_cast<float*>(smem + kSlots * kSlotBytes);
+  float* slabs = reinterpret_cast<float*>(smem + kSlots * kSlotBytes);
+  float* tile = slabs + kConsumerWarps * kRows * kTile;
   TileRecord* recs = reinterpret_cast<TileRecord*>(tile + kRows * kTile);
   uint64_t* bars = reinterpret_cast<uint64_t*>(recs + kMaxRecords);
   volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(bars + kNumBars);
@@ -147,7 +152,7 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) decode_linear_kerne
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(full(s), 1);
-      mbar_init(empty(s), kConsumerWarps);
+      mbar_init(empty(s), kGroupTiles);
     }
     *abort_flag = 0;
     mbar_init_fence();
@@ -159,25 +164,16 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) decode_linear_kerne
   const bool producer = warp == kConsumerWarps;
 
   // First ring fill: weights do not depend on the preceding kernel, so these copies are
-  // issued before the grid dependency is resolved.  Lane l fetches tile l of the range.
-  if (producer) {
-    constexpr int kFill = kSlots * kGroupTiles;
-    static_assert(kFill <= 32 && kGroupTiles == 8, "the first fill uses one lane per tile");
-    const bool active = lane < kFill && lane < count;
-    TileRecord r = {0u, 0.0f};
-    if (active) r = my_records[lane];
-    const uint32_t bytes = active ? tile_bytes(r) : 0u;
-    uint32_t group_bytes = bytes;
-    group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 1);
-    group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 2);
-    group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 4);
-    if (active && (lane % kGroupTiles) == 0) mbar_expect_tx(full(lane / kGroupTiles), group_bytes);
-    __syncwarp();
-    if (active) {
-      bulk_copy(ring_addr + lane * kW8TileBytes,
-                p.payload + static_cast<int64_t>(r.offset_flag & ~kW4Flag) * kW4TileBytes, bytes,
-                full(lane / kGroupTiles));
-    }
+  // issued before the grid dependency is resolved.  Lane l fetches slot l.
+  if (producer && lane < kSlots && lane < groups) {
+    const int first = lane * kGroupTiles;
+    const int last = (first + kGroupTiles < count ? first + kGroupTiles : count) - 1;
+    const TileRecord rf = my_records[first];
+    const TileRecord rl = my_records[last];
+    const uint32_t bytes = span_bytes(rf, rl);
+    mbar_expect_tx(full(lane), bytes);
+    bulk_copy(ring_addr + lane * kSlotBytes,
+              p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(lane));
   }
   for (int i = threadIdx.x; i < count; i += kThreads) recs[i] = my_records[i];
   grid_launch_dependents();
@@ -186,46 +182,33 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) decode_linear_kerne
   if (warp == 0) AQ_TRACE_MARK(4001);
 
   if (producer) {
-    // ---- refills: one slot (up to eight tiles) per trip, lanes 0..7 issue the copies ----
-    for (int gi = kSlots; gi < groups; ++gi) {
-      const int slot = gi % kSlots;
-      int ok = 1;
-      if (lane == 0) {
-        ok = mbar_wait(empty(slot), ((gi / kSlots) - 1) & 1, abort_flag, &g_decode_status, 21) ? 1 : 0;
+    // ---- refills: one copy per slot -----------------------------------------------------
+    if (lane == 0) {
+      for (int gi = kSlots; gi < groups; ++gi) {
+        const int slot = gi % kSlots;
+        if (!mbar_wait(empty(slot), ((gi / kSlots) - 1) & 1, abort_flag, &g_decode_status, 21)) break;
+        AQ_TRACE_MARK(2048 + 2 * gi);
+        const int first = gi * kGroupTiles;
+        const int last = (first + kGroupTiles < count ? first + kGroupTiles : count) - 1;
+        const TileRecord rf = recs[first];
+        const uint32_t bytes = span_bytes(rf, recs[last]);
+        mbar_expect_tx(full(slot), bytes);
+        bulk_copy(ring_addr + slot * kSlotBytes,
+                  p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(slot));
+        AQ_TRACE_MARK(2048 + 2 * gi + 1);
       }
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) break;
-      AQ_TRACE_MARK(2048 + 2 * gi);
-      const int i = gi * kGroupTiles + lane;
-      const bool active = lane < kGroupTiles && i < count;
-      TileRecord r = {0u, 0.0f};
-      if (active) r = recs[i];
-      const uint32_t bytes = active ? tile_bytes(r) : 0u;
-      uint32_t group_bytes = bytes;
-      group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 1);
-      group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 2);
-      group_bytes += __shfl_xor_sync(0xffffffffu, group_bytes, 4);
-      if (lane == 0) mbar_expect_tx(full(slot), group_bytes);
-      __syncwarp();
-      if (active) {
-        bulk_copy(ring_addr + slot * kSlotBytes + lane * kW8TileBytes,
-                  p.payload + static_cast<int64_t>(r.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(slot));
-      }
-      AQ_TRACE_MARK(2048 + 2 * gi + 1);
     }
     return;
   }
 
-  // ---- consumers: warp w owns output columns 16w .. 16w+15 -----------------------------
+  // ---- consumers ------------------------------------------------------------------------
   const int g = lane >> 2;
   const int c = lane & 3;
-  const int n_a = warp * 16 + g;  // second column of this lane is n_a + 8
   const int64_t k_bytes = static_cast<int64_t>(n_k) * kTile;
-  // byte offsets of this lane's 16-byte weight vectors inside a staged W8 / W4 tile
-  const uint32_t w8_off = static_cast<uint32_t>(n_a * 64 + ((c ^ ((n_a >> 1) & 3)) << 4));
-  const uint32_t w4_off = static_cast<uint32_t>(n_a * 32 + (c >> 1) * 16);
+  // byte offsets of this lane's weight vector for column g of a 16-column group
+  const uint32_t w8_off = static_cast<uint32_t>(g * 64 + ((c ^ ((g >> 1) & 3)) << 4));
+  const uint32_t w4_off = static_cast<uint32_t>(g * 32 + (c >> 1) * 16);
   const int w4_shift = (c & 1) ? 0 : 4;
-  // per-token activation scale of the two tokens this lane's results belong to
   float token_scale[NT][2];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
@@ -238,32 +221,138 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) decode_linear_kerne
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) x_lane[nt] = p.xq + static_cast<int64_t>(nt * 8 + g) * k_bytes + c * 16;
 
-  // running position inside the (j, k) grid
-  int j = static_cast<int>(t0 / n_k);
-  int kt = static_cast<int>(t0 - static_cast<int64_t>(j) * n_k);
-  bool first_segment = true;
-  int seg_k_lo = kt;
-  float acc[NT][4];
+  auto load_x = [&](int i, uint4 (&x)[NT]) {
+    const int kt = static_cast<int>((t0 + i) % n_k);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      x[nt] = make_uint4(0, 0, 0, 0);
+      if (nt * 8 + g < rows) x[nt] = ldg_x(x_lane[nt] + static_cast<int64_t>(kt) * kTile);
+    }
+  };
+
+  float acc[NT][4][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) acc[nt][q] = 0.0f;
+    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[nt][q][e] = 0.0f;
+    }
   }
 
-  // Finish the segment [seg_k_lo, k_hi) of row j held in `acc`.
-  auto flush = [&](int k_hi) {
+  bool ok = true;
+  bool first_segment = true;
+  int pos = 0;  // first tile (index inside the range) of the current row segment
+  // this warp's next tile and its activation vectors, requested one tile ahead
+  int mine = warp;
+  uint4 x_next[NT];
+  if (mine < count) load_x(mine, x_next);
+
+  while (pos < count && ok) {
+    const int64_t t_first = t0 + pos;
+    const int j = static_cast<int>(t_first / n_k);
+    const int k_lo = static_cast<int>(t_first - static_cast<int64_t>(j) * n_k);
+    const int64_t row_end = static_cast<int64_t>(j + 1) * n_k;
+    const int seg_tiles = static_cast<int>((row_end < t1 ? row_end : t1) - t_first);
+    const int seg_end = pos + seg_tiles;
+    const bool whole_row = k_lo == 0 && seg_tiles == n_k;
+
+    for (; mine < seg_end; mine += kConsumerWarps) {
+      const int i = mine;
+      const int gi = i / kGroupTiles;
+      const int slot = gi % kSlots;
+      const int kt = k_lo + (i - pos);
+      uint4 x[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int tok = nt * 8 + 2 * c;
-      tile[tok * kTile + n_a] = acc[nt][0];
-      tile[(tok + 1) * kTile + n_a] = acc[nt][1];
-      tile[tok * kTile + n_a + 8] = acc[nt][2];
-      tile[(tok + 1) * kTile + n_a + 8] = acc[nt][3];
+      for (int nt = 0; nt < NT; ++nt) x[nt] = x_next[nt];
+      if (i + kConsumerWarps < count) load_x(i + kConsumerWarps, x_next);
+      if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_decode_status, 22)) {
+        ok = false;
+        break;
+      }
+      const TileRecord rec = recs[i];
+      const TileRecord rec0 = recs[gi * kGroupTiles];
+      const bool is_w4 = (rec.offset_flag & kW4Flag) != 0;
+      const uint8_t* staged = ring + slot * kSlotBytes +
+                              ((rec.offset_flag & ~kW4Flag) - (rec0.offset_flag & ~kW4Flag)) * kW4TileBytes;
+      int d[NT][4][4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) acc[nt][q] = 0.0f;
+      for (int q = 0; q < 4; ++q) {
+        const uint8_t* group = staged + q * (is_w4 ? 16 * 32 : 16 * 64);
+        const uint4 wa = weight_vector(group, is_w4, w8_off, w4_off, w4_shift);
+        const uint4 wb = weight_vector(group + (is_w4 ? 8 * 32 : 8 * 64), is_w4, w8_off, w4_off, w4_shift);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          d[nt][q][0] = d[nt][q][1] = d[nt][q][2] = d[nt][q][3] = 0;
+          mma_s8(d[nt][q], wa.x, wb.x, wa.y, wb.y, x[nt].x, x[nt].y);
+          mma_s8(d[nt][q], wa.z, wb.z, wa.w, wb.w, x[nt].z, x[nt].w);
+        }
+      }
+      // every lane's operands have been consumed by the warp-wide MMAs: this tile is done
+      __syncwarp();
+      if (lane == 0 && gi + kSlots < groups) mbar_arrive(empty(slot));
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float s0, s1;
+        if (p.scale_mode == AQ_SCALE_TOKEN) {
+          s0 = __fmul_rn(token_scale[nt][0], rec.scale);
+          s1 = __fmul_rn(token_scale[nt][1], rec.scale);
+        } else {
+          // tokens 8*nt .. 8*nt+7 share the scale of their 16-row group
+          const float a_s = (nt * 8 < rows) ? p.act_scales[static_cast<int64_t>(nt >> 1) * n_k + kt] : 0.0f;
+          s0 = s1 = __fmul_rn(a_s, rec.scale);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc[nt][q][0] = __fadd_rn(acc[nt][q][0], __fmul_rn(static_cast<float>(d[nt][q][0]), s0));
+          acc[nt][q][1] = __fadd_rn(acc[nt][q][1], __fmul_rn(static_cast<float>(d[nt][q][1]), s1));
+          acc[nt][q][2] = __fadd_rn(acc[nt][q][2], __fmul_rn(static_cast<float>(d[nt][q][2]), s0));
+          acc[nt][q][3] = __fadd_rn(acc[nt][q][3], __fmul_rn(static_cast<float>(d[nt][q][3]), s1));
+        }
+        if (p.acc_dump != nullptr) {
+          const int shift = is_w4 ? 4 : 0;
+          const int tok = nt * 8 + 2 * c;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int t = tok + (e & 1);
+              const int col = q * 16 + g + ((e & 2) ? 8 : 0);
+              if (t < rows) {
+                p.acc_dump[((static_cast<int64_t>(t) * p.n_j + j) * n_k + kt) * kTile + col] = d[nt][q][e] >> shift;
+              }
+            }
+          }
+        }
+      }
+    }
+    if (!ok) break;
+
+    // ---- finish the segment: combine the sixteen warp sums in warp order --------------------
+    {
+      float* slab = slabs + warp * kRows * kTile;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int tok = nt * 8 + 2 * c;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          slab[tok * kTile + q * 16 + g] = acc[nt][q][0];
+          slab[(tok + 1) * kTile + q * 16 + g] = acc[nt][q][1];
+          slab[tok * kTile + q * 16 + g + 8] = acc[nt][q][2];
+          slab[(tok + 1) * kTile + q * 16 + g + 8] = acc[nt][q][3];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[nt][q][e] = 0.0f;
+        }
+      }
     }
     consumer_sync();
-    const bool whole_row = seg_k_lo == 0 && k_hi == n_k;
+    for (int e = threadIdx.x; e < kRows * kTile; e += kConsumerThreads) {
+      float v = slabs[e];
+#pragma unroll
+      for (int w = 1; w < kConsumerWarps; ++w) v = __fadd_rn(v, slabs[w * kRows * kTile + e]);
+      tile[e] = v;
+    }
+    consumer_sync();
     const int32_t* meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
     const bool has_u = meta != nullptr && meta[0] != 0;
     int first_cta = blockIdx.x, last_cta = blockIdx.x;
@@ -276,7 +365,7 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) decode_linear_kerne
       __threadfence();
       consumer_sync();
       first_cta = owner_of(static_cast<int64_t>(j) * n_k, p.total_tiles, p.ctas);
-      last_cta = owner_of(static_cast<int64_t>(j + 1) * n_k - 1, p.total_tiles, p.ctas);
+      last_cta = owner_of(row_end - 1, p.total_tiles, p.ctas);
       if (threadIdx.x == 0) {
         const int arrived = atomicAdd(p.counters + j, 1);
         const bool last = arrived == last_cta - first_cta;
@@ -312,102 +401,14 @@ __global__ void __launch_bounds__(kThreads, NT == 1 ? 2 : 1) decode_linear_kerne
         store_any(p.out, p.out_dtype, o + 32, hi);
       }
     }
-    consumer_sync();  // the tile and the last-arriver flag are reused by the next segment
+    consumer_sync();  // slabs, tile and the last-arriver flag are reused by the next segment
     first_segment = false;
-  };
-
-  for (int gi = 0; gi < groups; ++gi) {
-    const int slot = gi % kSlots;
-    const int base = gi * kGroupTiles;
-    const int batch = count - base < kGroupTiles ? count - base : kGroupTiles;
-
-    // (1) activations of the batch straight from global memory (a few KiB, L1/L2
-    //     resident); requested before the wait so that their latency hides behind it
-    uint4 x[kGroupTiles][NT];
-    {
-      int kk = kt;
-#pragma unroll
-      for (int u = 0; u < kGroupTiles; ++u) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          x[u][nt] = make_uint4(0, 0, 0, 0);
-          if (u < batch && nt * 8 + g < rows) x[u][nt] = ldg_x(x_lane[nt] + static_cast<int64_t>(kk) * kTile);
-        }
-        if (++kk == n_k) kk = 0;
-      }
-    }
-    // (2) the slot's weights
-    if (warp == 0) AQ_TRACE_MARK(2 * gi);
-    if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_decode_status, 22)) break;
-    if (warp == 0) AQ_TRACE_MARK(2 * gi + 1);
-    // (3) + (4) records, weight vectors and integer dot products of the batch
-    TileRecord rec[kGroupTiles];
-#pragma unroll
-    for (int u = 0; u < kGroupTiles; ++u) rec[u] = recs[base + (u < batch ? u : 0)];
-    int d[kGroupTiles][NT][4];
-#pragma unroll
-    for (int u = 0; u < kGroupTiles; ++u) {
-      const bool is_w4 = (rec[u].offset_flag & kW4Flag) != 0;
-      const uint8_t* staged = ring + slot * kSlotBytes + u * kW8TileBytes;
-      const uint4 wa = weight_vector(staged, is_w4, w8_off, w4_off, w4_shift);
-      const uint4 wb = weight_vector(staged + (is_w4 ? 8 * 32 : 8 * 64), is_w4, w8_off, w4_off, w4_shift);
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        d[u][nt][0] = d[u][nt][1] = d[u][nt][2] = d[u][nt][3] = 0;
-        mma_s8(d[u][nt], wa.x, wb.x, wa.y, wb.y, x[u][nt].x, x[u][nt].y);
-        mma_s8(d[u][nt], wa.z, wb.z, wa.w, wb.w, x[u][nt].z, x[u][nt].w);
-      }
-    }
-    // (5) every lane's operands have been consumed by the warp-wide MMAs: release the slot
-    __syncwarp();
-    if (lane == 0 && gi + kSlots < groups) mbar_arrive(empty(slot));
-    // (6) scale and accumulate in increasing k; a row boundary finishes the segment
-#pragma unroll
-    for (int u = 0; u < kGroupTiles; ++u) {
-      if (u < batch) {
-        const bool is_w4 = (rec[u].offset_flag & kW4Flag) != 0;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          float s0, s1;
-          if (p.scale_mode == AQ_SCALE_TOKEN) {
-            s0 = __fmul_rn(token_scale[nt][0], rec[u].scale);
-            s1 = __fmul_rn(token_scale[nt][1], rec[u].scale);
-          } else {
-            // tokens 8*nt .. 8*nt+7 share the scale of their 16-row group
-            const float a_s = (nt * 8 < rows) ? p.act_scales[static_cast<int64_t>(nt >> 1) * n_k + kt] : 0.0f;
-            s0 = s1 = __fmul_rn(a_s, rec[u].scale);
-          }
-          acc[nt][0] = __fadd_rn(acc[nt][0], __fmul_rn(static_cast<float>(d[u][nt][0]), s0));
-          acc[nt][1] = __fadd_rn(acc[nt][1], __fmul_rn(static_cast<float>(d[u][nt][1]), s1));
-          acc[nt][2] = __fadd_rn(acc[nt][2], __fmul_rn(static_cast<float>(d[u][nt][2]), s0));
-          acc[nt][3] = __fadd_rn(acc[nt][3], __fmul_rn(static_cast<float>(d[u][nt][3]), s1));
-          if (p.acc_dump != nullptr) {
-            const int shift = is_w4 ? 4 : 0;
-            const int tok = nt * 8 + 2 * c;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int t = tok + (q & 1);
-              const int col = n_a + ((q & 2) ? 8 : 0);
-              if (t < rows) {
-                p.acc_dump[((static_cast<int64_t>(t) * p.n_j + j) * n_k + kt) * kTile + col] = d[u][nt][q] >> shift;
-              }
-            }
-          }
-        }
-        if (++kt == n_k) {
-          flush(n_k);
-          kt = 0;
-          seg_k_lo = 0;
-          ++j;
-        }
-      }
-    }
+    pos = seg_end;
   }
-  if (kt != seg_k_lo && *abort_flag == 0) flush(kt);  // the range ended inside a row
 }
 
 int smem_bytes(int mt) {
-  return kSlots * kSlotBytes + 8 * mt * kTile * 4 + kMaxRecords * 8 + kNumBars * 8 + 16;
+  return kSlots * kSlotBytes + (kConsumerWarps + 1) * 8 * mt * kTile * 4 + kMaxRecords * 8 + kNumBars * 8 + 16;
 }
 
 template <int MT>
@@ -449,7 +450,7 @@ int decode_ctas(int n_j, int n_k) {
 }
 
 int64_t decode_workspace_bytes(int64_t m, int n_j, int n_k) {
-  const int nt = m <= 8 ? 1 : (m <= 16 ? 2 : 4);
+  const int nt = m <= 8 ? 1 : 2;
   return kCounterBytes + partial_bytes(decode_ctas(n_j, n_k), nt);
 }
 
@@ -474,7 +475,7 @@ int launch_decode_linear(const LinearArgs& a, cudaStream_t stream) {
   p.ctas = decode_ctas(a.n_j, a.n_k);
   p.scale_mode = a.scale_mode;
   p.out_dtype = a.out_dtype;
-  return a.m <= 8 ? launch_mt<1>(p, stream) : (a.m <= 16 ? launch_mt<2>(p, stream) : launch_mt<4>(p, stream));
+  return a.m <= 8 ? launch_mt<1>(p, stream) : launch_mt<2>(p, stream);
 }
 
 #ifdef AQ_TRACE

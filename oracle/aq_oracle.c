@@ -76,17 +76,22 @@ void aqo_linear_fp32(const int8_t* xq, const float* a, const int8_t* w, const fl
 }
 
 /*
- * Same arithmetic as aqo_linear_fp32 with the partial sums cut where the persistent
- * decode kernel cuts them: the (j, k)-ordered tile sequence of T = n_j*n_k tiles is
- * split into `ranges` contiguous ranges, range i = [i*T/ranges, (i+1)*T/ranges);
- * inside a range tiles of one row accumulate in increasing k, and the partial sums of
- * the ranges sharing a row are added in range order.
+ * Same arithmetic as aqo_linear_fp32 with the sums grouped the way the persistent
+ * decode kernel groups them.  The (j, k)-ordered tile sequence of T = n_j*n_k tiles is
+ * split into `ranges` contiguous ranges, range i = [i*T/ranges, (i+1)*T/ranges).
+ * Inside a range, tile t belongs to worker (t - range_begin) % workers; for every row
+ * segment of the range each worker adds its tiles in increasing k, the worker sums are
+ * added in worker order, and the segment sums of the ranges sharing a row are added in
+ * range order.
  */
 void aqo_linear_fp32_ranges(const int8_t* xq, const float* a, const int8_t* w, const float* ws,
-                            float* out, int64_t M, int64_t n_j, int64_t n_k, int64_t ranges) {
+                            float* out, int64_t M, int64_t n_j, int64_t n_k, int64_t ranges,
+                            int64_t workers) {
   const int64_t T = n_j * n_k;
   if (ranges < 1) ranges = 1;
   if (ranges > T) ranges = T;
+  if (workers < 1) workers = 1;
+  if (workers > 64) workers = 64;
 #pragma omp parallel for collapse(2) schedule(static)
   for (int64_t j = 0; j < n_j; ++j) {
     for (int64_t m = 0; m < M; ++m) {
@@ -96,20 +101,27 @@ void aqo_linear_fp32_ranges(const int8_t* xq, const float* a, const int8_t* w, c
       while (k < n_k) {
         const int64_t t = j * n_k + k;
         const int64_t owner = ((t + 1) * ranges - 1) / T;
+        const int64_t begin = owner * T / ranges;
         int64_t end = (owner + 1) * T / ranges - j * n_k; /* first k of the next range */
         if (end > n_k) end = n_k;
-        float part[TILE];
-        for (int c = 0; c < TILE; ++c) part[c] = 0.0f;
+        float part[64][TILE];
+        for (int64_t v = 0; v < workers; ++v)
+          for (int c = 0; c < TILE; ++c) part[v][c] = 0.0f;
         for (; k < end; ++k) {
+          const int64_t v = (j * n_k + k - begin) % workers;
           const float scale = a[m * n_k + k] * ws[j * n_k + k];
           const int8_t* x = xq + (m * n_k + k) * TILE;
           const int8_t* tl = w + ((j * n_k + k) * TILE) * TILE;
           for (int c = 0; c < TILE; ++c) {
             const float scaled = (float)dot64(x, tl + c * TILE) * scale;
-            part[c] = part[c] + scaled;
+            part[v][c] = part[v][c] + scaled;
           }
         }
-        for (int c = 0; c < TILE; ++c) total[c] = first ? part[c] : total[c] + part[c];
+        for (int c = 0; c < TILE; ++c) {
+          float seg = part[0][c];
+          for (int64_t v = 1; v < workers; ++v) seg = seg + part[v][c];
+          total[c] = first ? seg : total[c] + seg;
+        }
         first = 0;
       }
       for (int c = 0; c < TILE; ++c) out[m * n_j * TILE + j * TILE + c] = total[c];
