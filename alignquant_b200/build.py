@@ -10,7 +10,7 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIB_PATH = PACKAGE_DIR / "libalignquant_b200.so"
-SOURCES = ("aq_abi.cu", "aq_quantize.cu", "aq_repack.cu", "aq_stream.cu", "aq_decode.cu", "aq_gemm_tmem.cu")
+SOURCES = ("aq_abi.cu", "aq_quantize.cu", "aq_repack.cu", "aq_stream.cu", "aq_cluster_decode.cu", "aq_decode.cu", "aq_gemm_tmem.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
@@ -33,7 +33,7 @@ def is_stale() -> bool:
     if not LIB_PATH.exists():
         return True
     built = LIB_PATH.stat().st_mtime
-    deps = [CSRC / name for name in SOURCES] + [CSRC / "aq_common.cuh", CSRC / "aq_ptx.cuh", PACKAGE_DIR.parent / "include" / "alignquant_b200.h"]
+    deps = [CSRC / name for name in SOURCES] + [CSRC / "aq_common.cuh", CSRC / "aq_ptx.cuh", CSRC / "aq_tile_math.cuh", PACKAGE_DIR.parent / "include" / "alignquant_b200.h"]
     return any(dep.stat().st_mtime > built for dep in deps)
 
 

@@ -62,11 +62,18 @@ constexpr int64_t kDecodeMaxRows = 16;   // the persistent decode kernel handles
 
 bool valid_split(int s) { return s == 0 || s == 1 || s == 2 || s == 4 || s == 8 || s == 16; }
 
-// 0 = cluster streaming kernel, 1 = tensor-memory GEMM, 2 = persistent decode kernel
-int choose_kernel(int64_t m, int schedule, int decode_splits) {
+// Kernel families (also the values aq_linear_plan reports):
+//   0 cluster kernel, eight warps per tile, tiles of a split added in increasing k
+//     (explicit split counts and 17..128 rows)
+//   1 tensor-memory GEMM
+//   2 persistent stream-K kernel (at most 16 rows, layers with very few tile rows)
+//   3 cluster kernel, one warp per tile (at most 16 rows; the default decode kernel)
+int choose_kernel(int64_t m, int n_j, int n_k, int schedule, int decode_splits) {
   if (schedule == AQ_SCHEDULE_PREFILL_M64) return 1;
   if (schedule == AQ_SCHEDULE_AUTO && m > kStreamMaxRows) return 1;
-  return (decode_splits == 0 && m <= kDecodeMaxRows) ? 2 : 0;
+  if (decode_splits != 0 || m > kDecodeMaxRows) return 0;
+  if (8 * n_j < num_sms() || !cluster_decode_supported(n_j, n_k)) return 2;
+  return 3;
 }
 
 }  // namespace
@@ -135,13 +142,13 @@ int64_t aq_linear_workspace_bytes(int64_t m, int32_t n_j, int32_t n_k, int sched
     fail(AQ_ERR_INVALID, "aq_linear_workspace_bytes: invalid problem");
     return AQ_ERR_INVALID;
   }
-  switch (choose_kernel(m, schedule, decode_splits)) {
-    case 0:
-      return 0;
+  switch (choose_kernel(m, n_j, n_k, schedule, decode_splits)) {
+    case 1:
+      return tmem_gemm_workspace_bytes(m, n_j, n_k);
     case 2:
       return decode_workspace_bytes(m, n_j, n_k);
     default:
-      return tmem_gemm_workspace_bytes(m, n_j, n_k);
+      return 0;
   }
 }
 
@@ -194,7 +201,8 @@ int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t
   a.workspace_bytes = workspace_bytes;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  const int kernel = choose_kernel(m, schedule, decode_splits);
+  const int kernel = choose_kernel(m, n_j, n_k, schedule, decode_splits);
+  if (kernel == 3) return launch_cluster_decode(a, s);
   if (kernel == 0) {
     AQ_REQUIRE(decode_splits == 0 || m <= kStreamMaxRows,
                "split override requires at most 128 rows");
@@ -209,9 +217,27 @@ int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t
   return kernel == 2 ? launch_decode_linear(a, s) : launch_tmem_gemm(a, s);
 }
 
-int aq_decode_ctas(int32_t n_j, int32_t n_k) {
-  if (n_j <= 0 || n_k <= 0) return fail(AQ_ERR_INVALID, "aq_decode_ctas: n_j and n_k must be positive");
-  return decode_ctas(n_j, n_k);
+int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int decode_splits, int32_t* kernel,
+                   int32_t* splits, int32_t* workers) {
+  AQ_REQUIRE(m >= 1 && n_j > 0 && n_k > 0 && schedule >= 0 && schedule <= 3, "aq_linear_plan: invalid problem");
+  AQ_REQUIRE(kernel != nullptr && splits != nullptr && workers != nullptr, "aq_linear_plan: NULL output");
+  const int k = choose_kernel(m, n_j, n_k, schedule, decode_splits);
+  *kernel = k;
+  *workers = 1;
+  *splits = 1;
+  if (k == 0) {
+    int s = decode_splits != 0 ? decode_splits : stream_auto_split(m, n_j, n_k);
+    if (s > 8) s = 8;
+    while (s > n_k) s /= 2;
+    *splits = s;  // the launcher may raise it further for very long K; see aq_stream.cu
+  } else if (k == 2) {
+    *splits = decode_ctas(n_j, n_k);
+    *workers = 16;
+  } else if (k == 3) {
+    *splits = cluster_decode_split(n_j, n_k);
+    *workers = 8;
+  }
+  return AQ_OK;
 }
 
 int aq_device_status(void* stream) {
@@ -220,14 +246,15 @@ int aq_device_status(void* stream) {
   const int stream_status = take_stream_status();
   const int gemm_status = take_gemm_status();
   const int decode_status = take_decode_status();
-  if (stream_status < 0 || gemm_status < 0 || decode_status < 0) {
+  const int cluster_decode_status = take_cluster_decode_status();
+  if (stream_status < 0 || gemm_status < 0 || decode_status < 0 || cluster_decode_status < 0) {
     return fail(AQ_ERR_CUDA, "could not read the device status words");
   }
-  if (stream_status != 0 || gemm_status != 0 || decode_status != 0) {
+  if (stream_status != 0 || gemm_status != 0 || decode_status != 0 || cluster_decode_status != 0) {
     return fail(AQ_ERR_DEVICE,
-                "a kernel wait timed out on the device (wait ids: cluster kernel %d, GEMM %d, decode kernel %d); "
+                "a kernel wait timed out on the device (wait ids: cluster kernels %d/%d, GEMM %d, stream-K kernel %d); "
                 "outputs of that launch are invalid and any workspace must be zeroed again",
-                stream_status, gemm_status, decode_status);
+                stream_status, cluster_decode_status, gemm_status, decode_status);
   }
   return AQ_OK;
 }

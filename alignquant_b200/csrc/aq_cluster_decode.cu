@@ -1,0 +1,368 @@
+// Decode kernel for at most 16 rows: one CTA per (tile row j, K split), split-K partial
+// sums exchanged through the distributed shared memory of a thread-block cluster.
+//
+// This is the default small-M kernel.  It combines the two things that matter at decode
+// sizes, where a whole layer is a few microseconds of HBM traffic:
+//   * a byte stream that starts immediately and never stalls -- the tiles of one
+//     (row, K range) are contiguous in the prepared image, so the producer warp moves
+//     them with ONE bulk asynchronous copy per ring slot of eight tiles (up to 32 KiB,
+//     counted on the slot's mbarrier); the first two slots are requested before the grid
+//     dependency is resolved, so under programmatic dependent launch they overlap the
+//     preceding kernel;
+//   * tile-level parallelism -- eight consumer warps each take whole tiles (tile i of
+//     the range goes to warp i % 8; weights are the 16-row operand of
+//     mma.sync.m16n8k32.s8, up to eight activation rows the 8-column operand), so
+//     eight tiles are in progress per CTA and, with two CTAs per SM, sixteen per SM.
+// The split count is chosen so that rows x splits is at most two CTAs per SM; all CTAs
+// are then co-resident and stream concurrently.
+//
+// Summation order (all FP32, separately rounded multiply and add as in
+// alignquant/kernels/cuda/linear.cu:956-963): a warp adds its tiles in increasing k;
+// the eight warp sums are added in warp order; the split sums are added in split order
+// (the reference reducer's order, linear.cu:1339-1343).  No workspace, no atomics.
+#include <cooperative_groups.h>
+
+#include <mutex>
+
+#include "aq_common.cuh"
+#include "aq_ptx.cuh"
+#include "aq_tile_math.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace aq {
+
+__device__ int g_cluster_decode_status = 0;
+
+namespace {
+
+struct Params {
+  const int8_t* xq;
+  const float* act_scales;
+  const TileRecord* records;
+  const uint8_t* payload;
+  const int32_t* u_metadata;
+  void* out;
+  int32_t* acc_dump;
+  int64_t m;
+  int n_j;
+  int n_k;
+  int scale_mode;
+  int out_dtype;
+};
+
+constexpr int kGroupTiles = 8;  // tiles per ring slot
+constexpr int kSlots = 2;
+constexpr int kSlotBytes = kGroupTiles * kW8TileBytes;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kMaxCount = 512;  // tiles of one CTA's K range
+constexpr int kNumBars = 2 * kSlots;
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+// Shared memory: [ring kSlots x 32 KiB][slabs 8 x (8*NT) x 64 f32][tile (8*NT) x 64 f32]
+//                [records kMaxCount][barriers][abort flag]
+template <int NT>
+__global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Params p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  constexpr int kRows = 8 * NT;
+  uint8_t* ring = smem;
+  float* slabs = reinterpret_cast<float*>(smem + kSlots * kSlotBytes);
+  float* tile = slabs + kConsumerWarps * kRows * kTile;
+  TileRecord* recs = reinterpret_cast<TileRecord*>(tile + kRows * kTile);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(recs + kMaxCount);
+  volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(bars + kNumBars);
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int split_k = static_cast<int>(cluster.num_blocks());
+  const int split = static_cast<int>(cluster.block_rank());
+  const int j = blockIdx.x;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_k = p.n_k;
+  const int k_begin = static_cast<int>(static_cast<int64_t>(n_k) * split / split_k);
+  const int k_end = static_cast<int>(static_cast<int64_t>(n_k) * (split + 1) / split_k);
+  const int count = k_end - k_begin;
+  const int groups = (count + kGroupTiles - 1) / kGroupTiles;
+  const int rows = p.m < kRows ? static_cast<int>(p.m) : kRows;
+
+  const uint32_t bar0 = smem_u32(bars);
+  auto full = [&](int s) { return bar0 + 8u * s; };
+  auto empty = [&](int s) { return bar0 + 8u * (kSlots + s); };
+  const uint32_t ring_addr = smem_u32(ring);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(full(s), 1);
+      mbar_init(empty(s), kGroupTiles);
+    }
+    *abort_flag = 0;
+    mbar_init_fence();
+    fence_proxy_async();
+  }
+  __syncthreads();
+
+  const TileRecord* my_records = p.records + static_cast<int64_t>(j) * n_k + k_begin;
+  const bool producer = warp == kConsumerWarps;
+
+  // First ring fill before the grid dependency is resolved: weights are static.
+  if (producer && lane < kSlots && lane < groups) {
+    const int first = lane * kGroupTiles;
+    const int last = (first + kGroupTiles < count ? first + kGroupTiles : count) - 1;
+    const TileRecord rf = my_records[first];
+    const uint32_t bytes = span_bytes(rf, my_records[last]);
+    mbar_expect_tx(full(lane), bytes);
+    bulk_copy(ring_addr + lane * kSlotBytes,
+              p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(lane));
+  }
+  for (int i = threadIdx.x; i < count; i += kThreads) recs[i] = my_records[i];
+  grid_launch_dependents();
+  grid_dependency_wait();  // activations and their scales come from the preceding kernel
+  __syncthreads();
+
+  if (producer) {
+    if (lane == 0) {
+      for (int gi = kSlots; gi < groups; ++gi) {
+        const int slot = gi % kSlots;
+        if (!mbar_wait(empty(slot), ((gi / kSlots) - 1) & 1, abort_flag, &g_cluster_decode_status, 31)) break;
+        const int first = gi * kGroupTiles;
+        const int last = (first + kGroupTiles < count ? first + kGroupTiles : count) - 1;
+        const TileRecord rf = recs[first];
+        const uint32_t bytes = span_bytes(rf, recs[last]);
+        mbar_expect_tx(full(slot), bytes);
+        bulk_copy(ring_addr + slot * kSlotBytes,
+                  p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(slot));
+      }
+    }
+    __syncwarp();
+  } else {
+    // Lane (g, c) = (lane/4, lane%4) holds, for column group q = 0..3, the weight vectors
+    // of columns 16q+g and 16q+g+8 and the activation vector of token 8*pass+g, all for
+    // k in [16c, 16c+16).  MMA results: d[0], d[1] = column 16q+g, tokens 8*pass+2c, +1;
+    // d[2], d[3] = column 16q+g+8, same tokens.
+    const int g = lane >> 2;
+    const int c = lane & 3;
+    const int64_t k_bytes = static_cast<int64_t>(n_k) * kTile;
+    const uint32_t w8_off = static_cast<uint32_t>(g * 64 + ((c ^ ((g >> 1) & 3)) << 4));
+    const uint32_t w4_off = static_cast<uint32_t>(g * 32 + (c >> 1) * 16);
+    const int w4_shift = (c & 1) ? 0 : 4;
+    float token_scale[NT][2];
+    const int8_t* x_lane[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int tok = nt * 8 + 2 * c;
+      token_scale[nt][0] = (p.scale_mode == AQ_SCALE_TOKEN && tok < rows) ? p.act_scales[tok] : 0.0f;
+      token_scale[nt][1] = (p.scale_mode == AQ_SCALE_TOKEN && tok + 1 < rows) ? p.act_scales[tok + 1] : 0.0f;
+      x_lane[nt] = p.xq + static_cast<int64_t>(nt * 8 + g) * k_bytes + static_cast<int64_t>(k_begin) * kTile + c * 16;
+    }
+    auto load_x = [&](int i, uint4 (&x)[NT]) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        x[nt] = make_uint4(0, 0, 0, 0);
+        if (nt * 8 + g < rows) x[nt] = ldg_x(x_lane[nt] + static_cast<int64_t>(i) * kTile);
+      }
+    };
+
+    float acc[NT][4][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[nt][q][e] = 0.0f;
+      }
+    }
+    uint4 x_next[NT];
+    if (warp < count) load_x(warp, x_next);  // activation vectors are requested one tile ahead
+    for (int i = warp; i < count; i += kConsumerWarps) {
+      const int gi = i / kGroupTiles;
+      const int slot = gi % kSlots;
+      const int kt = k_begin + i;
+      uint4 x[NT];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) x[nt] = x_next[nt];
+      if (i + kConsumerWarps < count) load_x(i + kConsumerWarps, x_next);
+      if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_cluster_decode_status, 32)) break;
+      const TileRecord rec = recs[i];
+      const TileRecord rec0 = recs[gi * kGroupTiles];
+      const bool is_w4 = (rec.offset_flag & kW4Flag) != 0;
+      const uint8_t* staged = ring + slot * kSlotBytes +
+                              ((rec.offset_flag & ~kW4Flag) - (rec0.offset_flag & ~kW4Flag)) * kW4TileBytes;
+      int d[NT][4][4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint8_t* group = staged + q * (is_w4 ? 16 * 32 : 16 * 64);
+        const uint4 wa = weight_vector(group, is_w4, w8_off, w4_off, w4_shift);
+        const uint4 wb = weight_vector(group + (is_w4 ? 8 * 32 : 8 * 64), is_w4, w8_off, w4_off, w4_shift);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          d[nt][q][0] = d[nt][q][1] = d[nt][q][2] = d[nt][q][3] = 0;
+          mma_s8(d[nt][q], wa.x, wb.x, wa.y, wb.y, x[nt].x, x[nt].y);
+          mma_s8(d[nt][q], wa.z, wb.z, wa.w, wb.w, x[nt].z, x[nt].w);
+        }
+      }
+      // every lane's operands have been consumed by the warp-wide MMAs: this tile is done
+      __syncwarp();
+      if (lane == 0 && gi + kSlots < groups) mbar_arrive(empty(slot));
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float s0, s1;
+        if (p.scale_mode == AQ_SCALE_TOKEN) {
+          s0 = __fmul_rn(token_scale[nt][0], rec.scale);
+          s1 = __fmul_rn(token_scale[nt][1], rec.scale);
+        } else {
+          // tokens 8*nt .. 8*nt+7 share the scale of their 16-row group
+          const float a_s = (nt * 8 < rows) ? p.act_scales[static_cast<int64_t>(nt >> 1) * n_k + kt] : 0.0f;
+          s0 = s1 = __fmul_rn(a_s, rec.scale);
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          acc[nt][q][0] = __fadd_rn(acc[nt][q][0], __fmul_rn(static_cast<float>(d[nt][q][0]), s0));
+          acc[nt][q][1] = __fadd_rn(acc[nt][q][1], __fmul_rn(static_cast<float>(d[nt][q][1]), s1));
+          acc[nt][q][2] = __fadd_rn(acc[nt][q][2], __fmul_rn(static_cast<float>(d[nt][q][2]), s0));
+          acc[nt][q][3] = __fadd_rn(acc[nt][q][3], __fmul_rn(static_cast<float>(d[nt][q][3]), s1));
+        }
+        if (p.acc_dump != nullptr) {
+          const int shift = is_w4 ? 4 : 0;
+          const int tok = nt * 8 + 2 * c;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int t = tok + (e & 1);
+              const int col = q * 16 + g + ((e & 2) ? 8 : 0);
+              if (t < rows) {
+                p.acc_dump[((static_cast<int64_t>(t) * p.n_j + j) * n_k + kt) * kTile + col] = d[nt][q][e] >> shift;
+              }
+            }
+          }
+        }
+      }
+    }
+    // ---- combine the eight warp sums in warp order -----------------------------------------
+    float* slab = slabs + warp * kRows * kTile;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int tok = nt * 8 + 2 * c;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        slab[tok * kTile + q * 16 + g] = acc[nt][q][0];
+        slab[(tok + 1) * kTile + q * 16 + g] = acc[nt][q][1];
+        slab[tok * kTile + q * 16 + g + 8] = acc[nt][q][2];
+        slab[(tok + 1) * kTile + q * 16 + g + 8] = acc[nt][q][3];
+      }
+    }
+    consumer_sync();
+    for (int e = threadIdx.x; e < kRows * kTile; e += kConsumerThreads) {
+      float v = slabs[e];
+#pragma unroll
+      for (int w = 1; w < kConsumerWarps; ++w) v = __fadd_rn(v, slabs[w * kRows * kTile + e]);
+      tile[e] = v;
+    }
+  }
+
+  // ---- split-K exchange through cluster shared memory ------------------------------------
+  cluster.sync();
+  if (!producer) {
+    const int32_t* meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
+    const bool has_u = meta != nullptr && meta[0] != 0;
+    const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
+    // rank r finishes rows r, r + split_k, ...; its warps take them round robin
+    for (int row = split + split_k * warp; row < rows; row += split_k * kConsumerWarps) {
+      float lo = 0.0f, hi = 0.0f;
+      for (int s = 0; s < split_k; ++s) {
+        const float* remote = cluster.map_shared_rank(tile, s);
+        const float a = remote[row * kTile + lane];
+        const float b = remote[row * kTile + lane + 32];
+        lo = (s == 0) ? a : __fadd_rn(lo, a);
+        hi = (s == 0) ? b : __fadd_rn(hi, b);
+      }
+      if (has_u) inverse_u_row(lo, hi, meta, lane);
+      const int64_t o = static_cast<int64_t>(row) * n_cols + static_cast<int64_t>(j) * kTile + lane;
+      store_any(p.out, p.out_dtype, o, lo);
+      store_any(p.out, p.out_dtype, o + 32, hi);
+    }
+  }
+  cluster.sync();  // peers may still be reading this CTA's tile
+}
+
+int smem_bytes(int nt) {
+  return kSlots * kSlotBytes + (kConsumerWarps + 1) * 8 * nt * kTile * 4 + kMaxCount * 8 + kNumBars * 8 + 16;
+}
+
+template <int NT>
+int launch_nt(const Params& p, int split_k, cudaStream_t stream) {
+  static std::once_flag once[64];
+  int device = 0;
+  int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
+  if (rc != AQ_OK) return rc;
+  cudaError_t attr_status = cudaSuccess;
+  std::call_once(once[device & 63], [&] {
+    attr_status = cudaFuncSetAttribute(cluster_decode_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       smem_bytes(NT));
+  });
+  rc = check_cuda(attr_status, "cudaFuncSetAttribute(cluster_decode_kernel)");
+  if (rc != AQ_OK) return rc;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(p.n_j), static_cast<unsigned>(split_k), 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = static_cast<size_t>(smem_bytes(NT));
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = static_cast<unsigned>(split_k);
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = use_dependent_launch() ? 2 : 1;
+  return check_cuda(cudaLaunchKernelEx(&config, cluster_decode_kernel<NT>, p), "cluster decode launch");
+}
+
+}  // namespace
+
+// Largest split (cluster size, at most 8) that keeps rows x splits within two CTAs per SM,
+// never shorter than one tile per CTA and never longer than the record buffer.
+int cluster_decode_split(int n_j, int n_k) {
+  int split = 2 * num_sms() / n_j;
+  if (split < 1) split = 1;
+  if (split > 8) split = 8;
+  if (split > n_k) split = n_k;
+  while (split < 8 && (n_k + split - 1) / split > kMaxCount) ++split;
+  return split;
+}
+
+bool cluster_decode_supported(int n_j, int n_k) { return (n_k + 7) / 8 <= kMaxCount && n_j > 0; }
+
+int launch_cluster_decode(const LinearArgs& a, cudaStream_t stream) {
+  Params p;
+  p.xq = a.xq;
+  p.act_scales = a.act_scales;
+  p.records = a.records;
+  p.payload = a.payload;
+  p.u_metadata = a.u_metadata;
+  p.out = a.out;
+  p.acc_dump = a.acc_dump;
+  p.m = a.m;
+  p.n_j = a.n_j;
+  p.n_k = a.n_k;
+  p.scale_mode = a.scale_mode;
+  p.out_dtype = a.out_dtype;
+  const int split = cluster_decode_split(a.n_j, a.n_k);
+  return a.m <= 8 ? launch_nt<1>(p, split, stream) : launch_nt<2>(p, split, stream);
+}
+
+int take_cluster_decode_status() {
+  int status = 0;
+  if (cudaMemcpyFromSymbol(&status, g_cluster_decode_status, sizeof(int)) != cudaSuccess) return -1;
+  if (status != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_cluster_decode_status, &zero, sizeof(int));
+  }
+  return status;
+}
+
+}  // namespace aq

@@ -76,7 +76,13 @@ struct LinearArgs {
 int launch_stream_linear(const LinearArgs& a, int split_k, cudaStream_t stream);
 int stream_auto_split(int64_t m, int n_j, int n_k);
 
-// Persistent stream-K kernel for m <= 32 (needs a zeroed, self-cleaning workspace).
+// Warp-per-tile cluster kernel for m <= 16 (the default decode kernel).
+int launch_cluster_decode(const LinearArgs& a, cudaStream_t stream);
+int cluster_decode_split(int n_j, int n_k);
+bool cluster_decode_supported(int n_j, int n_k);
+int take_cluster_decode_status();
+
+// Persistent stream-K kernel for m <= 16 (needs a zeroed, self-cleaning workspace).
 int launch_decode_linear(const LinearArgs& a, cudaStream_t stream);
 int64_t decode_workspace_bytes(int64_t m, int n_j, int n_k);
 int decode_ctas(int n_j, int n_k);

@@ -82,37 +82,10 @@ constexpr int64_t kCounterBytes = static_cast<int64_t>(kMaxCounterRows) * 4;
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
-__device__ __forceinline__ uint4 ldg_x(const int8_t* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-
 // first tile of CTA i, and the CTA that owns tile t, for T tiles cut into G ranges
 __device__ __forceinline__ int64_t range_begin(int64_t i, int64_t total, int ctas) { return i * total / ctas; }
 __device__ __forceinline__ int owner_of(int64_t t, int64_t total, int ctas) {
   return static_cast<int>(((t + 1) * ctas - 1) / total);
-}
-
-// payload bytes of tiles [first, last] given their records (tiles are contiguous)
-__device__ __forceinline__ uint32_t span_bytes(const TileRecord& first, const TileRecord& last) {
-  const uint32_t units = (last.offset_flag & ~kW4Flag) + ((last.offset_flag & kW4Flag) ? 1u : 2u) -
-                         (first.offset_flag & ~kW4Flag);
-  return units * kW4TileBytes;
-}
-
-// 16-byte weight vector of output column n, k in [16c, 16c+16), from a staged tile
-// (layouts in aq_tile_math.cuh); W4 nibbles are widened to bytes holding 16*w.
-__device__ __forceinline__ uint4 weight_vector(const uint8_t* tile, bool is_w4, uint32_t w8_off, uint32_t w4_off,
-                                               int w4_shift) {
-  uint4 v = *reinterpret_cast<const uint4*>(tile + (is_w4 ? w4_off : w8_off));
-  if (is_w4) {
-    v.x = (v.x << w4_shift) & 0xf0f0f0f0u;
-    v.y = (v.y << w4_shift) & 0xf0f0f0f0u;
-    v.z = (v.z << w4_shift) & 0xf0f0f0f0u;
-    v.w = (v.w << w4_shift) & 0xf0f0f0f0u;
-  }
-  return v;
 }
 
 // Lane (g, c) = (lane/4, lane%4) of a consumer warp holds, for column group q = 0..3,
@@ -266,10 +239,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) x[nt] = x_next[nt];
       if (i + kConsumerWarps < count) load_x(i + kConsumerWarps, x_next);
+      if (warp == 0) AQ_TRACE_MARK(100 + 2 * (i / kConsumerWarps));
       if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_decode_status, 22)) {
         ok = false;
         break;
       }
+      if (warp == 0) AQ_TRACE_MARK(101 + 2 * (i / kConsumerWarps));
       const TileRecord rec = recs[i];
       const TileRecord rec0 = recs[gi * kGroupTiles];
       const bool is_w4 = (rec.offset_flag & kW4Flag) != 0;
@@ -329,6 +304,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
     if (!ok) break;
 
     // ---- finish the segment: combine the sixteen warp sums in warp order --------------------
+    if (warp == 0) AQ_TRACE_MARK(3000 + 8 * (first_segment ? 0 : 1));
     {
       float* slab = slabs + warp * kRows * kTile;
 #pragma unroll
@@ -353,6 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
       tile[e] = v;
     }
     consumer_sync();
+    if (warp == 0) AQ_TRACE_MARK(3001 + 8 * (first_segment ? 0 : 1));
     const int32_t* meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
     const bool has_u = meta != nullptr && meta[0] != 0;
     int first_cta = blockIdx.x, last_cta = blockIdx.x;
@@ -375,6 +352,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
       consumer_sync();
       finish = *last_flag != 0;
       if (finish) __threadfence();
+      if (warp == 0) AQ_TRACE_MARK(3002 + 8 * (first_segment ? 0 : 1));
     }
     if (finish) {
       for (int row = warp; row < rows; row += kConsumerWarps) {
@@ -402,6 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
       }
     }
     consumer_sync();  // slabs, tile and the last-arriver flag are reused by the next segment
+    if (warp == 0) AQ_TRACE_MARK(3003 + 8 * (first_segment ? 0 : 1));
     first_segment = false;
     pos = seg_end;
   }

@@ -56,6 +56,37 @@ __device__ __forceinline__ void tile_accumulate(float (&acc)[4], const int (&d)[
   acc[3] = __fadd_rn(acc[3], __fmul_rn(static_cast<float>(d[3]), s_hi));
 }
 
+// ---- helpers of the warp-per-tile kernels ------------------------------------------
+// There the weights are the 16-row MMA operand (16 output columns per MMA pair) and up
+// to eight activation rows ("tokens") the 8-column operand.
+
+__device__ __forceinline__ uint4 ldg_x(const int8_t* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// payload bytes of tiles [first, last] given their records (tiles are contiguous)
+__device__ __forceinline__ uint32_t span_bytes(const TileRecord& first, const TileRecord& last) {
+  const uint32_t units = (last.offset_flag & ~kW4Flag) + ((last.offset_flag & kW4Flag) ? 1u : 2u) -
+                         (first.offset_flag & ~kW4Flag);
+  return units * kW4TileBytes;
+}
+
+// 16-byte weight vector at a precomputed lane offset of a staged tile; W4 nibbles are
+// widened to bytes holding 16*w.
+__device__ __forceinline__ uint4 weight_vector(const uint8_t* tile, bool is_w4, uint32_t w8_off, uint32_t w4_off,
+                                               int w4_shift) {
+  uint4 v = *reinterpret_cast<const uint4*>(tile + (is_w4 ? w4_off : w8_off));
+  if (is_w4) {
+    v.x = (v.x << w4_shift) & 0xf0f0f0f0u;
+    v.y = (v.y << w4_shift) & 0xf0f0f0f0u;
+    v.z = (v.z << w4_shift) & 0xf0f0f0f0u;
+    v.w = (v.w << w4_shift) & 0xf0f0f0f0u;
+  }
+  return v;
+}
+
 __device__ __forceinline__ void store_any(void* out, int dtype, int64_t index, float value) {
   if (dtype == AQ_F32) {
     static_cast<float*>(out)[index] = value;

@@ -378,12 +378,24 @@ def device_status(device: torch.device | str | None = None) -> None:
         _lib.check(status)
 
 
-def decode_ctas(n_j: int, n_k: int) -> int:
-    """Number of tile ranges the persistent decode kernel uses for an n_j x n_k layer."""
-    value = int(_lib.load().aq_decode_ctas(int(n_j), int(n_k)))
-    if value < 0:
-        _lib.check(value)
-    return value
+def linear_plan(m: int, n_j: int, n_k: int, *, schedule: str = "auto", decode_splits: int = 0) -> dict[str, int]:
+    """Kernel family, split count and accumulator count ``aq_linear`` will use.
+
+    ``kernel``: 0 cluster kernel (tiles of a split added in increasing k), 1 GEMM,
+    2 persistent stream-K kernel, 3 warp-per-tile cluster kernel; see ``aq_linear_plan``
+    in ``include/alignquant_b200.h`` for how ``splits`` and ``workers`` fix the FP32
+    summation order.
+    """
+    import ctypes
+
+    kernel, splits, workers = ctypes.c_int32(), ctypes.c_int32(), ctypes.c_int32()
+    _lib.check(
+        _lib.load().aq_linear_plan(
+            int(m), int(n_j), int(n_k), _lib.SCHEDULE_CODES[str(schedule)], int(decode_splits),
+            ctypes.addressof(kernel), ctypes.addressof(splits), ctypes.addressof(workers),
+        )
+    )
+    return {"kernel": kernel.value, "splits": splits.value, "workers": workers.value}
 
 
 __all__ = [
@@ -394,5 +406,5 @@ __all__ = [
     "prepare_weights",
     "PreparedWeights",
     "device_status",
-    "decode_ctas",
+    "linear_plan",
 ]

@@ -143,14 +143,24 @@ AQ_API int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, 
               void* workspace, int64_t workspace_bytes, int32_t* acc_dump, void* stream);
 
 /*
- * Number of contiguous tile ranges (CTAs) the persistent decode kernel cuts an
- * n_j x n_k layer into on the current device.  Range i covers tiles
- * [i*T/G, (i+1)*T/G) of the (j, k)-ordered tile sequence (T = n_j*n_k, G = result);
- * partial sums of ranges that share a tile row are added in range order.  Exposed so
- * that callers can reproduce the floating-point summation order; the reference's
- * counterpart is its split-K heuristic (alignquant/kernels/cuda/linear.cu:1679-1691).
+ * How aq_linear will run a problem on the current device, so that a caller can
+ * reproduce the FP32 summation order (the integer tile sums never depend on it):
+ *   *kernel  0  cluster kernel: K tiles cut into *splits ranges
+ *               [n_k*s/splits, n_k*(s+1)/splits), tiles of a range added in increasing k,
+ *               range sums added in range order (the reference's split-K order,
+ *               alignquant/kernels/cuda/linear.cu:1237-1238, 1339-1343)
+ *            1  tensor-memory GEMM: one range, increasing k
+ *            2  persistent stream-K kernel: the (j, k)-ordered tile sequence cut into
+ *               *splits contiguous ranges [i*T/splits, (i+1)*T/splits); inside a range
+ *               tile t goes to accumulator (t - range begin) % *workers
+ *            3  warp-per-tile cluster kernel: ranges as for 0; inside a range tile k
+ *               goes to accumulator (k - range begin) % *workers
+ *   In 2 and 3 every accumulator adds its tiles in increasing k, the accumulators of a
+ *   range (row segment) are added in index order, and the range sums in range order.
+ * The reference's counterpart is its split-K heuristic (linear.cu:1679-1691).
  */
-AQ_API int aq_decode_ctas(int32_t n_j, int32_t n_k);
+AQ_API int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int decode_splits,
+                          int32_t* kernel, int32_t* splits, int32_t* workers);
 
 /*
  * Synchronises `stream`, then returns AQ_ERR_DEVICE if a kernel of this library gave

@@ -47,28 +47,42 @@ void aqo_tile_accumulators(const int8_t* xq, const int8_t* w, int32_t* out,
   }
 }
 
-/* out[M][n_j*64] float32, kernel operation order */
+/*
+ * out[M][n_j*64] float32, kernel operation order.  K tiles are cut into split_k ranges
+ * [n_k*s/split_k, n_k*(s+1)/split_k); inside a range tile k belongs to worker
+ * (k - range_begin) % workers, every worker adds its tiles in increasing k, the worker
+ * sums are added in worker order and the range sums in range order.  workers = 1 is the
+ * reference kernels' own order.
+ */
 void aqo_linear_fp32(const int8_t* xq, const float* a, const int8_t* w, const float* ws,
-                     float* out, int64_t M, int64_t n_j, int64_t n_k, int64_t split_k) {
+                     float* out, int64_t M, int64_t n_j, int64_t n_k, int64_t split_k, int64_t workers) {
   if (split_k < 1) split_k = 1;
+  if (workers < 1) workers = 1;
+  if (workers > 64) workers = 64;
 #pragma omp parallel for collapse(2) schedule(static)
   for (int64_t j = 0; j < n_j; ++j) {
     for (int64_t m = 0; m < M; ++m) {
       float total[TILE];
       for (int64_t s = 0; s < split_k; ++s) {
-        float part[TILE];
-        for (int c = 0; c < TILE; ++c) part[c] = 0.0f;
+        float part[64][TILE];
+        for (int64_t v = 0; v < workers; ++v)
+          for (int c = 0; c < TILE; ++c) part[v][c] = 0.0f;
         const int64_t k0 = n_k * s / split_k, k1 = n_k * (s + 1) / split_k;
         for (int64_t k = k0; k < k1; ++k) {
+          const int64_t v = (k - k0) % workers;
           const float scale = a[m * n_k + k] * ws[j * n_k + k];
           const int8_t* x = xq + (m * n_k + k) * TILE;
           const int8_t* t = w + ((j * n_k + k) * TILE) * TILE;
           for (int c = 0; c < TILE; ++c) {
             const float scaled = (float)dot64(x, t + c * TILE) * scale;
-            part[c] = part[c] + scaled;
+            part[v][c] = part[v][c] + scaled;
           }
         }
-        for (int c = 0; c < TILE; ++c) total[c] = (s == 0) ? part[c] : total[c] + part[c];
+        for (int c = 0; c < TILE; ++c) {
+          float seg = part[0][c];
+          for (int64_t v = 1; v < workers; ++v) seg = seg + part[v][c];
+          total[c] = (s == 0) ? seg : total[c] + seg;
+        }
       }
       for (int c = 0; c < TILE; ++c) out[m * n_j * TILE + j * TILE + c] = total[c];
     }

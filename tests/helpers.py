@@ -62,3 +62,11 @@ def torch_activation(x: np.ndarray, dtype: torch.dtype, device="cuda") -> torch.
 def forced_layer(n: int, k: int, seed: int, fraction: float):
     """synthetic_layer with an exact all-W4 (1.0) / all-W8 (0.0) / mixed map."""
     return oc.synthetic_layer(n, k, seed, w4_fraction=fraction)
+
+
+def planned_fp32(ext, xq_np, a_mk, tiles, scales, m, n_j, n_k, **plan_args):
+    """FP32 result in the summation order the library reports for this problem."""
+    plan = ext.linear_plan(m, n_j, n_k, **plan_args)
+    if plan["kernel"] == 2:
+        return oc.linear_fp32_ranges_c(xq_np, a_mk, tiles, scales, plan["splits"], plan["workers"])
+    return oc.linear_fp32_c(xq_np, a_mk, tiles, scales, plan["splits"], plan["workers"])

@@ -116,17 +116,18 @@ def test_stream_linear_matches_oracle(ext, n, k, m, scale_mode):
         if split:
             want = oc.linear_fp32_c(xq_np, a_mk, tiles, scales, split)
             assert np.array_equal(got, want), f"fp32 result not in reference operation order (split {split})"
-        elif m <= 16:  # automatic schedule: persistent decode kernel, sums grouped by range and warp
-            want = oc.linear_fp32_ranges_c(xq_np, a_mk, tiles, scales, ext.decode_ctas(n_j, n_k))
-            assert np.array_equal(got, want), "fp32 result differs from the range-ordered emulation"
+        elif m <= 16:  # automatic schedule: decode kernels, sums grouped as the library's plan says
+            want = helpers.planned_fp32(ext, xq_np, a_mk, tiles, scales, m, n_j, n_k, schedule=schedule)
+            assert np.array_equal(got, want), "fp32 result differs from the planned summation order"
         assert np.allclose(got, y64, rtol=REL, atol=ABS)
 
 
 @pytest.mark.parametrize("m", [1, 7, 8, 16])
-@pytest.mark.parametrize("n,k", [(3072, 3072), (1024, 8192), (5120, 256)])
+@pytest.mark.parametrize("n,k", [(3072, 3072), (1024, 8192), (5120, 256), (16384, 1024), (640, 4096)])
 def test_decode_kernel_many_ranges(ext, n, k, m):
-    """Layers with more tiles than SMs: ranges start and end inside tile rows, rows are
-    finished by whichever CTA arrives last, and repeated calls reuse the workspace."""
+    """Layers with more tiles than SMs through both decode kernels (few tile rows: the
+    persistent stream-K kernel, whose ranges start and end inside tile rows and reuse the
+    workspace across calls; otherwise the warp-per-tile cluster kernel)."""
     n_j, n_k = n // 64, k // 64
     packed, states, tiles, scales = oc.synthetic_layer(n, k, seed=n + k)
     weights, _ = helpers.prepare_layer(packed, n_k)
@@ -138,7 +139,7 @@ def test_decode_kernel_many_ranges(ext, n, k, m):
             a_mk = oc.expand_act_scales(a_s.cpu().numpy(), m, n_k, "token")
         else:
             a_mk = np.repeat(a_s.cpu().numpy().reshape(-1, n_k), 16, axis=0)[:m]
-        want = oc.linear_fp32_ranges_c(xq_np, a_mk, tiles, scales, ext.decode_ctas(n_j, n_k))
+        want = helpers.planned_fp32(ext, xq_np, a_mk, tiles, scales, m, n_j, n_k)
         for _ in range(3):
             out = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode=scale_mode)
             ext.device_status()
