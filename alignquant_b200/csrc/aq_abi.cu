@@ -234,7 +234,7 @@ int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int decode
     *splits = decode_ctas(n_j, n_k);
     *workers = 16;
   } else if (k == 3) {
-    *splits = cluster_decode_split(n_j, n_k);
+    *splits = cluster_decode_split(m, n_j, n_k);
     *workers = 8;
   }
   return AQ_OK;

@@ -324,13 +324,51 @@ int launch_nt(const Params& p, int split_k, cudaStream_t stream) {
 
 }  // namespace
 
-// Largest split (cluster size, at most 8) that keeps rows x splits within two CTAs per SM,
-// never shorter than one tile per CTA and never longer than the record buffer.
-int cluster_decode_split(int n_j, int n_k) {
-  int split = 2 * num_sms() / n_j;
-  if (split < 1) split = 1;
-  if (split > 8) split = 8;
-  if (split > n_k) split = n_k;
+namespace {
+
+// How many clusters of `split` CTAs of the NT-variant can be resident at once on the
+// current device (0 when the query fails); cached per device.
+int max_active_clusters(int nt, int split) {
+  static std::mutex mutex;
+  static int cache[64][2][9];  // [device][nt - 1][split], 0 = not queried yet, -1 = failed
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+  std::lock_guard<std::mutex> lock(mutex);
+  int& slot = cache[device][nt - 1][split];
+  if (slot == 0) {
+    const void* kernel = nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1>)
+                                 : reinterpret_cast<const void*>(cluster_decode_kernel<2>);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(nt));
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(1, static_cast<unsigned>(split), 1);
+    config.blockDim = dim3(kThreads, 1, 1);
+    config.dynamicSmemBytes = static_cast<size_t>(smem_bytes(nt));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = static_cast<unsigned>(split);
+    attr[0].val.clusterDim.z = 1;
+    config.attrs = attr;
+    config.numAttrs = 1;
+    int clusters = 0;
+    const cudaError_t status = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
+    if (status != cudaSuccess) (void)cudaGetLastError();
+    slot = (status == cudaSuccess && clusters > 0) ? clusters : -1;
+  }
+  return slot > 0 ? slot : 0;
+}
+
+}  // namespace
+
+// Largest split (cluster size, at most 8) for which all n_j clusters are resident at
+// once, so that every CTA streams from the start; never shorter than one tile per CTA
+// and never longer than the record buffer.
+int cluster_decode_split(int64_t m, int n_j, int n_k) {
+  const int nt = m <= 8 ? 1 : 2;
+  int split = 1;
+  for (int s = 2; s <= 8 && s <= n_k; ++s) {
+    if (max_active_clusters(nt, s) >= n_j) split = s;
+  }
   while (split < 8 && (n_k + split - 1) / split > kMaxCount) ++split;
   return split;
 }
@@ -351,7 +389,7 @@ int launch_cluster_decode(const LinearArgs& a, cudaStream_t stream) {
   p.n_k = a.n_k;
   p.scale_mode = a.scale_mode;
   p.out_dtype = a.out_dtype;
-  const int split = cluster_decode_split(a.n_j, a.n_k);
+  const int split = cluster_decode_split(a.m, a.n_j, a.n_k);
   return a.m <= 8 ? launch_nt<1>(p, split, stream) : launch_nt<2>(p, split, stream);
 }
 

@@ -78,7 +78,7 @@ int stream_auto_split(int64_t m, int n_j, int n_k);
 
 // Warp-per-tile cluster kernel for m <= 16 (the default decode kernel).
 int launch_cluster_decode(const LinearArgs& a, cudaStream_t stream);
-int cluster_decode_split(int n_j, int n_k);
+int cluster_decode_split(int64_t m, int n_j, int n_k);
 bool cluster_decode_supported(int n_j, int n_k);
 int take_cluster_decode_status();
 
