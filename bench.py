@@ -46,6 +46,9 @@ GROUPS = {
 }
 WORKLOAD = "llama-3.2-3b decode sweep: 28 layers x (qkv, o, gate_up, down), M in {1,4,8,16}, 60% W4, per-token A8"
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the packed-GEMV kernel, from the
+# ncu capture summarised in profiles/ (average over the four projection groups at M = 1).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
 
 
 def parse_args():
@@ -304,6 +307,11 @@ def run_native(args) -> None:
         step = lambda: sweep(True, True)  # noqa: E731
     with ClockSampler(local_rank) as clocks:
         seconds = timed(step, args.steps, max(args.warmup, 3))
+        # keep the same step running until nvidia-smi (100 ms period) has had time to sample it
+        sampling_deadline = time.perf_counter() + 1.0
+        while time.perf_counter() < sampling_deadline:
+            step()
+            torch.cuda.synchronize()
     ext.device_status(device)
 
     # ---- the packed-GEMV kernel alone (roofline of the dominant kernel)
@@ -359,9 +367,9 @@ def run_native(args) -> None:
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": 2 * pairs_per_step * args.steps,
         "roofline": {
-            "kernel": "stream_linear_kernel (packed W4/W8 GEMV, M<=16)", "bound": "hbm",
+            "kernel": "cluster_decode_kernel (packed W4/W8 GEMV, M<=16)", "bound": "hbm",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-            "peak_source": f"{peak_source} HBM copy bandwidth", "traffic": None,
+            "peak_source": f"{peak_source} HBM copy bandwidth", "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
             "bytes_per_launch": linear_bytes / pairs_per_step, "us_per_launch": kernel_seconds * 1e6,
         },
     }
