@@ -217,6 +217,40 @@ int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t
   return kernel == 2 ? launch_decode_linear(a, s) : launch_tmem_gemm(a, s);
 }
 
+int aq_linear_decode_static(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
+                            const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
+                            int out_dtype, void* out, void* stream) {
+  AQ_REQUIRE(xq != nullptr && act_scales != nullptr && prepared != nullptr && out != nullptr,
+             "xq, act_scales, prepared and out must not be NULL");
+  AQ_REQUIRE(m >= 1 && m <= kDecodeMaxRows, "aq_linear_decode_static handles 1 to %d rows, got %lld",
+             static_cast<int>(kDecodeMaxRows), static_cast<long long>(m));
+  AQ_REQUIRE(n_j > 0 && n_k > 0, "N and K must contain at least one 64-wide tile");
+  AQ_REQUIRE(scale_mode == AQ_SCALE_TILE || scale_mode == AQ_SCALE_TOKEN,
+             "scale_mode must be AQ_SCALE_TILE or AQ_SCALE_TOKEN, got %d", scale_mode);
+  AQ_REQUIRE(out_dtype == AQ_F32 || out_dtype == AQ_BF16 || out_dtype == AQ_F16,
+             "out_dtype must be AQ_F32, AQ_BF16 or AQ_F16");
+  AQ_REQUIRE(aligned(xq, 16) && aligned(out, 16), "x_int8 and out must be 16-byte aligned");
+  AQ_REQUIRE(aligned(prepared, 256), "prepared image must be 256-byte aligned");
+  AQ_REQUIRE(aligned(act_scales, 4) && aligned(u_metadata, 4), "act_scales and u_metadata must be 4-byte aligned");
+  const int64_t tiles = static_cast<int64_t>(n_j) * n_k;
+  LinearArgs a;
+  a.xq = xq;
+  a.act_scales = act_scales;
+  a.scale_mode = scale_mode;
+  a.m = m;
+  a.records = static_cast<const TileRecord*>(prepared);
+  a.payload = static_cast<const uint8_t*>(prepared) + records_bytes(tiles);
+  a.n_j = n_j;
+  a.n_k = n_k;
+  a.u_metadata = u_metadata;
+  a.out_dtype = out_dtype;
+  a.out = out;
+  a.acc_dump = nullptr;
+  a.workspace = nullptr;
+  a.workspace_bytes = 0;
+  return launch_decode_linear_static(a, static_cast<cudaStream_t>(stream));
+}
+
 int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int decode_splits, int32_t* kernel,
                    int32_t* splits, int32_t* workers) {
   AQ_REQUIRE(m >= 1 && n_j > 0 && n_k > 0 && schedule >= 0 && schedule <= 3, "aq_linear_plan: invalid problem");

@@ -87,6 +87,9 @@ int launch_decode_linear(const LinearArgs& a, cudaStream_t stream);
 int64_t decode_workspace_bytes(int64_t m, int n_j, int n_k);
 int decode_ctas(int n_j, int n_k);
 int take_decode_status();
+// Same kernel on the library's built-in scratch array (no caller workspace).
+int launch_decode_linear_static(const LinearArgs& a, cudaStream_t stream);
+int64_t decode_static_scratch_bytes();
 
 // Tensor-memory GEMM (tcgen05) for large m.
 int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream);

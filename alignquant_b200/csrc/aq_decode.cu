@@ -463,6 +463,54 @@ extern "C" __attribute__((visibility("default"))) int aq_debug_read_trace(long l
 }
 #endif
 
+// ---- allocation-free variant ------------------------------------------------------------
+// Scratch for callers that cannot hand over a workspace (see aq_linear_decode_static in
+// the header): arrival counters followed by partial tiles for up to kStaticMaxCtas
+// ranges of 16 rows.  Lives in every device context that loads the library.
+constexpr int kStaticMaxCtas = 256;
+constexpr int64_t kStaticScratchBytes = kCounterBytes + 2LL * kStaticMaxCtas * 16 * kTile * 4;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int64_t decode_static_scratch_bytes() { return kStaticScratchBytes; }
+
+int launch_decode_linear_static(const LinearArgs& args, cudaStream_t stream) {
+  // In host code `g_static_scratch` is only a handle for the symbol; the device address
+  // has to be looked up, once per device, with that device current.
+  static std::mutex mutex;
+  static void* device_address[64] = {nullptr};
+  int device = 0;
+  int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
+  if (rc != AQ_OK) return rc;
+  if (device < 0 || device >= 64) return fail(AQ_ERR_INVALID, "device index %d is not supported", device);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mutex);
+    if (device_address[device] == nullptr) {
+      void* address = nullptr;
+      rc = check_cuda(cudaGetSymbolAddress(&address, g_static_scratch), "cudaGetSymbolAddress(static scratch)");
+      if (rc != AQ_OK) return rc;
+      device_address[device] = address;
+    }
+    scratch = device_address[device];
+  }
+  const int64_t need = decode_workspace_bytes(args.m, args.n_j, args.n_k);
+  if (need > kStaticScratchBytes) {
+    return fail(AQ_ERR_WORKSPACE,
+                "this layer needs %lld bytes of scratch, the built-in scratch holds %lld; use aq_linear with a "
+                "caller-owned workspace",
+                static_cast<long long>(need), static_cast<long long>(kStaticScratchBytes));
+  }
+  // The array keeps whatever the previous call left behind; only the arrival counters of
+  // the rows this call touches have to start at zero.
+  rc = check_cuda(cudaMemsetAsync(scratch, 0, static_cast<size_t>(args.n_j) * sizeof(int32_t), stream),
+                  "cudaMemsetAsync(static scratch counters)");
+  if (rc != AQ_OK) return rc;
+  LinearArgs a = args;
+  a.workspace = scratch;
+  a.workspace_bytes = kStaticScratchBytes;
+  return launch_decode_linear(a, stream);
+}
+
 int take_decode_status() {
   int status = 0;
   if (cudaMemcpyFromSymbol(&status, g_decode_status, sizeof(int)) != cudaSuccess) return -1;

@@ -378,6 +378,54 @@ def device_status(device: torch.device | str | None = None) -> None:
         _lib.check(status)
 
 
+def alignquant_linear_decode_static(
+    activation: torch.Tensor,
+    activation_scales: torch.Tensor,
+    weights: PreparedWeights,
+    u_metadata: torch.Tensor | None,
+    *,
+    output_dtype: torch.dtype = torch.float32,
+    scale_mode: str = "tile",
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Decode projection (at most 16 rows) that needs no workspace from the caller.
+
+    For hosts that may only hand over inputs and outputs -- fixed-signature operator
+    plug-ins, runtimes that forbid device allocation once they are up -- the library
+    runs its stream-K decode kernel on a 2 MiB scratch array of its own
+    (``aq_linear_decode_static``).  Layers that need more scratch raise ``RuntimeError``.
+    All calls on a device share that array: calls whose kernels could overlap (different
+    streams) must be serialised by the caller.  The very first call on a device looks up
+    the array's address and should be made outside of a stream capture.  Only ``out`` is
+    allocated here (by torch) when the caller does not pass it.
+    """
+    if output_dtype not in _DTYPE_CODES:
+        raise ValueError("Projection output_dtype must be torch.float32, torch.bfloat16 or torch.float16.")
+    mode = _scale_mode_code(scale_mode)
+    x = activation.contiguous()
+    if x.dtype != torch.int8 or x.dim() != 2 or not x.is_cuda:
+        raise RuntimeError("x_int8 must be a CUDA int8 [M,K] tensor")
+    m = int(x.size(0))
+    n_j, n_k = weights.n_j, weights.n_k
+    if int(x.size(1)) != n_k * 64:
+        raise RuntimeError(f"K mismatch: activation has {int(x.size(1))}, weights have {n_k * 64}")
+    scales = activation_scales.contiguous()
+    if scales.dtype != torch.float32 or scales.numel() != (m if mode == _lib.AQ_SCALE_TOKEN else ((m + 15) // 16) * n_k):
+        raise RuntimeError("activation_scales has the wrong dtype or size for this scale_mode")
+    device = x.device
+    meta = None if u_metadata is None else u_metadata.contiguous()
+    with torch.cuda.device(device):
+        if out is None:
+            out = torch.empty((m, n_j * 64), dtype=output_dtype, device=device)
+        _lib.check(
+            _lib.load().aq_linear_decode_static(
+                _ptr(x), _ptr(scales), mode, m, _ptr(weights.image), n_j, n_k, _ptr(meta),
+                _DTYPE_CODES[output_dtype], _ptr(out), _stream(device),
+            )
+        )
+    return out
+
+
 def linear_plan(m: int, n_j: int, n_k: int, *, schedule: str = "auto", decode_splits: int = 0) -> dict[str, int]:
     """Kernel family, split count and accumulator count ``aq_linear`` will use.
 
@@ -403,6 +451,7 @@ __all__ = [
     "alignquant_activation_quantize_cuda",
     "alignquant_linear_cuda",
     "alignquant_linear_prepared",
+    "alignquant_linear_decode_static",
     "prepare_weights",
     "PreparedWeights",
     "device_status",

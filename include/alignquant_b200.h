@@ -143,6 +143,35 @@ AQ_API int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, 
               void* workspace, int64_t workspace_bytes, int32_t* acc_dump, void* stream);
 
 /*
+ * aq_linear for callers that have no way to supply a workspace.  (No counterpart in the
+ * reference, whose host function allocates its temporaries itself.)
+ *
+ * Some hosts of this library can pass in inputs and outputs but nothing else: operator
+ * plug-in interfaces whose call signature is fixed to the tensors of the layer, and
+ * serving runtimes that size their device memory once at start-up and refuse any
+ * allocation afterwards.  For them this entry point runs the persistent stream-K decode
+ * kernel (m <= 16) on a scratch array built into the library instead of a caller-owned
+ * workspace.  It never allocates: no cudaMalloc, no cudaFree, no allocating library call.
+ *
+ *   Limit: the built-in scratch is 2 162 688 bytes (64 KiB of row counters plus partial
+ *   tiles for 256 CTA ranges of 16 rows).  Layers that need more (aq_linear_workspace_bytes
+ *   with AQ_SCHEDULE_AUTO reports the need for layers that take this kernel) are rejected
+ *   with AQ_ERR_WORKSPACE; N is limited to 1 048 576.  Every device that loads the library
+ *   holds the array until the process exits.
+ *   First call on a device: looks up the array's device address (cudaGetSymbolAddress);
+ *   make that first call outside of any stream capture.
+ *   Sharing: all calls on a device use the same array, and it keeps what the last call
+ *   left in it.  Each call clears the row counters it needs on `stream` before the kernel
+ *   starts.  Two calls whose kernels may overlap on the GPU (different streams) race on
+ *   the array and produce wrong results; serialise them.
+ *   Arguments as for aq_linear; the summation order is that of kernel family 2 of
+ *   aq_linear_plan (ranges = number of CTAs of that kernel, 16 accumulators).
+ */
+AQ_API int aq_linear_decode_static(const int8_t* xq, const float* act_scales, int scale_mode,
+                                   int64_t m, const void* prepared, int32_t n_j, int32_t n_k,
+                                   const int32_t* u_metadata, int out_dtype, void* out, void* stream);
+
+/*
  * How aq_linear will run a problem on the current device, so that a caller can
  * reproduce the FP32 summation order (the integer tile sums never depend on it):
  *   *kernel  0  cluster kernel: K tiles cut into *splits ranges
