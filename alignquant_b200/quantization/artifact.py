@@ -191,6 +191,49 @@ def validate_w4w8_replacement_module(
     return states
 
 
+def shard_w4w8_replacement_module(
+    tensors: Mapping[str, torch.Tensor],
+    *,
+    n_j: int,
+    n_k: int,
+    rows: tuple[int, int] | None = None,
+    cols: tuple[int, int] | None = None,
+) -> dict[str, torch.Tensor]:
+    """The seven tensors of the sub-layer made of tile rows ``rows`` and tile columns ``cols``.
+
+    Tensor-parallel sharding happens on tile boundaries: a column-parallel projection keeps
+    a range of tile rows (output features), a row-parallel one a range of tile columns
+    (input features).  Precision bits, payloads and scales are per tile, so the shard is an
+    exact sub-selection -- nothing is re-quantized.  Arena order stays (j, k) row-major.
+    """
+    j0, j1 = rows if rows is not None else (0, int(n_j))
+    k0, k1 = cols if cols is not None else (0, int(n_k))
+    if not (0 <= j0 < j1 <= n_j and 0 <= k0 < k1 <= n_k):
+        raise ValueError(f"Invalid shard rows={rows} cols={cols} for a {n_j}x{n_k} tile grid.")
+    states = unpack_w4w8_state_bits(tensors["state_bits"].cpu(), n_j=n_j, n_k=n_k)
+    is4 = (states == P4).reshape(-1)
+    # arena index of every tile inside its own precision's arena
+    index4 = torch.cumsum(is4.to(torch.int64), 0) - 1
+    index8 = torch.cumsum((~is4).to(torch.int64), 0) - 1
+    keep = torch.zeros((n_j, n_k), dtype=torch.bool)
+    keep[j0:j1, k0:k1] = True
+    keep = keep.reshape(-1)
+    take4 = index4[keep & is4]
+    take8 = index8[keep & ~is4]
+    sub_states = states[j0:j1, k0:k1].contiguous()
+    zero = torch.zeros(1, dtype=torch.int64)
+    device = tensors["w4_payload"].device
+    return {
+        "state_bits": pack_w4w8_state_bits(sub_states).to(tensors["state_bits"].device),
+        "w4_payload": tensors["w4_payload"][take4.to(device)].contiguous(),
+        "w4_scales": tensors["w4_scales"][take4.to(device)].contiguous(),
+        "w8_payload": tensors["w8_payload"][take8.to(device)].contiguous(),
+        "w8_scales": tensors["w8_scales"][take8.to(device)].contiguous(),
+        "w4_row_offsets": torch.cat((zero, (sub_states == P4).sum(1).cumsum(0))).to(torch.int32).to(device),
+        "w8_row_offsets": torch.cat((zero, (sub_states == P8).sum(1).cumsum(0))).to(torch.int32).to(device),
+    }
+
+
 def _sha256_bytes(value: bytes) -> str:
     return hashlib.sha256(value).hexdigest()
 
@@ -264,6 +307,7 @@ __all__ = [
     "load_artifact",
     "pack_w4w8_replacement_module",
     "pack_w4w8_state_bits",
+    "shard_w4w8_replacement_module",
     "unpack_signed_int4",
     "unpack_w4w8_state_bits",
     "validate_w4w8_replacement_module",

@@ -1,0 +1,417 @@
+"""Install and execute a W4/W8-A8 replacement artifact on the B200 kernels.
+
+Same public surface as the reference's ``alignquant/quantization/model.py``
+(``install_alignquant``, ``AlignQuantLinear``, ``reset_alignquant_state``,
+``projection_groups``): q/k/v and gate/up projections of a decoder layer are fused into
+one launch over their concatenated output tiles (members in alphabetical order, as in
+the reference, model.py:27-46), the group output is computed once per activation and
+handed out as column slices.
+
+Differences, all behind keyword arguments with reference-compatible defaults:
+  * the concatenated arenas are re-laid-out once into the prepared image the kernels
+    stream (``prepare_weights``) and the raw arenas are dropped;
+  * rows are never padded -- the kernels accept any row count;
+  * ``scale_mode="token"`` selects per-row activation scales (only for identity V);
+  * ``tp_rank`` / ``tp_size`` / ``process_group`` install a tile-aligned tensor-parallel
+    shard: q/k/v/gate/up keep a range of tile rows per member (column parallel), o/down a
+    range of tile columns (row parallel) followed by an all-reduce of the partial output.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Mapping, Sequence
+from pathlib import Path
+from typing import Any
+
+import torch
+from torch import nn
+
+from alignquant_b200.kernels.cuda import extension as _ext
+from alignquant_b200.models.decoder import iter_target_linears
+from alignquant_b200.quantization.artifact import (
+    REPLACEMENT_TENSOR_NAMES,
+    load_artifact,
+    pack_w4w8_state_bits,
+    shard_w4w8_replacement_module,
+    unpack_w4w8_state_bits,
+)
+from alignquant_b200.quantization.exact import metadata_stack
+
+COLUMN_PARALLEL_SUFFIXES = (".q_proj", ".k_proj", ".v_proj", ".gate_proj", ".up_proj")
+ROW_PARALLEL_SUFFIXES = (".o_proj", ".down_proj")
+
+
+def projection_groups(module_names: Sequence[str]) -> dict[str, tuple[str, ...]]:
+    """Group q/k/v into ``<attn>.qkv`` and gate/up into ``<mlp>.gate_up``; others stay single."""
+    groups: dict[str, list[str]] = {}
+    for name in sorted({str(value) for value in module_names}):
+        parent, _, leaf = name.rpartition(".")
+        if parent.endswith(".self_attn") and leaf in ("q_proj", "k_proj", "v_proj"):
+            key = parent + ".qkv"
+        elif parent.endswith(".mlp") and leaf in ("gate_proj", "up_proj"):
+            key = parent + ".gate_up"
+        else:
+            key = name
+        groups.setdefault(key, []).append(name)
+    result = {key: tuple(values) for key, values in sorted(groups.items())}
+    for key, members in result.items():
+        expected = 3 if key.endswith(".qkv") else 2 if key.endswith(".gate_up") else 1
+        if len(members) != expected:
+            raise ValueError(f"Incomplete projection group {key}: {members}.")
+    return result
+
+
+def _cuda_device(value: torch.device | str) -> torch.device:
+    device = torch.device(value)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    if device.type != "cuda":
+        raise ValueError(f"Native W4/W8A8 runtime requires a CUDA device, got {device}.")
+    return device
+
+
+def _seed_list(raw: Any, *, count: int, name: str) -> tuple[int, ...]:
+    if not isinstance(raw, (list, tuple)) or len(raw) != int(count):
+        raise ValueError(f"R5 {name} must contain exactly {count} seeds.")
+    seeds = tuple(int(item) for item in raw)
+    if any(item < -1 for item in seeds):
+        raise ValueError(f"R5 {name} contains an invalid seed.")
+    return seeds
+
+
+def _validated_seeds(row: Mapping[str, Any], *, n_j: int, n_k: int) -> tuple[tuple[int, ...], tuple[int, ...]]:
+    """(V seeds, U seeds) of one manifest row; rejects anything but the frozen R5 runtime form."""
+    decision = row.get("r5")
+    if not isinstance(decision, Mapping) or str(decision.get("variant", "")) != "R5":
+        raise ValueError(f"{row.get('layer_name', '<unknown>')} is not a frozen R5 module.")
+    if int(decision.get("t_seed", -1)) != -1:
+        raise ValueError("Native W4/W8A8 R5 runtime rejects a non-identity T transform.")
+    if set(decision) != {"variant", "t_seed", "v_seeds", "u_seeds"}:
+        raise ValueError(
+            f"R5 artifact for {row.get('layer_name', '<unknown>')} contains unsupported "
+            "diagonal/factor payload or unknown fields."
+        )
+    return (
+        _seed_list(decision["v_seeds"], count=n_k, name="V"),
+        _seed_list(decision["u_seeds"], count=n_j, name="U"),
+    )
+
+
+def tensor_parallel_range(total: int, rank: int, size: int, what: str) -> tuple[int, int]:
+    """Tile range of shard ``rank`` of ``size`` over ``total`` tiles (must divide evenly)."""
+    if size < 1 or not 0 <= rank < size:
+        raise ValueError(f"Invalid tensor-parallel rank {rank} of {size}.")
+    if total % size:
+        raise ValueError(f"{what}: {total} tiles cannot be split evenly over {size} ranks.")
+    step = total // size
+    return rank * step, (rank + 1) * step
+
+
+class _PreparedGroupOutput:
+    __slots__ = ("key", "original_shape", "rows", "combined", "consumed_members")
+
+    def __init__(self, key, original_shape, rows, combined):
+        self.key = key
+        self.original_shape = original_shape
+        self.rows = rows
+        self.combined = combined
+        self.consumed_members: set[str] = set()
+
+
+class _ProjectionGroupRuntime:
+    """Owns and executes one fused QKV, gate/up or single projection group."""
+
+    def __init__(
+        self,
+        group_id: str,
+        members: Sequence[str],
+        rows: Mapping[str, Mapping[str, Any]],
+        tensors: Mapping[str, Mapping[str, torch.Tensor]],
+        device: torch.device,
+        *,
+        reuse_activation: bool = True,
+        scale_mode: str = "tile",
+        tp_rank: int = 0,
+        tp_size: int = 1,
+    ) -> None:
+        self.group_id = str(group_id)
+        self.members = tuple(str(item) for item in members)
+        if not self.members or len(set(self.members)) != len(self.members):
+            raise ValueError(f"Projection group {self.group_id} has empty or duplicate members.")
+        if set(rows) != set(self.members) or set(tensors) != set(self.members):
+            raise ValueError(f"Projection group {self.group_id} has incomplete member artifacts.")
+        self.device = torch.device(device)
+        self.reuse_activation = bool(reuse_activation)
+        self.scale_mode = str(scale_mode)
+        self.member_slices: dict[str, tuple[int, int]] = {}
+        self.row_parallel = tp_size > 1 and self.members[0].endswith(ROW_PARALLEL_SUFFIXES)
+
+        state_rows, u_seeds = [], []
+        arenas = {"w4_payload": [], "w4_scales": [], "w8_payload": [], "w8_scales": []}
+        offsets = {"w4": [0], "w8": [0]}
+        v_seeds: tuple[int, ...] | None = None
+        n_k: int | None = None
+        column = 0
+        for member in self.members:
+            row, member_tensors = rows[member], dict(tensors[member])
+            if set(member_tensors) != set(REPLACEMENT_TENSOR_NAMES):
+                raise ValueError(f"Unexpected replacement tensors for {member}.")
+            m_nj, m_nk = int(row["n_j"]), int(row["n_k"])
+            if m_nj <= 0 or m_nk <= 0:
+                raise ValueError(f"Invalid tile geometry for {member}.")
+            m_v, m_u = _validated_seeds(row, n_j=m_nj, n_k=m_nk)
+            if tp_size > 1:
+                if member.endswith(COLUMN_PARALLEL_SUFFIXES):
+                    j0, j1 = tensor_parallel_range(m_nj, tp_rank, tp_size, member)
+                    member_tensors = shard_w4w8_replacement_module(member_tensors, n_j=m_nj, n_k=m_nk, rows=(j0, j1))
+                    m_u, m_nj = m_u[j0:j1], j1 - j0
+                elif member.endswith(ROW_PARALLEL_SUFFIXES):
+                    k0, k1 = tensor_parallel_range(m_nk, tp_rank, tp_size, member)
+                    member_tensors = shard_w4w8_replacement_module(member_tensors, n_j=m_nj, n_k=m_nk, cols=(k0, k1))
+                    m_v, m_nk = m_v[k0:k1], k1 - k0
+                else:
+                    raise ValueError(f"{member} has no tensor-parallel sharding rule.")
+            if n_k is None:
+                n_k, v_seeds = m_nk, m_v
+            elif m_nk != n_k or m_v != v_seeds:
+                raise ValueError(f"Projection group {self.group_id} does not share K geometry and V seeds.")
+            state_rows.append(unpack_w4w8_state_bits(member_tensors["state_bits"].cpu(), n_j=m_nj, n_k=m_nk))
+            for prefix in ("w4", "w8"):
+                payload = member_tensors[f"{prefix}_payload"].detach()
+                scale = member_tensors[f"{prefix}_scales"].detach()
+                prefix_offsets = member_tensors[f"{prefix}_row_offsets"].detach().cpu().to(torch.int64).view(-1)
+                if (
+                    int(prefix_offsets.numel()) != m_nj + 1
+                    or int(prefix_offsets[0]) != 0
+                    or bool((prefix_offsets[1:] < prefix_offsets[:-1]).any())
+                    or int(prefix_offsets[-1]) != int(payload.shape[0])
+                    or int(scale.numel()) != int(payload.shape[0])
+                ):
+                    raise ValueError(f"Malformed {prefix.upper()} arena or offsets for {member}.")
+                base = offsets[prefix][-1]
+                offsets[prefix].extend(base + int(value) for value in prefix_offsets[1:])
+                arenas[f"{prefix}_payload"].append(payload)
+                arenas[f"{prefix}_scales"].append(scale)
+            u_seeds.extend(m_u)
+            self.member_slices[member] = (column, column + m_nj * 64)
+            column += m_nj * 64
+
+        assert n_k is not None and v_seeds is not None
+        self.n_k = n_k
+        self.v_seeds = v_seeds
+        self.out_features = column
+        if self.scale_mode == "token" and any(seed != -1 for seed in v_seeds):
+            raise ValueError(f"{self.group_id}: per-token activation scales need identity V transforms.")
+        to_device = lambda t: t.to(device=self.device).contiguous()  # noqa: E731
+        raw = {
+            "state_bits": to_device(pack_w4w8_state_bits(torch.cat(state_rows, dim=0))),
+            "w4_payload": to_device(torch.cat(arenas["w4_payload"], dim=0)),
+            "w4_scales": to_device(torch.cat(arenas["w4_scales"], dim=0)),
+            "w8_payload": to_device(torch.cat(arenas["w8_payload"], dim=0)),
+            "w8_scales": to_device(torch.cat(arenas["w8_scales"], dim=0)),
+            "w4_row_offsets": to_device(torch.tensor(offsets["w4"], dtype=torch.int32)),
+            "w8_row_offsets": to_device(torch.tensor(offsets["w8"], dtype=torch.int32)),
+        }
+        # one-time re-layout; the raw arenas are not kept
+        self.weights = _ext.prepare_weights(*(raw[name] for name in REPLACEMENT_TENSOR_NAMES), n_k=n_k)
+        del raw
+        identity_v = all(seed == -1 for seed in v_seeds)
+        self.v_metadata = None if identity_v else metadata_stack(v_seeds, self.device)
+        self.u_metadata = None if all(seed == -1 for seed in u_seeds) else metadata_stack(u_seeds, self.device)
+        self._prepared: _PreparedGroupOutput | None = None
+
+    @staticmethod
+    def _activation_key(activation: torch.Tensor) -> tuple[Any, ...]:
+        return (
+            activation.device.type, activation.device.index, activation.data_ptr(),
+            int(activation.storage_offset()), tuple(int(v) for v in activation.shape),
+            tuple(int(v) for v in activation.stride()), str(activation.dtype),
+        )
+
+    def project_member(self, activation: torch.Tensor, *, member: str) -> tuple[torch.Tensor, tuple[int, ...]]:
+        """Slice of the group's output that belongs to ``member``, computing the group once."""
+        name = str(member)
+        if name not in self.members:
+            raise ValueError(f"{name} is not a member of projection group {self.group_id}.")
+        key = self._activation_key(activation)
+        if not self.reuse_activation:
+            self._prepared = None
+        if self._prepared is not None:
+            if self._prepared.key != key:
+                missing = sorted(set(self.members) - self._prepared.consumed_members)
+                raise RuntimeError(
+                    f"Projection group {self.group_id} received a new activation before "
+                    f"members {missing} consumed the prior combined output."
+                )
+            if name in self._prepared.consumed_members:
+                raise RuntimeError(
+                    f"Projection group {self.group_id} member {name} was called twice for the same activation."
+                )
+            prepared = self._prepared
+        else:
+            if activation.device != self.device:
+                raise ValueError(f"Projection group {self.group_id} is on {self.device}, got {activation.device}.")
+            if activation.dim() < 1:
+                raise ValueError(f"Native W4/W8A8 linear expects [...,K], got {tuple(activation.shape)}.")
+            original_shape = tuple(int(v) for v in activation.shape)
+            width = original_shape[-1]
+            if width != self.n_k * 64:
+                raise ValueError(f"Activation K mismatch for {self.group_id}: {width} vs {self.n_k * 64}.")
+            rows = int(activation.numel()) // width
+            if rows <= 0:
+                raise ValueError("Activation must contain at least one row.")
+            flat = activation.reshape(rows, width)
+            qx, scales = _ext.alignquant_activation_quantize_cuda(flat, self.v_metadata, scale_mode=self.scale_mode)
+            out_dtype = activation.dtype if activation.dtype in (torch.bfloat16, torch.float16) and not self.row_parallel else torch.float32
+            combined = _ext.alignquant_linear_prepared(
+                qx, scales, self.weights, self.u_metadata, scale_mode=self.scale_mode, output_dtype=out_dtype
+            )
+            if tuple(combined.shape) != (rows, self.out_features):
+                raise RuntimeError(
+                    f"Projection group {self.group_id} returned {tuple(combined.shape)}, "
+                    f"expected {(rows, self.out_features)}."
+                )
+            prepared = _PreparedGroupOutput(key, original_shape, rows, combined)
+            self._prepared = prepared
+        start, stop = self.member_slices[name]
+        result = prepared.combined[:, start:stop]
+        prepared.consumed_members.add(name)
+        if not self.reuse_activation or prepared.consumed_members == set(self.members):
+            self._prepared = None
+        return result, prepared.original_shape
+
+    def reset_pending(self) -> None:
+        """Discard an incomplete shared projection after an aborted forward."""
+        self._prepared = None
+
+
+class AlignQuantLinear(nn.Module):
+    """A frozen artifact-backed linear running on the native W4/W8A8 kernels."""
+
+    def __init__(self, linear: nn.Linear, *, layer_name: str, runtime: _ProjectionGroupRuntime,
+                 process_group: Any = None) -> None:
+        super().__init__()
+        self.layer_name = str(layer_name)
+        object.__setattr__(self, "runtime", runtime)
+        object.__setattr__(self, "process_group", process_group)
+        self.in_features = int(linear.in_features)
+        self.out_features = int(linear.out_features)
+        start, stop = runtime.member_slices[self.layer_name]
+        if self.in_features != runtime.n_k * 64 or self.out_features != stop - start:
+            raise ValueError(f"Linear geometry disagrees with projection group for {self.layer_name}.")
+        bias = None if linear.bias is None else linear.bias.detach().to(device=runtime.device).contiguous()
+        self.register_buffer("bias", bias, persistent=False)
+
+    def forward(self, activation: torch.Tensor) -> torch.Tensor:
+        result, original_shape = self.runtime.project_member(activation, member=self.layer_name)
+        if self.runtime.row_parallel:
+            import torch.distributed as dist
+
+            result = result.contiguous()
+            dist.all_reduce(result, group=self.process_group)  # sum of the K-shard partials
+        if self.bias is not None:
+            result = result + self.bias.to(dtype=result.dtype)
+        result = result.reshape(*original_shape[:-1], self.out_features)
+        return result.to(dtype=activation.dtype)
+
+
+def install_alignquant(
+    model: nn.Module,
+    artifact: Mapping[str, Any] | str | Path,
+    device: torch.device | str | None,
+    *,
+    reuse_activation: bool = True,
+    scale_mode: str = "tile",
+    tp_rank: int = 0,
+    tp_size: int = 1,
+    process_group: Any = None,
+) -> tuple[list[AlignQuantLinear], dict[str, Any]]:
+    """Replace exactly the artifact-covered decoder projections of ``model``.
+
+    With ``tp_size > 1`` the model's linears must already have the per-rank shapes
+    (output features / tp for q, k, v, gate, up; input features / tp for o, down) while the
+    artifact holds the full layers; each rank keeps its tile-aligned shard.
+    Returns the installed modules and a metadata dict, like the reference
+    (alignquant/quantization/model.py:419-539).
+    """
+    target_device = None if device is None else _cuda_device(device)
+    loaded = artifact if isinstance(artifact, Mapping) else load_artifact(artifact, device="cpu")
+    if set(loaded) != {"root", "manifest", "modules"}:
+        raise ValueError("Replacement artifact must contain root, manifest, and modules.")
+    manifest, module_tensors = loaded["manifest"], loaded["modules"]
+    if not isinstance(manifest, Mapping) or not isinstance(module_tensors, Mapping):
+        raise TypeError("Replacement artifact manifest and modules must be mappings.")
+    manifest_rows = list(manifest.get("modules", ()))
+    if not manifest_rows:
+        raise ValueError("Replacement artifact must contain at least one module.")
+    row_map: dict[str, Mapping[str, Any]] = {}
+    for row in manifest_rows:
+        name = str(row.get("layer_name", ""))
+        if not name or name in row_map:
+            raise ValueError(f"Duplicate or empty artifact module name: {name!r}.")
+        row_map[name] = row
+    targets = iter_target_linears(model)
+    if not targets:
+        raise ValueError("Model has no target linear projections.")
+    target_names = {name for _, _, name, _ in targets}
+    if len(target_names) != len(targets) or target_names != set(row_map):
+        raise ValueError(
+            "Artifact/model target coverage mismatch: "
+            f"model={len(targets)} artifact={len(row_map)} "
+            f"missing={sorted(target_names - set(row_map))[:3]} "
+            f"extra={sorted(set(row_map) - target_names)[:3]}"
+        )
+    if set(module_tensors) != set(row_map):
+        raise ValueError("Loaded replacement tensor coverage differs from manifest coverage.")
+
+    records: dict[str, tuple[nn.Module, str, torch.device]] = {}
+    for parent, attr, name, linear in targets:
+        full = tuple(int(v) for v in row_map[name].get("shape", ()))
+        local = (int(linear.out_features), int(linear.in_features))
+        expected = full
+        if tp_size > 1 and len(full) == 2:
+            expected = (full[0] // tp_size, full[1]) if name.endswith(COLUMN_PARALLEL_SUFFIXES) else (full[0], full[1] // tp_size)
+        if local != expected:
+            raise ValueError(f"Artifact shape mismatch for {name}: {list(full)} (tp {tp_size}) vs {local}.")
+        if int(row_map[name]["n_j"]) != full[0] // 64 or int(row_map[name]["n_k"]) != full[1] // 64:
+            raise ValueError(f"Artifact tile geometry mismatch for {name}.")
+        records[name] = (parent, attr, target_device if target_device is not None else _cuda_device(linear.weight.device))
+    del targets
+
+    groups = projection_groups(tuple(sorted(records)))
+    runtimes: dict[str, _ProjectionGroupRuntime] = {}
+    installed: list[AlignQuantLinear] = []
+    for group_id, members in groups.items():
+        devices = {records[m][2] for m in members}
+        if len(devices) != 1:
+            raise ValueError(f"Projection group {group_id} spans CUDA devices: {devices}.")
+        runtime = _ProjectionGroupRuntime(
+            group_id, members, {m: row_map[m] for m in members}, {m: module_tensors[m] for m in members},
+            next(iter(devices)), reuse_activation=reuse_activation, scale_mode=scale_mode,
+            tp_rank=tp_rank, tp_size=tp_size,
+        )
+        runtimes[group_id] = runtime
+        for name in members:
+            parent, attr, _ = records.pop(name)
+            module = AlignQuantLinear(getattr(parent, attr), layer_name=name, runtime=runtime, process_group=process_group)
+            setattr(parent, attr, module)
+            installed.append(module)
+    model._alignquant_projection_groups = tuple(runtimes.values())
+    metadata = {
+        "module_count": len(installed),
+        "projection_group_count": len(runtimes),
+        "groups": {group: list(members) for group, members in groups.items()},
+        "reuse_activation": bool(reuse_activation),
+        "scale_mode": str(scale_mode),
+        "tensor_parallel": {"rank": int(tp_rank), "size": int(tp_size)},
+    }
+    return installed, metadata
+
+
+def reset_alignquant_state(model: nn.Module) -> None:
+    """Reset transient shared-projection state between independent forwards."""
+    for runtime in getattr(model, "_alignquant_projection_groups", ()):
+        runtime.reset_pending()
+
+
+__all__ = ["AlignQuantLinear", "install_alignquant", "projection_groups", "reset_alignquant_state"]
