@@ -48,7 +48,7 @@ WORKLOAD = "llama-3.2-3b decode sweep: 28 layers x (qkv, o, gate_up, down), M in
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the packed-GEMV kernel, from the
 # ncu capture summarised in profiles/ (average over the four projection groups at M = 1).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 17.72e6  # (11.077 + 6.65 + 35.367 + 17.77) MB / 4; o and down scaled from their byte counts
 
 
 def parse_args():
