@@ -125,6 +125,27 @@ __device__ __forceinline__ uint32_t instr_desc_i8(int n) {
          (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
+// acc[32*C .. 32*C+31] += float(v) * scale, multiply and add rounded separately
+template <int C>
+__device__ __forceinline__ void drain_chunk(float (&acc)[128], const int (&v)[32], float scale) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    acc[C * 32 + i] = __fadd_rn(acc[C * 32 + i], __fmul_rn(static_cast<float>(v[i]), scale));
+  }
+}
+
+// Debug aid: the exact integer tile sums (W4 tiles were fed 16*w to the MMA).
+__device__ __forceinline__ void dump_chunk(int32_t* tile_dump, int first_col, const int (&v)[32], const TileRecord& r) {
+  if (tile_dump == nullptr) return;
+  const int shift = (r.offset_flag & kW4Flag) ? 4 : 0;
+  int4* o = reinterpret_cast<int4*>(tile_dump + first_col);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    o[i] = make_int4(v[4 * i] >> shift, v[4 * i + 1] >> shift, v[4 * i + 2] >> shift, v[4 * i + 3] >> shift);
+  }
+}
+
+template <bool kDump>
 __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* stages = smem;
@@ -183,7 +204,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp == 0) {
       // ---------------- producer: weights (bulk copies) + activations (cp.async) --
       int issued = 0;
@@ -311,7 +332,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
       }
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
     // ---------------- drain: int32 accumulator -> scaled FP32 registers -------------
     const int quarter = warp & 3;       // tensor-memory lane quarter this warp may read
     const int half = (warp - 4) >> 2;   // column half: weight tile rows 2*half, 2*half+1
@@ -325,50 +346,59 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
     for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
     const float token_scale =
         (p.scale_mode == AQ_SCALE_TOKEN && row_valid) ? p.act_scales[grow] : 0.0f;
-    bool ok = true;
-    for (int kt = 0; kt < n_k; ++kt) {
-      const int b = kt & 1;
-      const uint32_t pha = (kt >> 1) & 1;
-      if (!mbar_wait(acc_full(b), pha, abort_flag, &g_gemm_status, 7)) {
-        ok = false;
-        break;
-      }
+    const float* tile_scales =
+        (p.scale_mode == AQ_SCALE_TILE && row_valid) ? p.act_scales + (grow >> 4) * n_k : nullptr;
+    const TileRecord* rec_lo = rec_smem + (2 * half) * kMaxNk;
+    const TileRecord* rec_hi = rec_lo + kMaxNk;
+
+    // Software pipeline over 32-column chunks (two per weight tile, four per K step) with two
+    // register buffers: while the FP32 work of one chunk runs, the tensor-memory load of the
+    // next one is in flight; the accumulator is handed back to the MMA thread as soon as its
+    // last chunk has been loaded, before that chunk's arithmetic.
+    int va[32], vb[32];
+    bool ok = mbar_wait(acc_full(0), 0, abort_flag, &g_gemm_status, 7);
+    if (ok) {
       tc_fence_after();
-      float a_scale = token_scale;
-      if (p.scale_mode == AQ_SCALE_TILE) {
-        a_scale = row_valid ? p.act_scales[(grow >> 4) * n_k + kt] : 0.0f;
+      tc_ld32(taddr, va);
+    }
+    for (int kt = 0; kt < n_k && ok; ++kt) {
+      const int b = kt & 1;
+      const uint32_t col = static_cast<uint32_t>(b * 256);
+      const float a_scale = tile_scales != nullptr ? tile_scales[kt] : token_scale;
+      const TileRecord r0 = rec_lo[kt];
+      const TileRecord r1 = rec_hi[kt];
+      const float s0 = __fmul_rn(a_scale, r0.scale);
+      const float s1 = __fmul_rn(a_scale, r1.scale);
+      int32_t* dump0 = nullptr;
+      int32_t* dump1 = nullptr;
+      if (kDump && row_valid) {
+        if (2 * half < tiles_here) dump0 = p.acc_dump + ((grow * p.n_j + (j0 + 2 * half)) * n_k + kt) * kTile;
+        if (2 * half + 1 < tiles_here) dump1 = p.acc_dump + ((grow * p.n_j + (j0 + 2 * half + 1)) * n_k + kt) * kTile;
       }
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        const int tl = 2 * half + t;
-        if (tl < tiles_here) {
-          const TileRecord rec = rec_smem[tl * kMaxNk + kt];
-          const float scale = __fmul_rn(a_scale, rec.scale);
-          const int shift = (rec.offset_flag & kW4Flag) ? 4 : 0;
-#pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            int v[32];
-            tc_ld32(taddr + static_cast<uint32_t>(b * 256 + t * 64 + q * 32), v);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              acc[t * 64 + q * 32 + i] =
-                  __fadd_rn(acc[t * 64 + q * 32 + i], __fmul_rn(static_cast<float>(v[i]), scale));
-            }
-            if (p.acc_dump != nullptr && row_valid) {
-              int4* o = reinterpret_cast<int4*>(
-                  p.acc_dump + ((grow * p.n_j + (j0 + tl)) * n_k + kt) * kTile + q * 32);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                o[i] = make_int4(v[4 * i] >> shift, v[4 * i + 1] >> shift, v[4 * i + 2] >> shift,
-                                 v[4 * i + 3] >> shift);
-              }
-            }
-          }
-        }
-      }
+      tc_wait_ld();  // chunk 0 in va
+      tc_ld32(taddr + col + 32, vb);
+      drain_chunk<0>(acc, va, s0);
+      if (kDump) dump_chunk(dump0, 0, va, r0);
+      tc_wait_ld();  // chunk 1 in vb
+      tc_ld32(taddr + col + 64, va);
+      drain_chunk<1>(acc, vb, s0);
+      if (kDump) dump_chunk(dump0, 32, vb, r0);
+      tc_wait_ld();  // chunk 2 in va
+      tc_ld32(taddr + col + 96, vb);
+      drain_chunk<2>(acc, va, s1);
+      if (kDump) dump_chunk(dump1, 0, va, r1);
+      tc_wait_ld();  // chunk 3 in vb: this accumulator has been read completely
       tc_fence_before();
       mbar_arrive(acc_empty(b));
+      if (kt + 1 < n_k) {
+        ok = mbar_wait(acc_full(b ^ 1), ((kt + 1) >> 1) & 1, abort_flag, &g_gemm_status, 7);
+        if (ok) {
+          tc_fence_after();
+          tc_ld32(taddr + static_cast<uint32_t>((b ^ 1) * 256), va);
+        }
+      }
+      drain_chunk<3>(acc, vb, s1);
+      if (kDump) dump_chunk(dump1, 32, vb, r1);
     }
 
     // ---------------- epilogue: rows through shared memory, coalesced stores --------
@@ -427,8 +457,12 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   if (rc != AQ_OK) return rc;
   cudaError_t attr_status = cudaSuccess;
   std::call_once(g_attr_once[device & 63], [&] {
-    attr_status = cudaFuncSetAttribute(tmem_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_status = cudaFuncSetAttribute(tmem_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kSmemBytes);
+    if (attr_status == cudaSuccess) {
+      attr_status = cudaFuncSetAttribute(tmem_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes);
+    }
   });
   rc = check_cuda(attr_status, "cudaFuncSetAttribute(tmem_gemm_kernel)");
   if (rc != AQ_OK) return rc;
@@ -447,7 +481,11 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   p.out_dtype = a.out_dtype;
   const dim3 grid(static_cast<unsigned>((a.n_j + kTilesN - 1) / kTilesN),
                   static_cast<unsigned>((a.m + kBM - 1) / kBM));
-  tmem_gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(p);
+  if (a.acc_dump != nullptr) {
+    tmem_gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  } else {
+    tmem_gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(p);
+  }
   return check_cuda(cudaGetLastError(), "tensor-memory GEMM launch");
 }
 
