@@ -1,0 +1,149 @@
+"""End-to-end generation runs with random-init decoder models and synthetic artifacts.
+
+    python -m alignquant_b200.runner --model qwen3-4b --batch 8 --prompt-len 2048 --new-tokens 128
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
+        -m alignquant_b200.runner --model qwen3-14b --batch 32 --prompt-len 1024 --new-tokens 256
+
+The model is built from a Hugging Face config with the named shape (no checkpoint, no
+tokenizer: random weights, random token ids), every decoder projection is replaced by
+the packed W4/W8-A8 format with a seeded 60 % W4 map, and greedy decoding is timed with
+CUDA events: prefill tokens/s over the prompt pass, decode tokens/s over the generated
+tokens.  Under ``torch.distributed.run`` the decoder is built per rank with 1/tp of the
+heads and of the MLP width (tile-aligned tensor parallelism, all-reduce after o_proj and
+down_proj); embeddings, norms and the LM head are replicated.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+SHAPES = {
+    # name: hidden, intermediate, layers, q heads, kv heads, head dim, vocab, family
+    "llama-3.2-3b": (3072, 8192, 28, 24, 8, 128, 128256, "llama"),
+    "qwen3-4b": (2560, 9728, 36, 32, 8, 128, 151936, "qwen3"),
+    "qwen3-14b": (5120, 17408, 40, 40, 8, 128, 151936, "qwen3"),
+    "tiny": (256, 512, 2, 4, 2, 64, 1024, "qwen3"),
+}
+
+
+def build_model(name: str, tp: int, device: torch.device, layers: int | None = None):
+    """Random-init decoder of the named shape with 1/tp of the heads and MLP width."""
+    import transformers
+
+    hidden, inter, n_layers, heads, kv_heads, head_dim, vocab, family = SHAPES[name]
+    if heads % tp or kv_heads % tp or (inter // 64) % tp:
+        raise ValueError(f"{name} cannot be split over {tp} ranks on tile boundaries")
+    common = dict(
+        hidden_size=hidden, intermediate_size=inter // tp, num_hidden_layers=layers or n_layers,
+        num_attention_heads=heads // tp, num_key_value_heads=kv_heads // tp, head_dim=head_dim,
+        vocab_size=vocab, max_position_embeddings=8192, tie_word_embeddings=False,
+    )
+    config = (transformers.LlamaConfig if family == "llama" else transformers.Qwen3Config)(**common)
+    config._attn_implementation = "sdpa"
+    torch.manual_seed(1234)  # same embeddings / norms / head on every rank
+    with torch.device(device):
+        model = transformers.AutoModelForCausalLM.from_config(config, torch_dtype=torch.bfloat16)
+    return model.eval()
+
+
+def synthetic_artifact(model, name: str, tp: int, seed: int, device: torch.device) -> dict:
+    """Artifact mapping (manifest rows + packed tensors) with the FULL layer shapes."""
+    from alignquant_b200.models.decoder import iter_target_linears
+    from alignquant_b200.quantization.model import COLUMN_PARALLEL_SUFFIXES
+    from alignquant_b200.synthetic import synthetic_module_tensors
+
+    rows, modules = [], {}
+    for index, (_, _, full_name, linear) in enumerate(iter_target_linears(model)):
+        n, k = int(linear.out_features), int(linear.in_features)
+        if full_name.endswith(COLUMN_PARALLEL_SUFFIXES):
+            n *= tp
+        else:
+            k *= tp
+        modules[full_name] = synthetic_module_tensors(n, k, seed=seed * 100003 + index, device=device)
+        rows.append({
+            "layer_name": full_name, "shape": [n, k], "n_j": n // 64, "n_k": k // 64,
+            "r5": {"variant": "R5", "t_seed": -1, "v_seeds": [-1] * (k // 64), "u_seeds": [-1] * (n // 64)},
+        })
+    return {"root": None, "manifest": {"modules": rows}, "modules": modules}
+
+
+def run(args) -> dict:
+    import torch.distributed as dist
+
+    from alignquant_b200.kernels.cuda import extension as ext
+    from alignquant_b200.quantization.model import install_alignquant, reset_alignquant_state
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    ext.load_extension()
+    model = build_model(args.model, world, device, layers=args.layers)
+    artifact = synthetic_artifact(model, args.model, world, seed=7, device=device)
+    installed, _ = install_alignquant(model, artifact, device, scale_mode=args.scale_mode, tp_rank=rank, tp_size=world)
+    del artifact
+    torch.cuda.empty_cache()
+
+    gen = torch.Generator(device=device).manual_seed(99)
+    vocab = SHAPES[args.model][6]
+    prompt = torch.randint(0, vocab, (args.batch, args.prompt_len), generator=gen, device=device)
+
+    def generate():
+        reset_alignquant_state(model)
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        with torch.inference_mode():
+            events[0].record()
+            out = model(input_ids=prompt, use_cache=True)
+            token = out.logits[:, -1].argmax(dim=-1, keepdim=True)
+            events[1].record()
+            cache = out.past_key_values
+            for _ in range(args.new_tokens - 1):
+                out = model(input_ids=token, past_key_values=cache, use_cache=True)
+                cache = out.past_key_values
+                token = out.logits[:, -1].argmax(dim=-1, keepdim=True)
+            events[2].record()
+        torch.cuda.synchronize()
+        return events[0].elapsed_time(events[1]) / 1e3, events[1].elapsed_time(events[2]) / 1e3
+
+    if args.warmup:
+        generate()
+    prefill_s, decode_s = generate()
+    ext.device_status(device)
+    if world > 1:
+        t = torch.tensor([prefill_s, decode_s], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        prefill_s, decode_s = (float(v) for v in t)
+        dist.destroy_process_group()
+    return {
+        "model": args.model, "layers": args.layers or SHAPES[args.model][2], "tp": world, "batch": args.batch,
+        "prompt_len": args.prompt_len, "new_tokens": args.new_tokens, "scale_mode": args.scale_mode,
+        "quantized_modules": len(installed),
+        "prefill_tokens_per_s": args.batch * args.prompt_len / prefill_s,
+        "decode_tokens_per_s": args.batch * (args.new_tokens - 1) / decode_s,
+        "prefill_s": prefill_s, "decode_s": decode_s, "rank": rank,
+    }
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--model", choices=sorted(SHAPES), default="qwen3-4b")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--new-tokens", type=int, default=128)
+    ap.add_argument("--layers", type=int, default=None, help="override the number of decoder layers")
+    ap.add_argument("--scale-mode", choices=("tile", "token"), default="token")
+    ap.add_argument("--warmup", type=int, default=1)
+    result = run(ap.parse_args())
+    if result["rank"] == 0:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()
