@@ -31,7 +31,7 @@ def main() -> None:
     tokenizer = AutoTokenizer.from_pretrained(args.model, revision=model_info.get("revision"), trust_remote_code=False)
     loader = getattr(transformers, model_info.get("loader", "AutoModelForCausalLM"))
     model = loader.from_pretrained(
-        args.model, revision=model_info.get("revision"), torch_dtype=torch.bfloat16,
+        args.model, revision=model_info.get("revision"), dtype=torch.bfloat16,
         attn_implementation="sdpa", trust_remote_code=False,
     ).to("cuda").eval()
     install_alignquant(model, args.artifact, "cuda")

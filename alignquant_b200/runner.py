@@ -46,7 +46,7 @@ def build_model(name: str, tp: int, device: torch.device, layers: int | None = N
     config._attn_implementation = "sdpa"
     torch.manual_seed(1234)  # same embeddings / norms / head on every rank
     with torch.device(device):
-        model = transformers.AutoModelForCausalLM.from_config(config, torch_dtype=torch.bfloat16)
+        model = transformers.AutoModelForCausalLM.from_config(config, dtype=torch.bfloat16)
     return model.eval()
 
 
