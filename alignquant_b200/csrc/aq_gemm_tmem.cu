@@ -12,10 +12,13 @@
 //     the operand layout and publish them to the asynchronous proxy;
 //   * one thread issues tcgen05.mma kind::i8 (M=128, N<=256, K=32, twice per step)
 //     into one of two 256-column tensor-memory accumulators and commits to mbarriers;
-//   * eight drain warps read the int32 accumulator with tcgen05.ld, convert to FP32,
+//   * eight drain warps read the int32 accumulator with tcgen05.ld, turn it into FP32,
 //     scale by (activation scale * tile scale) and add into FP32 registers -- integer
 //     accumulation never spans two K64 tiles because every tile has its own scale
-//     (operation order of alignquant/kernels/cuda/linear.cu:951-963).
+//     (operation order of alignquant/kernels/cuda/linear.cu:951-963).  The accumulators
+//     are preset (tcgen05.st) to the bit pattern of 1.5 * 2^23, so the int32 result read
+//     as a float is exactly 1.5 * 2^23 + sum and one exact FP32 subtraction stands in
+//     for the much slower integer-to-float conversion.
 // The epilogue stages rows through shared memory so that global stores are coalesced
 // and applies the inverse output transform (linear.cu:983-1040) where a tile has one.
 //
@@ -105,7 +108,34 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, int (&v)[32]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, int (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Store one 32-bit value into 16 consecutive columns of this warp's 32 tensor-memory lanes.
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+      "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+
+// The int32 accumulators start every K step at kBiasBits instead of zero.  Read back as
+// an IEEE float, kBiasBits + d is exactly kBiasFloat + d for |d| < 2^22 (tile sums stay
+// below 2^21 in magnitude, 16x-scaled W4 sums included), so one exact FP32 subtraction
+// replaces the integer-to-float conversion, which runs at a quarter of the FP32 rate.
+constexpr uint32_t kBiasBits = 0x4B400000u;  // 12582912.0f = 1.5 * 2^23
+constexpr float kBiasFloat = 12582912.0f;
 
 // K-major shared-memory operand descriptor.  Without swizzle the operand is made of
 // 8-row x 16-byte core matrices: LBO = byte step between the two 16-byte K chunks of one
@@ -125,23 +155,27 @@ __device__ __forceinline__ uint32_t instr_desc_i8(int n) {
          (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
-// acc[32*C .. 32*C+31] += float(v) * scale, multiply and add rounded separately
+// acc[16*C .. 16*C+15] += float(d) * scale with d = v - kBiasBits; the subtraction is exact,
+// multiply and add are rounded separately
 template <int C>
-__device__ __forceinline__ void drain_chunk(float (&acc)[128], const int (&v)[32], float scale) {
+__device__ __forceinline__ void drain_chunk(float (&acc)[128], const int (&v)[16], float scale) {
 #pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    acc[C * 32 + i] = __fadd_rn(acc[C * 32 + i], __fmul_rn(static_cast<float>(v[i]), scale));
+  for (int i = 0; i < 16; ++i) {
+    const float d = __fadd_rn(__int_as_float(v[i]), -kBiasFloat);
+    acc[C * 16 + i] = __fadd_rn(acc[C * 16 + i], __fmul_rn(d, scale));
   }
 }
 
 // Debug aid: the exact integer tile sums (W4 tiles were fed 16*w to the MMA).
-__device__ __forceinline__ void dump_chunk(int32_t* tile_dump, int first_col, const int (&v)[32], const TileRecord& r) {
+__device__ __forceinline__ void dump_chunk(int32_t* tile_dump, int first_col, const int (&v)[16], const TileRecord& r) {
   if (tile_dump == nullptr) return;
   const int shift = (r.offset_flag & kW4Flag) ? 4 : 0;
+  constexpr int kBias = static_cast<int>(kBiasBits);
   int4* o = reinterpret_cast<int4*>(tile_dump + first_col);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    o[i] = make_int4(v[4 * i] >> shift, v[4 * i + 1] >> shift, v[4 * i + 2] >> shift, v[4 * i + 3] >> shift);
+  for (int i = 0; i < 4; ++i) {
+    o[i] = make_int4((v[4 * i] - kBias) >> shift, (v[4 * i + 1] - kBias) >> shift, (v[4 * i + 2] - kBias) >> shift,
+                     (v[4 * i + 3] - kBias) >> shift);
   }
 }
 
@@ -204,7 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0) {
       // ---------------- producer: weights (bulk copies) + activations (cp.async) --
       int issued = 0;
@@ -272,7 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
           const uint32_t pha = (kt >> 1) & 1;
           ok = mbar_wait(raw_full(s), ph, abort_flag, &g_gemm_status, 2) && mbar_wait(a_full(s), ph, abort_flag, &g_gemm_status, 3) &&
                mbar_wait(unpacked(s), ph, abort_flag, &g_gemm_status, 4) &&
-               mbar_wait(acc_empty(b), pha ^ 1u, abort_flag, &g_gemm_status, 5);
+               mbar_wait(acc_empty(b), pha, abort_flag, &g_gemm_status, 5);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(stages + s * kStageBytes);
@@ -281,7 +315,8 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
           // A: no swizzle, 16-byte K chunks 2048 B apart, 8-row groups 128 B apart.
           // B: 64-byte swizzle, rows of 64 B, 8-row groups 512 B apart; the second K32
           // half of a row starts 32 B further on.
-          tc_mma_i8(d, smem_desc(a_addr, 2048, 128, 0), smem_desc(b_addr, 16, 512, kSwizzle64), idesc, 0u);
+          // the accumulator was preset to kBiasBits by the drain warps: always accumulate
+          tc_mma_i8(d, smem_desc(a_addr, 2048, 128, 0), smem_desc(b_addr, 16, 512, kSwizzle64), idesc, 1u);
           tc_mma_i8(d, smem_desc(a_addr + 4096, 2048, 128, 0), smem_desc(b_addr + 32, 16, 512, kSwizzle64), idesc, 1u);
           tc_commit(empty(s));
           tc_commit(acc_full(b));
@@ -332,7 +367,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
       }
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
     // ---------------- drain: int32 accumulator -> scaled FP32 registers -------------
     const int quarter = warp & 3;       // tensor-memory lane quarter this warp may read
     const int half = (warp - 4) >> 2;   // column half: weight tile rows 2*half, 2*half+1
@@ -351,19 +386,30 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
     const TileRecord* rec_lo = rec_smem + (2 * half) * kMaxNk;
     const TileRecord* rec_hi = rec_lo + kMaxNk;
 
-    // Software pipeline over 32-column chunks (two per weight tile, four per K step) with two
-    // register buffers: while the FP32 work of one chunk runs, the tensor-memory load of the
-    // next one is in flight; the accumulator is handed back to the MMA thread as soon as its
-    // last chunk has been loaded, before that chunk's arithmetic.
-    int va[32], vb[32];
+    // Software pipeline over 16-column chunks (four per weight tile, eight per K step) with
+    // two register buffers: while the FP32 work of one chunk runs, the tensor-memory load of
+    // the next one is in flight.  A chunk's columns are preset again right after they have been
+    // read, and the accumulator goes back to the MMA thread as soon as its last chunk has been
+    // loaded, before that chunk's arithmetic.
+    int va[16], vb[16];
+    uint32_t bias[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) bias[i] = kBiasBits;
+    // preset this warp's part of both accumulators, then hand them to the MMA thread
+#pragma unroll
+    for (int c = 0; c < 16; ++c) tc_st16(taddr + static_cast<uint32_t>((c >> 3) * 256 + (c & 7) * 16), bias);
+    tc_wait_st();
+    tc_fence_before();
+    mbar_arrive(acc_empty(0));
+    mbar_arrive(acc_empty(1));
     bool ok = mbar_wait(acc_full(0), 0, abort_flag, &g_gemm_status, 7);
     if (ok) {
       tc_fence_after();
-      tc_ld32(taddr, va);
+      tc_ld16(taddr, va);
     }
     for (int kt = 0; kt < n_k && ok; ++kt) {
       const int b = kt & 1;
-      const uint32_t col = static_cast<uint32_t>(b * 256);
+      const uint32_t col = taddr + static_cast<uint32_t>(b * 256);
       const float a_scale = tile_scales != nullptr ? tile_scales[kt] : token_scale;
       const TileRecord r0 = rec_lo[kt];
       const TileRecord r1 = rec_hi[kt];
@@ -375,30 +421,34 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
         if (2 * half < tiles_here) dump0 = p.acc_dump + ((grow * p.n_j + (j0 + 2 * half)) * n_k + kt) * kTile;
         if (2 * half + 1 < tiles_here) dump1 = p.acc_dump + ((grow * p.n_j + (j0 + 2 * half + 1)) * n_k + kt) * kTile;
       }
-      tc_wait_ld();  // chunk 0 in va
-      tc_ld32(taddr + col + 32, vb);
-      drain_chunk<0>(acc, va, s0);
-      if (kDump) dump_chunk(dump0, 0, va, r0);
-      tc_wait_ld();  // chunk 1 in vb
-      tc_ld32(taddr + col + 64, va);
-      drain_chunk<1>(acc, vb, s0);
-      if (kDump) dump_chunk(dump0, 32, vb, r0);
-      tc_wait_ld();  // chunk 2 in va
-      tc_ld32(taddr + col + 96, vb);
-      drain_chunk<2>(acc, va, s1);
-      if (kDump) dump_chunk(dump1, 0, va, r1);
-      tc_wait_ld();  // chunk 3 in vb: this accumulator has been read completely
+#define AQ_DRAIN_STEP(C, CUR, NEXT, SCALE, DUMP, REC)                 \
+      tc_wait_ld();                                                  \
+      tc_st16(col + (C) * 16, bias);                                 \
+      tc_ld16(col + ((C) + 1) * 16, NEXT);                           \
+      drain_chunk<C>(acc, CUR, SCALE);                               \
+      if (kDump) dump_chunk(DUMP, ((C) & 3) * 16, CUR, REC);
+      AQ_DRAIN_STEP(0, va, vb, s0, dump0, r0)
+      AQ_DRAIN_STEP(1, vb, va, s0, dump0, r0)
+      AQ_DRAIN_STEP(2, va, vb, s0, dump0, r0)
+      AQ_DRAIN_STEP(3, vb, va, s0, dump0, r0)
+      AQ_DRAIN_STEP(4, va, vb, s1, dump1, r1)
+      AQ_DRAIN_STEP(5, vb, va, s1, dump1, r1)
+      AQ_DRAIN_STEP(6, va, vb, s1, dump1, r1)
+#undef AQ_DRAIN_STEP
+      tc_wait_ld();  // chunk 7 in vb: this accumulator has been read completely
+      tc_st16(col + 7 * 16, bias);
+      tc_wait_st();
       tc_fence_before();
       mbar_arrive(acc_empty(b));
       if (kt + 1 < n_k) {
         ok = mbar_wait(acc_full(b ^ 1), ((kt + 1) >> 1) & 1, abort_flag, &g_gemm_status, 7);
         if (ok) {
           tc_fence_after();
-          tc_ld32(taddr + static_cast<uint32_t>((b ^ 1) * 256), va);
+          tc_ld16(taddr + static_cast<uint32_t>((b ^ 1) * 256), va);
         }
       }
-      drain_chunk<3>(acc, vb, s1);
-      if (kDump) dump_chunk(dump1, 32, vb, r1);
+      drain_chunk<7>(acc, vb, s1);
+      if (kDump) dump_chunk(dump1, 48, vb, r1);
     }
 
     // ---------------- epilogue: rows through shared memory, coalesced stores --------
