@@ -1,30 +1,36 @@
 // Mixed W4/W8 x A8 GEMM for large row counts on the Blackwell tensor cores (sm_100a).
 //
 // One CTA computes a 128-row x 256-column output tile (four 64-column weight tile
-// rows) and walks K in 64-wide steps.  Per step:
-//   * one elected thread streams the step's weight tiles from the prepared image into
-//     shared memory with bulk asynchronous copies (cp.async.bulk, completion counted
-//     on an mbarrier); a W8 tile is already in the 64-byte-swizzled K-major operand
-//     layout and lands in place with one copy, W4 tiles land packed in a staging area;
-//   * the producer warp copies the 128 x 64 int8 activation block with 16-byte
-//     cp.async into the same K-major "core matrix" layout (8 rows x 16 bytes);
-//   * two warps widen staged W4 tiles to int8 (value 16*w: one shift, one mask) into
-//     the operand layout and publish them to the asynchronous proxy;
-//   * one thread issues tcgen05.mma kind::i8 (M=128, N<=256, K=32, twice per step)
-//     into one of two 256-column tensor-memory accumulators and commits to mbarriers;
-//   * eight drain warps read the int32 accumulator with tcgen05.ld, turn it into FP32,
-//     scale by (activation scale * tile scale) and add into FP32 registers -- integer
+// rows) and walks K in 64-wide steps through an 8-stage shared-memory ring.  Roles:
+//   * warps 0-3, one per weight tile row of the CTA tile: lane 0 streams the row's
+//     tile of every K step from the prepared image with one bulk asynchronous copy
+//     (cp.async.bulk).  A W8 tile is stored in the K-major 64-byte-swizzle operand
+//     layout, so its copy signals the stage's "ready" mbarrier directly; a W4 tile
+//     lands packed in the first half of its operand slot and the warp widens it in
+//     place (value 16*w: one shift, one mask), publishes it to the asynchronous proxy
+//     and arrives on "ready".  Issuing a bulk copy costs its warp about 150 cycles
+//     whatever its size, which is why every stream has a warp of its own;
+//   * warp 5 streams the activations: one tensor-map copy (cp.async.bulk.tensor.2d,
+//     64-byte swizzle) per K step brings the 128 x 64 int8 block of the row-major
+//     activation matrix into the same operand layout; rows past M read as zero;
+//   * warp 4: one thread issues tcgen05.mma kind::i8 (M=128, N<=256, K=32, twice per
+//     step) into one of two 256-column tensor-memory accumulators and commits to
+//     mbarriers (stage free, accumulator full);
+//   * warps 8-15 drain: tcgen05.ld the int32 accumulator, scale by
+//     (activation scale * tile scale) and add into FP32 registers -- integer
 //     accumulation never spans two K64 tiles because every tile has its own scale
 //     (operation order of alignquant/kernels/cuda/linear.cu:951-963).  The accumulators
 //     are preset (tcgen05.st) to the bit pattern of 1.5 * 2^23, so the int32 result read
 //     as a float is exactly 1.5 * 2^23 + sum and one exact FP32 subtraction stands in
-//     for the much slower integer-to-float conversion.
+//     for the integer-to-float conversion, which runs at a quarter of the FP32 rate.
 // The epilogue stages rows through shared memory so that global stores are coalesced
 // and applies the inverse output transform (linear.cu:983-1040) where a tile has one.
 //
 // Every mbarrier wait is bounded; on a time-out the CTA raises a device status word
-// (read by aq_device_status), drains what it issued, frees its tensor memory and
-// returns instead of hanging.
+// (read by aq_device_status), stops issuing, gives copies in flight time to land,
+// frees its tensor memory and returns.
+#include <cuda.h>
+
 #include <mutex>
 
 #include "aq_common.cuh"
@@ -35,25 +41,36 @@ namespace aq {
 
 __device__ int g_gemm_status = 0;
 
+#ifdef AQ_TRACE
+// Development aid: timestamps of CTA (0,0).
+__device__ long long g_gemm_trace[4096];
+#define AQ_GT(slot) \
+  do { if (blockIdx.x == 0 && blockIdx.y == 0 && (slot) < 4096) g_gemm_trace[(slot)] = clock64(); } while (0)
+#else
+#define AQ_GT(slot) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kBM = 128;
 constexpr int kTilesN = 4;
-constexpr int kStages = 4;
-constexpr int kLag = 2;  // activation copies are published this many steps late
-constexpr int kABytes = kBM * kTile;                 // 8192
-constexpr int kBBytes = kTilesN * kW8TileBytes;      // 16384
-constexpr int kPBytes = kTilesN * kW4TileBytes;      // 8192
-constexpr int kStageBytes = kABytes + kBBytes + kPBytes;
+constexpr int kStages = 8;
+constexpr int kABytes = kBM * kTile;             // 8192
+constexpr int kBBytes = kTilesN * kW8TileBytes;  // 16384
+constexpr int kStageBytes = kABytes + kBBytes;   // 24576, a multiple of the 1024-byte operand alignment
 constexpr int kMaxNk = 512;
 constexpr int kRecBytes = kTilesN * kMaxNk * static_cast<int>(sizeof(TileRecord));
-constexpr int kNumBars = 4 * kStages + 5;
-constexpr int kSmemBytes = kStages * kStageBytes + kRecBytes + 512;
-constexpr int kThreads = 384;
+// ready[S], empty[S], packed[S][4], acc_full[2], acc_empty[2], final
+constexpr int kNumBars = 6 * kStages + 5;
+constexpr int kSmemBytes = kStages * kStageBytes + kRecBytes + kNumBars * 8 + 16;
+constexpr int kThreads = 512;
+constexpr int kDrainThreads = 256;
+constexpr int kFirstDrainWarp = 8;
+constexpr int kMmaWarp = 4;
+constexpr int kActWarp = 5;
 constexpr int kEpiRowFloats = 65;
 
 struct GemmParams {
-  const int8_t* xq;
   const float* act_scales;
   const TileRecord* records;
   const uint8_t* payload;
@@ -67,14 +84,24 @@ struct GemmParams {
   int out_dtype;
 };
 
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
-               : "memory");
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+// One box of a 2-D tensor map, global -> shared; x counts elements of the inner
+// dimension and x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tensor_copy_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -93,19 +120,6 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, int (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr)
       : "memory");
 }
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, int (&v)[16]) {
@@ -137,17 +151,13 @@ __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&v)[16])
 constexpr uint32_t kBiasBits = 0x4B400000u;  // 12582912.0f = 1.5 * 2^23
 constexpr float kBiasFloat = 12582912.0f;
 
-// K-major shared-memory operand descriptor.  Without swizzle the operand is made of
-// 8-row x 16-byte core matrices: LBO = byte step between the two 16-byte K chunks of one
-// MMA, SBO = byte step between 8-row groups.  With the 64-byte swizzle a row is 64
-// contiguous bytes whose 16-byte chunks are XOR-ed with address bits 7-8, SBO is the
-// step between 8-row groups (512 B) and LBO is not used (encoded as 16 B).
-constexpr uint32_t kSwizzle64 = 4;
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
-  return static_cast<uint64_t>((addr & 0x3ffffu) >> 4) |
-         (static_cast<uint64_t>((lbo >> 4) & 0x3fffu) << 16) |
-         (static_cast<uint64_t>((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46) |
-         (static_cast<uint64_t>(layout) << 61);
+// K-major shared-memory operand descriptor with the 64-byte swizzle: a row is 64
+// contiguous bytes whose 16-byte chunks are XOR-ed with address bits 7-8, 8-row groups
+// are 512 bytes apart (stride byte offset); the leading byte offset is not used by
+// swizzled K-major layouts and is encoded as 16 bytes.  Bit 46: sm_100 descriptor format.
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t addr) {
+  return static_cast<uint64_t>((addr & 0x3ffffu) >> 4) | (static_cast<uint64_t>(16u >> 4) << 16) |
+         (static_cast<uint64_t>(512u >> 4) << 32) | (1ull << 46) | (4ull << 61);
 }
 // kind::i8: D = S32 (2), A = B = signed 8-bit (1), both K-major, M = 128.
 __device__ __forceinline__ uint32_t instr_desc_i8(int n) {
@@ -180,7 +190,8 @@ __device__ __forceinline__ void dump_chunk(int32_t* tile_dump, int first_col, co
 }
 
 template <bool kDump>
-__global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(kThreads, 1)
+tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* stages = smem;
   TileRecord* rec_smem = reinterpret_cast<TileRecord*>(smem + kStages * kStageBytes);
@@ -194,27 +205,24 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
   const int j0 = blockIdx.x * kTilesN;
   const int tiles_here = min(kTilesN, p.n_j - j0);
   const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kBM;
-  const int64_t k_bytes = static_cast<int64_t>(n_k) * kTile;
 
   const uint32_t bar0 = smem_u32(bars);
-  auto raw_full = [&](int s) { return bar0 + 8u * s; };
-  auto a_full = [&](int s) { return bar0 + 8u * (kStages + s); };
-  auto unpacked = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
-  auto empty = [&](int s) { return bar0 + 8u * (3 * kStages + s); };
-  auto acc_full = [&](int b) { return bar0 + 8u * (4 * kStages + b); };
-  auto acc_empty = [&](int b) { return bar0 + 8u * (4 * kStages + 2 + b); };
-  const uint32_t final_bar = bar0 + 8u * (4 * kStages + 4);
+  auto ready = [&](int s) { return bar0 + 8u * s; };
+  auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+  auto packed = [&](int s, int t) { return bar0 + 8u * (2 * kStages + 4 * s + t); };
+  auto acc_full = [&](int b) { return bar0 + 8u * (6 * kStages + b); };
+  auto acc_empty = [&](int b) { return bar0 + 8u * (6 * kStages + 2 + b); };
+  const uint32_t final_bar = bar0 + 8u * (6 * kStages + 4);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(raw_full(s), 1);
-      mbar_init(a_full(s), 32);
-      mbar_init(unpacked(s), 64);
+      mbar_init(ready(s), static_cast<uint32_t>(tiles_here) + 1);  // one arrival per weight stream + activations
       mbar_init(empty(s), 1);
+      for (int t = 0; t < kTilesN; ++t) mbar_init(packed(s, t), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), 256);
+      mbar_init(acc_empty(b), kDrainThreads);
     }
     mbar_init(final_bar, 1);
     *abort_flag = 0;
@@ -225,7 +233,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
     const int t = i / n_k, kt = i % n_k;
     rec_smem[t * kMaxNk + kt] = p.records[static_cast<int64_t>(j0 + t) * n_k + kt];
   }
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(512u)
@@ -237,89 +245,128 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 4) {
+  if (warp < kFirstDrainWarp) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-    if (warp == 0) {
-      // ---------------- producer: weights (bulk copies) + activations (cp.async) --
-      int issued = 0;
-      for (int kt = 0; kt < n_k; ++kt) {
-        const int s = kt % kStages;
-        const uint32_t ph = (kt / kStages) & 1;
-        if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, &g_gemm_status, 1)) break;
-        uint8_t* a_s = stages + s * kStageBytes;
-        const uint32_t a_addr = smem_u32(a_s);
-        const uint32_t b_addr = a_addr + kABytes;
-        const uint32_t p_addr = b_addr + kBBytes;
-        if (lane == 0) {
-          uint32_t bytes = 0;
-          for (int t = 0; t < tiles_here; ++t) {
-            bytes += (rec_smem[t * kMaxNk + kt].offset_flag & kW4Flag) ? kW4TileBytes : kW8TileBytes;
+    if (warp < tiles_here) {
+      // ---------------- weight stream of tile row j0 + warp ---------------------------
+      // Two cursors over the K steps: `issue` requests tiles up to a ring ahead, `done`
+      // hands landed tiles (widened, if W4) to the MMA thread.  Neither blocks the other:
+      // barriers are probed, not waited on.
+      const int t = warp;
+      const TileRecord* recs = rec_smem + t * kMaxNk;
+      int issue = 0, done = 0;
+      uint32_t packed_parity = 0;  // bit s: phase the next wait on packed(s, t) looks for
+      uint32_t idle = 0;
+      while (done < n_k) {
+        bool progressed = false;
+        if (issue < n_k && issue < done + kStages) {
+          const int s = issue % kStages;
+          int free_now = 1;
+          if (issue >= kStages) {
+            free_now = (lane == 0 && mbar_test_wait(empty(s), ((issue / kStages) - 1) & 1)) ? 1 : 0;
+            free_now = __shfl_sync(0xffffffffu, free_now, 0);
           }
-          mbar_expect_tx(raw_full(s), bytes);
-          for (int t = 0; t < tiles_here; ++t) {
-            const uint32_t of = rec_smem[t * kMaxNk + kt].offset_flag;
-            const uint8_t* src = p.payload + static_cast<int64_t>(of & ~kW4Flag) * kW4TileBytes;
-            if (of & kW4Flag) {
-              bulk_copy(p_addr + t * kW4TileBytes, src, kW4TileBytes, raw_full(s));
-            } else {
-              bulk_copy(b_addr + t * kW8TileBytes, src, kW8TileBytes, raw_full(s));
+          if (free_now) {
+            if (lane == 0) {
+              const uint32_t of = recs[issue].offset_flag;
+              const uint8_t* src = p.payload + static_cast<int64_t>(of & ~kW4Flag) * kW4TileBytes;
+              const uint32_t dst = smem_u32(stages + s * kStageBytes + kABytes + t * kW8TileBytes);
+              if (of & kW4Flag) {
+                mbar_expect_tx(packed(s, t), kW4TileBytes);
+                bulk_copy(dst, src, kW4TileBytes, packed(s, t));
+              } else {
+                mbar_expect_tx(ready(s), kW8TileBytes);
+                bulk_copy(dst, src, kW8TileBytes, ready(s));
+              }
+            }
+            ++issue;
+            progressed = true;
+          }
+        }
+        if (done < issue) {
+          const int s = done % kStages;
+          if ((recs[done].offset_flag & kW4Flag) == 0) {
+            ++done;  // the copy of a W8 tile completes "ready" by itself
+            progressed = true;
+          } else {
+            int landed = (lane == 0 && mbar_test_wait(packed(s, t), (packed_parity >> s) & 1u)) ? 1 : 0;
+            landed = __shfl_sync(0xffffffffu, landed, 0);
+            if (landed) {
+              packed_parity ^= 1u << s;
+              // Widen in place.  Packed chunk q = 2*n + h (16 bytes) holds the k16 blocks 2h
+              // (low nibbles) and 2h+1 (high nibbles) of row n; the widened row n takes bytes
+              // 64n..64n+63 of the slot, so every lane reads its four chunks before any
+              // lane writes.
+              uint8_t* tile = stages + s * kStageBytes + kABytes + t * kW8TileBytes;
+              uint4 pk[4];
+#pragma unroll
+              for (int r = 0; r < 4; ++r) pk[r] = *reinterpret_cast<const uint4*>(tile + (r * 32 + lane) * 16);
+              __syncwarp();
+#pragma unroll
+              for (int r = 0; r < 4; ++r) {
+                const int q = r * 32 + lane;
+                const int n = q >> 1, h = q & 1;
+                uint4 lo, hi;
+                lo.x = (pk[r].x << 4) & 0xf0f0f0f0u;
+                lo.y = (pk[r].y << 4) & 0xf0f0f0f0u;
+                lo.z = (pk[r].z << 4) & 0xf0f0f0f0u;
+                lo.w = (pk[r].w << 4) & 0xf0f0f0f0u;
+                hi.x = pk[r].x & 0xf0f0f0f0u;
+                hi.y = pk[r].y & 0xf0f0f0f0u;
+                hi.z = pk[r].z & 0xf0f0f0f0u;
+                hi.w = pk[r].w & 0xf0f0f0f0u;
+                uint8_t* row = tile + n * 64;
+                const int swz = (n >> 1) & 3;
+                *reinterpret_cast<uint4*>(row + (((2 * h) ^ swz) << 4)) = lo;
+                *reinterpret_cast<uint4*>(row + (((2 * h + 1) ^ swz) << 4)) = hi;
+              }
+              fence_proxy_async();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(ready(s));
+              ++done;
+              progressed = true;
             }
           }
         }
-#pragma unroll 4
-        for (int i = 0; i < 16; ++i) {
-          const int q = lane + 32 * i;
-          const int row = q >> 2, c = q & 3;
-          const int64_t grow = m0 + row;
-          const bool valid = grow < p.m;
-          const int8_t* src = p.xq + (valid ? grow : 0) * k_bytes + static_cast<int64_t>(kt) * kTile + c * 16;
-          cp_async16(a_addr + c * 2048 + (row >> 3) * 128 + (row & 7) * 16, src, valid ? 16u : 0u);
-        }
-        cp_async_commit();
-        issued = kt + 1;
-        if (kt >= kLag) {
-          cp_async_wait<kLag>();
-          fence_proxy_async();
-          mbar_arrive(a_full((kt - kLag) % kStages));
-        }
-      }
-      cp_async_wait<0>();
-      fence_proxy_async();
-      for (int kt = max(0, issued - kLag); kt < issued; ++kt) mbar_arrive(a_full(kt % kStages));
-      if (*abort_flag != 0 && lane == 0) {
-        // give bulk copies still in flight a bounded chance to land before the CTA exits
-        for (int kt = max(0, issued - kStages); kt < issued; ++kt) {
-          const uint32_t bar = raw_full(kt % kStages);
-          for (uint32_t i = 0; i < (1u << 16) && !mbar_try_wait(bar, (kt / kStages) & 1); ++i) {
+        if (progressed) {
+          idle = 0;
+        } else {
+          ++idle;
+          if (idle >= kSpinLimit) {
+            if (lane == 0) {
+              *abort_flag = 1;
+              atomicCAS(&g_gemm_status, 0, 1);
+            }
+            break;
           }
+          if ((idle & 255u) == 0 && *abort_flag != 0) break;
         }
       }
-    } else if (warp == 1) {
-      // ---------------- MMA issuer -------------------------------------------------
+    } else if (warp == kMmaWarp) {
+      // ---------------- MMA issuer ---------------------------------------------------
       if (lane == 0) {
         const uint32_t idesc = instr_desc_i8(64 * tiles_here);
         bool ok = true;
-        for (int kt = 0; kt < n_k && ok; ++kt) {
+        for (int kt = 0; kt < n_k; ++kt) {
           const int s = kt % kStages;
-          const uint32_t ph = (kt / kStages) & 1;
           const int b = kt & 1;
-          const uint32_t pha = (kt >> 1) & 1;
-          ok = mbar_wait(raw_full(s), ph, abort_flag, &g_gemm_status, 2) && mbar_wait(a_full(s), ph, abort_flag, &g_gemm_status, 3) &&
-               mbar_wait(unpacked(s), ph, abort_flag, &g_gemm_status, 4) &&
-               mbar_wait(acc_empty(b), pha, abort_flag, &g_gemm_status, 5);
+          AQ_GT(4 * kt);
+          ok = mbar_wait(ready(s), (kt / kStages) & 1, abort_flag, &g_gemm_status, 2);
+          AQ_GT(4 * kt + 1);
+          ok = ok && mbar_wait(acc_empty(b), (kt >> 1) & 1, abort_flag, &g_gemm_status, 5);
+          AQ_GT(4 * kt + 2);
           if (!ok) break;
           tc_fence_after();
           const uint32_t a_addr = smem_u32(stages + s * kStageBytes);
           const uint32_t b_addr = a_addr + kABytes;
           const uint32_t d = tmem_base + static_cast<uint32_t>(b) * 256u;
-          // A: no swizzle, 16-byte K chunks 2048 B apart, 8-row groups 128 B apart.
-          // B: 64-byte swizzle, rows of 64 B, 8-row groups 512 B apart; the second K32
-          // half of a row starts 32 B further on.
-          // the accumulator was preset to kBiasBits by the drain warps: always accumulate
-          tc_mma_i8(d, smem_desc(a_addr, 2048, 128, 0), smem_desc(b_addr, 16, 512, kSwizzle64), idesc, 1u);
-          tc_mma_i8(d, smem_desc(a_addr + 4096, 2048, 128, 0), smem_desc(b_addr + 32, 16, 512, kSwizzle64), idesc, 1u);
+          // Both operands: rows of 64 bytes, the second K32 half of a row starts 32 bytes in.
+          // The accumulator was preset to kBiasBits by the drain warps: always accumulate.
+          tc_mma_i8(d, smem_desc_sw64(a_addr), smem_desc_sw64(b_addr), idesc, 1u);
+          tc_mma_i8(d, smem_desc_sw64(a_addr + 32), smem_desc_sw64(b_addr + 32), idesc, 1u);
           tc_commit(empty(s));
           tc_commit(acc_full(b));
+          AQ_GT(4 * kt + 3);
         }
         if (!ok) {
           // make sure nothing issued is still running before tensor memory is freed
@@ -329,48 +376,28 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
         }
       }
       __syncwarp();
-    } else {
-      // ---------------- W4 widening: packed staging -> int8 operand layout ---------
-      const int u = threadIdx.x - 64;
-      for (int kt = 0; kt < n_k; ++kt) {
-        const int s = kt % kStages;
-        const uint32_t ph = (kt / kStages) & 1;
-        if (!mbar_wait(raw_full(s), ph, abort_flag, &g_gemm_status, 6)) break;
-        uint8_t* b_s = stages + s * kStageBytes + kABytes;
-        const uint8_t* p_s = b_s + kBBytes;
-        for (int t = 0; t < tiles_here; ++t) {
-          if (rec_smem[t * kMaxNk + kt].offset_flag & kW4Flag) {
-#pragma unroll
-            for (int rep = 0; rep < 2; ++rep) {
-              // packed chunk q = 2*n + h: low nibbles are k16 block 2h of row n, high nibbles 2h+1
-              const int q = rep * 64 + u;
-              const int n = q >> 1, h = q & 1;
-              const uint4 pk = *reinterpret_cast<const uint4*>(p_s + t * kW4TileBytes + q * 16);
-              uint4 lo, hi;
-              lo.x = (pk.x << 4) & 0xf0f0f0f0u;
-              lo.y = (pk.y << 4) & 0xf0f0f0f0u;
-              lo.z = (pk.z << 4) & 0xf0f0f0f0u;
-              lo.w = (pk.w << 4) & 0xf0f0f0f0u;
-              hi.x = pk.x & 0xf0f0f0f0u;
-              hi.y = pk.y & 0xf0f0f0f0u;
-              hi.z = pk.z & 0xf0f0f0f0u;
-              hi.w = pk.w & 0xf0f0f0f0u;
-              uint8_t* row = b_s + t * kW8TileBytes + n * 64;
-              const int swz = (n >> 1) & 3;
-              *reinterpret_cast<uint4*>(row + (((2 * h) ^ swz) << 4)) = lo;
-              *reinterpret_cast<uint4*>(row + (((2 * h + 1) ^ swz) << 4)) = hi;
-            }
-          }
+    } else if (warp == kActWarp) {
+      // ---------------- activation stream ----------------------------------------------
+      if (lane == 0) {
+        for (int kt = 0; kt < n_k; ++kt) {
+          const int s = kt % kStages;
+          if (kt >= kStages && !mbar_wait(empty(s), ((kt / kStages) - 1) & 1, abort_flag, &g_gemm_status, 3)) break;
+          mbar_expect_tx(ready(s), kABytes);
+          tensor_copy_2d(smem_u32(stages + s * kStageBytes), &x_map, kt * kTile, static_cast<int>(m0), ready(s));
         }
-        fence_proxy_async();
-        mbar_arrive(unpacked(s));
       }
+      __syncwarp();
+    }
+    if (*abort_flag != 0) {
+      // bulk copies may still be in flight: give them a bounded time to land before the CTA
+      // and its shared memory go away
+      for (int i = 0; i < 64; ++i) __nanosleep(2000);
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     // ---------------- drain: int32 accumulator -> scaled FP32 registers -------------
     const int quarter = warp & 3;       // tensor-memory lane quarter this warp may read
-    const int half = (warp - 4) >> 2;   // column half: weight tile rows 2*half, 2*half+1
+    const int half = (warp - kFirstDrainWarp) >> 2;   // column half: weight tile rows 2*half, 2*half+1
     const int row = quarter * 32 + lane;
     const int64_t grow = m0 + row;
     const bool row_valid = grow < p.m;
@@ -453,7 +480,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
 
     // ---------------- epilogue: rows through shared memory, coalesced stores --------
     if (ok) {
-      float* region = reinterpret_cast<float*>(stages) + (warp - 4) * (32 * kEpiRowFloats);
+      float* region = reinterpret_cast<float*>(stages) + (warp - kFirstDrainWarp) * (32 * kEpiRowFloats);
       const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
@@ -484,7 +511,7 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
                  : "memory");
@@ -492,6 +519,43 @@ __global__ void __launch_bounds__(kThreads, 1) tmem_gemm_kernel(const GemmParams
 }
 
 std::once_flag g_attr_once[64];
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+std::once_flag g_encode_once;
+EncodeTiledFn g_encode_tiled = nullptr;
+
+// The driver's tensor-map encoder, looked up through the runtime so that the library
+// does not link against the driver library.
+EncodeTiledFn encode_tiled_fn() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &fn, 12000, cudaEnableDefault, &found) ==
+            cudaSuccess &&
+        found == cudaDriverEntryPointSuccess) {
+      g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+  });
+  return g_encode_tiled;
+}
+
+// Row-major int8 [m][k] seen as boxes of 128 rows x 64 bytes that land with the 64-byte
+// swizzle; rows past m are filled with zeros.
+int encode_activation_map(CUtensorMap* map, const int8_t* xq, int64_t m, int64_t k) {
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return fail(AQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k)};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTile), static_cast<cuuint32_t>(kBM)};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(xq), dims, strides, box,
+                            elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", static_cast<int>(r));
+  return AQ_OK;
+}
 
 }  // namespace
 
@@ -516,8 +580,11 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   });
   rc = check_cuda(attr_status, "cudaFuncSetAttribute(tmem_gemm_kernel)");
   if (rc != AQ_OK) return rc;
+  if (a.m >= (1LL << 31)) return fail(AQ_ERR_INVALID, "the GEMM kernel supports fewer than 2^31 rows");
+  alignas(64) CUtensorMap x_map;
+  rc = encode_activation_map(&x_map, a.xq, a.m, static_cast<int64_t>(a.n_k) * kTile);
+  if (rc != AQ_OK) return rc;
   GemmParams p;
-  p.xq = a.xq;
   p.act_scales = a.act_scales;
   p.records = a.records;
   p.payload = a.payload;
@@ -532,12 +599,18 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   const dim3 grid(static_cast<unsigned>((a.n_j + kTilesN - 1) / kTilesN),
                   static_cast<unsigned>((a.m + kBM - 1) / kBM));
   if (a.acc_dump != nullptr) {
-    tmem_gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(p);
+    tmem_gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(x_map, p);
   } else {
-    tmem_gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(p);
+    tmem_gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(x_map, p);
   }
   return check_cuda(cudaGetLastError(), "tensor-memory GEMM launch");
 }
+
+#ifdef AQ_TRACE
+extern "C" __attribute__((visibility("default"))) int aq_debug_read_gemm_trace(long long* dst) {
+  return static_cast<int>(cudaMemcpyFromSymbol(dst, g_gemm_trace, sizeof(long long) * 4096));
+}
+#endif
 
 int take_gemm_status() {
   int status = 0;
