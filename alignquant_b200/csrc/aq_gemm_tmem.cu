@@ -19,10 +19,7 @@
 //   * warps 8-15 drain: tcgen05.ld the int32 accumulator, scale by
 //     (activation scale * tile scale) and add into FP32 registers -- integer
 //     accumulation never spans two K64 tiles because every tile has its own scale
-//     (operation order of alignquant/kernels/cuda/linear.cu:951-963).  The accumulators
-//     are preset (tcgen05.st) to the bit pattern of 1.5 * 2^23, so the int32 result read
-//     as a float is exactly 1.5 * 2^23 + sum and one exact FP32 subtraction stands in
-//     for the integer-to-float conversion, which runs at a quarter of the FP32 rate.
+//     (operation order of alignquant/kernels/cuda/linear.cu:951-963).
 // The epilogue stages rows through shared memory so that global stores are coalesced
 // and applies the inverse output transform (linear.cu:983-1040) where a tile has one.
 //
@@ -46,8 +43,15 @@ __device__ int g_gemm_status = 0;
 __device__ long long g_gemm_trace[4096];
 #define AQ_GT(slot) \
   do { if (blockIdx.x == 0 && blockIdx.y == 0 && (slot) < 4096) g_gemm_trace[(slot)] = clock64(); } while (0)
+#define AQ_SUM_BEGIN() long long aq_t = clock64()
+#define AQ_SUM_MARK(i) do { const long long n = clock64(); aq_sums[i] += n - aq_t; aq_t = n; } while (0)
+#define AQ_SUM_WRITE(slot) \
+  do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) for (int i = 0; i < 4; ++i) g_gemm_trace[(slot) + i] = aq_sums[i]; } while (0)
 #else
 #define AQ_GT(slot) do { } while (0)
+#define AQ_SUM_BEGIN() do { } while (0)
+#define AQ_SUM_MARK(i) do { } while (0)
+#define AQ_SUM_WRITE(slot) do { } while (0)
 #endif
 
 namespace {
@@ -95,6 +99,19 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Bounded wait by polling (mbarrier.test_wait never suspends the thread).  Returns false
+// when the CTA is aborting; a wait that runs out of polls raises the abort flag and records
+// `code` in the status word.
+__device__ __forceinline__ bool mbar_poll_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               int code) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((i & 255u) == 255u && *abort_flag != 0) return false;
+  }
+  *abort_flag = 1;
+  atomicCAS(&g_gemm_status, 0, code);
+  return false;
+}
 // One box of a 2-D tensor map, global -> shared; x counts elements of the inner
 // dimension and x * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tensor_copy_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -132,24 +149,35 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, int (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// Store one 32-bit value into 16 consecutive columns of this warp's 32 tensor-memory lanes.
-__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
-      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
-      "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
-      : "memory");
+// Wait for this thread's tensor-memory loads.  The loaded registers are named as operands so
+// that the compiler cannot move their uses ahead of the wait.
+__device__ __forceinline__ void tc_wait_ld(int (&v)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                 "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+               :
+               : "memory");
 }
-
-// The int32 accumulators start every K step at kBiasBits instead of zero.  Read back as
-// an IEEE float, kBiasBits + d is exactly kBiasFloat + d for |d| < 2^22 (tile sums stay
-// below 2^21 in magnitude, 16x-scaled W4 sums included), so one exact FP32 subtraction
-// replaces the integer-to-float conversion, which runs at a quarter of the FP32 rate.
-constexpr uint32_t kBiasBits = 0x4B400000u;  // 12582912.0f = 1.5 * 2^23
-constexpr float kBiasFloat = 12582912.0f;
+// A whole warp waits on an mbarrier through one polling lane: thirty-two lanes polling (or
+// arriving on) one barrier word are served one after the other by the shared-memory unit,
+// which was measured at several hundred cycles per wait.  The shuffle that hands out the
+// result is a warp-level synchronisation and orders the other lanes after the poll.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int lane, volatile uint32_t* abort_flag,
+                                          int code = 7) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_poll_wait(bar, parity, abort_flag, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 
 // K-major shared-memory operand descriptor with the 64-byte swizzle: a row is 64
 // contiguous bytes whose 16-byte chunks are XOR-ed with address bits 7-8, 8-row groups
@@ -165,14 +193,35 @@ __device__ __forceinline__ uint32_t instr_desc_i8(int n) {
          (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
-// acc[16*C .. 16*C+15] += float(d) * scale with d = v - kBiasBits; the subtraction is exact,
-// multiply and add are rounded separately
+// Packed FP32 pairs (add.f32x2 / mul.f32x2): the same IEEE round-to-nearest results as the
+// scalar instructions at two thirds of the issue slots.
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// There is no packed multiply here on purpose: the assembler contracts a packed multiply
+// (however it is written) that feeds a packed add into one fused multiply-add, which
+// rounds a * b + c once instead of twice.  The products are therefore formed with the
+// scalar instruction, which keeps its own rounding.
+
+// acc[16*C .. 16*C+15] += float(v) * scale, multiply and add rounded separately (operation
+// order of linear.cu:958-962); the two sums of a pair are added with one packed instruction
 template <int C>
-__device__ __forceinline__ void drain_chunk(float (&acc)[128], const int (&v)[16], float scale) {
+__device__ __forceinline__ void drain_chunk(uint64_t (&acc)[64], const int (&v)[16], float scale) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float d = __fadd_rn(__int_as_float(v[i]), -kBiasFloat);
-    acc[C * 16 + i] = __fadd_rn(acc[C * 16 + i], __fmul_rn(d, scale));
+  for (int i = 0; i < 8; ++i) {
+    const float p0 = __fmul_rn(__int2float_rn(v[2 * i]), scale);
+    const float p1 = __fmul_rn(__int2float_rn(v[2 * i + 1]), scale);
+    acc[C * 8 + i] = add2(acc[C * 8 + i], pack2(__float_as_uint(p0), __float_as_uint(p1)));
   }
 }
 
@@ -180,12 +229,10 @@ __device__ __forceinline__ void drain_chunk(float (&acc)[128], const int (&v)[16
 __device__ __forceinline__ void dump_chunk(int32_t* tile_dump, int first_col, const int (&v)[16], const TileRecord& r) {
   if (tile_dump == nullptr) return;
   const int shift = (r.offset_flag & kW4Flag) ? 4 : 0;
-  constexpr int kBias = static_cast<int>(kBiasBits);
   int4* o = reinterpret_cast<int4*>(tile_dump + first_col);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    o[i] = make_int4((v[4 * i] - kBias) >> shift, (v[4 * i + 1] - kBias) >> shift, (v[4 * i + 2] - kBias) >> shift,
-                     (v[4 * i + 3] - kBias) >> shift);
+    o[i] = make_int4(v[4 * i] >> shift, v[4 * i + 1] >> shift, v[4 * i + 2] >> shift, v[4 * i + 3] >> shift);
   }
 }
 
@@ -222,7 +269,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), kDrainThreads);
+      mbar_init(acc_empty(b), kDrainThreads / 32);  // one arrival per drain warp
     }
     mbar_init(final_bar, 1);
     *abort_flag = 0;
@@ -244,9 +291,12 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+#ifdef AQ_TRACE
+  if (lane == 0) AQ_GT(3900 + warp);  // clock of every warp right after the barrier
+#endif
 
   if (warp < kFirstDrainWarp) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp < tiles_here) {
       // ---------------- weight stream of tile row j0 + warp ---------------------------
       // Two cursors over the K steps: `issue` requests tiles up to a ring ahead, `done`
@@ -331,6 +381,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         if (progressed) {
           idle = 0;
         } else {
+          __nanosleep(200);  // leave the issue slots and the shared-memory pipe to the drain warps
           ++idle;
           if (idle >= kSpinLimit) {
             if (lane == 0) {
@@ -344,35 +395,39 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       }
     } else if (warp == kMmaWarp) {
       // ---------------- MMA issuer ---------------------------------------------------
-      if (lane == 0) {
-        const uint32_t idesc = instr_desc_i8(64 * tiles_here);
-        bool ok = true;
-        for (int kt = 0; kt < n_k; ++kt) {
-          const int s = kt % kStages;
-          const int b = kt & 1;
-          AQ_GT(4 * kt);
-          ok = mbar_wait(ready(s), (kt / kStages) & 1, abort_flag, &g_gemm_status, 2);
-          AQ_GT(4 * kt + 1);
-          ok = ok && mbar_wait(acc_empty(b), (kt >> 1) & 1, abort_flag, &g_gemm_status, 5);
-          AQ_GT(4 * kt + 2);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t a_addr = smem_u32(stages + s * kStageBytes);
-          const uint32_t b_addr = a_addr + kABytes;
-          const uint32_t d = tmem_base + static_cast<uint32_t>(b) * 256u;
+      // The whole warp walks the loop so that addresses and descriptors stay warp-uniform
+      // values (the MMA takes them from uniform registers); one elected lane issues.
+      const uint32_t idesc = instr_desc_i8(64 * tiles_here);
+      const uint32_t stage0 = smem_u32(stages);
+      bool ok = true;
+      for (int kt = 0; kt < n_k; ++kt) {
+        const int s = kt % kStages;
+        const int b = kt & 1;
+        if (lane == 0) AQ_GT(4 * kt);
+        ok = warp_wait(ready(s), (kt / kStages) & 1, lane, abort_flag, 2);
+        if (lane == 0) AQ_GT(4 * kt + 1);
+        ok = ok && warp_wait(acc_empty(b), (kt >> 1) & 1, lane, abort_flag, 5);
+        if (lane == 0) AQ_GT(4 * kt + 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = stage0 + static_cast<uint32_t>(s) * kStageBytes;
+        const uint32_t b_addr = a_addr + kABytes;
+        const uint32_t d = tmem_base + static_cast<uint32_t>(b) * 256u;
+        if (elect_one()) {
           // Both operands: rows of 64 bytes, the second K32 half of a row starts 32 bytes in.
-          // The accumulator was preset to kBiasBits by the drain warps: always accumulate.
-          tc_mma_i8(d, smem_desc_sw64(a_addr), smem_desc_sw64(b_addr), idesc, 1u);
+          // Every K step starts a fresh integer sum: the first MMA overwrites the accumulator.
+          tc_mma_i8(d, smem_desc_sw64(a_addr), smem_desc_sw64(b_addr), idesc, 0u);
           tc_mma_i8(d, smem_desc_sw64(a_addr + 32), smem_desc_sw64(b_addr + 32), idesc, 1u);
           tc_commit(empty(s));
           tc_commit(acc_full(b));
-          AQ_GT(4 * kt + 3);
         }
-        if (!ok) {
-          // make sure nothing issued is still running before tensor memory is freed
-          tc_commit(final_bar);
-          for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(final_bar, 0); ++i) {
-          }
+        __syncwarp();
+        if (lane == 0) AQ_GT(4 * kt + 3);
+      }
+      if (!ok && lane == 0) {
+        // make sure nothing issued is still running before tensor memory is freed
+        tc_commit(final_bar);
+        for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(final_bar, 0); ++i) {
         }
       }
       __syncwarp();
@@ -394,7 +449,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       for (int i = 0; i < 64; ++i) __nanosleep(2000);
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ---------------- drain: int32 accumulator -> scaled FP32 registers -------------
     const int quarter = warp & 3;       // tensor-memory lane quarter this warp may read
     const int half = (warp - kFirstDrainWarp) >> 2;   // column half: weight tile rows 2*half, 2*half+1
@@ -403,9 +458,9 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
     const bool row_valid = grow < p.m;
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                            static_cast<uint32_t>(half * 128);
-    float acc[128];
+    uint64_t acc[64];  // 128 FP32 sums as packed pairs
 #pragma unroll
-    for (int i = 0; i < 128; ++i) acc[i] = 0.0f;
+    for (int i = 0; i < 64; ++i) acc[i] = 0ull;
     const float token_scale =
         (p.scale_mode == AQ_SCALE_TOKEN && row_valid) ? p.act_scales[grow] : 0.0f;
     const float* tile_scales =
@@ -414,22 +469,20 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
     const TileRecord* rec_hi = rec_lo + kMaxNk;
 
     // Software pipeline over 16-column chunks (four per weight tile, eight per K step) with
-    // two register buffers: while the FP32 work of one chunk runs, the tensor-memory load of
-    // the next one is in flight.  A chunk's columns are preset again right after they have been
-    // read, and the accumulator goes back to the MMA thread as soon as its last chunk has been
-    // loaded, before that chunk's arithmetic.
+    // two register buffers: while the arithmetic of one chunk runs, the tensor-memory load of
+    // the next one is in flight.  The accumulator goes back to the MMA thread as soon as its
+    // last chunk has been loaded, before that chunk's arithmetic.
     int va[16], vb[16];
-    uint32_t bias[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) bias[i] = kBiasBits;
-    // preset this warp's part of both accumulators, then hand them to the MMA thread
-#pragma unroll
-    for (int c = 0; c < 16; ++c) tc_st16(taddr + static_cast<uint32_t>((c >> 3) * 256 + (c & 7) * 16), bias);
-    tc_wait_st();
+#ifdef AQ_TRACE
+    long long aq_sums[4] = {0, 0, 0, 0};
+#endif
     tc_fence_before();
-    mbar_arrive(acc_empty(0));
-    mbar_arrive(acc_empty(1));
-    bool ok = mbar_wait(acc_full(0), 0, abort_flag, &g_gemm_status, 7);
+    __syncwarp();
+    if (lane == 0) {  // both accumulators start out free
+      mbar_arrive(acc_empty(0));
+      mbar_arrive(acc_empty(1));
+    }
+    bool ok = warp_wait(acc_full(0), 0, lane, abort_flag);
     if (ok) {
       tc_fence_after();
       tc_ld16(taddr, va);
@@ -437,6 +490,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
     for (int kt = 0; kt < n_k && ok; ++kt) {
       const int b = kt & 1;
       const uint32_t col = taddr + static_cast<uint32_t>(b * 256);
+      AQ_SUM_BEGIN();
       const float a_scale = tile_scales != nullptr ? tile_scales[kt] : token_scale;
       const TileRecord r0 = rec_lo[kt];
       const TileRecord r1 = rec_hi[kt];
@@ -449,8 +503,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         if (2 * half + 1 < tiles_here) dump1 = p.acc_dump + ((grow * p.n_j + (j0 + 2 * half + 1)) * n_k + kt) * kTile;
       }
 #define AQ_DRAIN_STEP(C, CUR, NEXT, SCALE, DUMP, REC)                 \
-      tc_wait_ld();                                                  \
-      tc_st16(col + (C) * 16, bias);                                 \
+      tc_wait_ld(CUR);                                               \
       tc_ld16(col + ((C) + 1) * 16, NEXT);                           \
       drain_chunk<C>(acc, CUR, SCALE);                               \
       if (kDump) dump_chunk(DUMP, ((C) & 3) * 16, CUR, REC);
@@ -460,23 +513,34 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       AQ_DRAIN_STEP(3, vb, va, s0, dump0, r0)
       AQ_DRAIN_STEP(4, va, vb, s1, dump1, r1)
       AQ_DRAIN_STEP(5, vb, va, s1, dump1, r1)
+      // The wait for the next accumulator sits here, inside the arithmetic, where the other
+      // drain warp of the scheduler fills the issue slots; it cannot dead-lock because the
+      // MMA of step kt+1 only needs the accumulator that step kt-1 gave back.  A poll made
+      // right after this step's hand-over would queue behind the MMA thread, which starts
+      // issuing at that very moment.
+      AQ_SUM_MARK(0);
+      if (kt + 1 < n_k) ok = warp_wait(acc_full(b ^ 1), ((kt + 1) >> 1) & 1, lane, abort_flag);
+      AQ_SUM_MARK(3);
+      if (threadIdx.x == kFirstDrainWarp * 32) AQ_GT(2048 + 2 * kt);  // next accumulator seen full
       AQ_DRAIN_STEP(6, va, vb, s1, dump1, r1)
 #undef AQ_DRAIN_STEP
-      tc_wait_ld();  // chunk 7 in vb: this accumulator has been read completely
-      tc_st16(col + 7 * 16, bias);
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(acc_empty(b));
+      if (!ok) break;
+      tc_wait_ld(vb);  // chunk 7 in vb: this accumulator has been read completely
+      AQ_SUM_MARK(0);
       if (kt + 1 < n_k) {
-        ok = mbar_wait(acc_full(b ^ 1), ((kt + 1) >> 1) & 1, abort_flag, &g_gemm_status, 7);
-        if (ok) {
-          tc_fence_after();
-          tc_ld16(taddr + static_cast<uint32_t>((b ^ 1) * 256), va);
-        }
+        tc_fence_after();
+        tc_ld16(taddr + static_cast<uint32_t>((b ^ 1) * 256), va);
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty(b));
+      if (threadIdx.x == kFirstDrainWarp * 32) AQ_GT(2048 + 2 * kt + 1);  // accumulator handed back
+      AQ_SUM_MARK(1);
       drain_chunk<7>(acc, vb, s1);
       if (kDump) dump_chunk(dump1, 48, vb, r1);
+      AQ_SUM_MARK(2);
     }
+    AQ_SUM_WRITE(3500 + (warp - kFirstDrainWarp) * 4);
 
     // ---------------- epilogue: rows through shared memory, coalesced stores --------
     if (ok) {
@@ -488,7 +552,12 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         if (tl < tiles_here) {
           const int j = j0 + tl;
 #pragma unroll
-          for (int c = 0; c < 64; ++c) region[lane * kEpiRowFloats + c] = acc[t * 64 + c];
+          for (int c = 0; c < 32; ++c) {
+            float lo, hi;
+            unpack2(acc[t * 32 + c], lo, hi);
+            region[lane * kEpiRowFloats + 2 * c] = lo;
+            region[lane * kEpiRowFloats + 2 * c + 1] = hi;
+          }
           __syncwarp();
           const int32_t* meta =
               p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
