@@ -2,14 +2,15 @@
 //
 // One CTA computes a 128-row x 256-column output tile (four 64-column weight tile
 // rows) and walks K in 64-wide steps through an 8-stage shared-memory ring.  Roles:
-//   * warps 0-3, one per weight tile row of the CTA tile: lane 0 streams the row's
-//     tile of every K step from the prepared image with one bulk asynchronous copy
-//     (cp.async.bulk).  A W8 tile is stored in the K-major 64-byte-swizzle operand
-//     layout, so its copy signals the stage's "ready" mbarrier directly; a W4 tile
-//     lands packed in the first half of its operand slot and the warp widens it in
-//     place (value 16*w: one shift, one mask), publishes it to the asynchronous proxy
-//     and arrives on "ready".  Issuing a bulk copy costs its warp about 150 cycles
-//     whatever its size, which is why every stream has a warp of its own;
+//   * warps 6-7 stream the weights: one bulk asynchronous copy (cp.async.bulk) per tile
+//     of the prepared image and K step.  A W8 tile is stored in the K-major 64-byte-swizzle
+//     operand layout, so its copy signals the stage's "ready" mbarrier directly; a W4 tile
+//     lands packed in the first half of its operand slot.  Issuing a bulk copy costs its
+//     warp about 150 cycles whatever its size, which is why the copies of a step are spread
+//     over several warps;
+//   * warps 0-3, one per weight tile row of the CTA tile, widen landed W4 tiles in place
+//     (value 16*w: one shift, one mask), publish them to the asynchronous proxy and arrive
+//     on "ready";
 //   * warp 5 streams the activations: one tensor-map copy (cp.async.bulk.tensor.2d,
 //     64-byte swizzle) per K step brings the 128 x 64 int8 block of the row-major
 //     activation matrix into the same operand layout; rows past M read as zero;
@@ -28,6 +29,7 @@
 // frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "aq_common.cuh"
@@ -57,22 +59,34 @@ __device__ long long g_gemm_trace[4096];
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kTilesN = 4;
 constexpr int kStages = 8;
-constexpr int kABytes = kBM * kTile;             // 8192
-constexpr int kBBytes = kTilesN * kW8TileBytes;  // 16384
-constexpr int kStageBytes = kABytes + kBBytes;   // 24576, a multiple of the 1024-byte operand alignment
+constexpr int kABytes = kBM * kTile;  // 8192
 constexpr int kMaxNk = 512;
-constexpr int kRecBytes = kTilesN * kMaxNk * static_cast<int>(sizeof(TileRecord));
-// ready[S], empty[S], packed[S][4], acc_full[2], acc_empty[2], final
-constexpr int kNumBars = 6 * kStages + 5;
-constexpr int kSmemBytes = kStages * kStageBytes + kRecBytes + kNumBars * 8 + 16;
 constexpr int kThreads = 512;
-constexpr int kDrainThreads = 256;
+constexpr int kDrainWarps = 8;
 constexpr int kFirstDrainWarp = 8;
 constexpr int kMmaWarp = 4;
 constexpr int kActWarp = 5;
+constexpr int kFirstCopyWarp = 6;
 constexpr int kEpiRowFloats = 65;
+constexpr int kTmemColumns = 512;
+
+// Sizes that depend on the width of the CTA tile: TN weight tile rows (64 columns each).
+// The 512 tensor-memory columns hold 512 / (64 * TN) accumulators: two for the 256-column
+// tile, four for the 128-column tile, which is used where the wider one would leave SMs idle.
+template <int TN>
+struct Shape {
+  static constexpr int kCols = TN * kTile;
+  static constexpr int kBBytes = TN * kW8TileBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;  // a multiple of the 1024-byte operand alignment
+  static constexpr int kRecBytes = TN * kMaxNk * static_cast<int>(sizeof(TileRecord));
+  static constexpr int kAccs = kTmemColumns / kCols;
+  // ready[S], empty[S], packed[S][TN], acc_full[kAccs], acc_empty[kAccs], final
+  static constexpr int kNumBars = (2 + TN) * kStages + 2 * kAccs + 1;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kRecBytes + kNumBars * 8 + 16;
+  static constexpr int kTilesPerHalf = TN / 2;       // weight tile rows drained by one warp
+  static constexpr int kChunks = 4 * kTilesPerHalf;  // 16-column chunks per drain warp and K step
+};
 
 struct GemmParams {
   const float* act_scales;
@@ -213,15 +227,15 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
 // rounds a * b + c once instead of twice.  The products are therefore formed with the
 // scalar instruction, which keeps its own rounding.
 
-// acc[16*C .. 16*C+15] += float(v) * scale, multiply and add rounded separately (operation
+// acc[16*c .. 16*c+15] += float(v) * scale, multiply and add rounded separately (operation
 // order of linear.cu:958-962); the two sums of a pair are added with one packed instruction
-template <int C>
-__device__ __forceinline__ void drain_chunk(uint64_t (&acc)[64], const int (&v)[16], float scale) {
+template <int NACC>
+__device__ __forceinline__ void drain_chunk(uint64_t (&acc)[NACC], int c, const int (&v)[16], float scale) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const float p0 = __fmul_rn(__int2float_rn(v[2 * i]), scale);
     const float p1 = __fmul_rn(__int2float_rn(v[2 * i + 1]), scale);
-    acc[C * 8 + i] = add2(acc[C * 8 + i], pack2(__float_as_uint(p0), __float_as_uint(p1)));
+    acc[c * 8 + i] = add2(acc[c * 8 + i], pack2(__float_as_uint(p0), __float_as_uint(p1)));
   }
 }
 
@@ -236,14 +250,18 @@ __device__ __forceinline__ void dump_chunk(int32_t* tile_dump, int first_col, co
   }
 }
 
-template <bool kDump>
+template <int TN, bool kDump>
 __global__ void __launch_bounds__(kThreads, 1)
 tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) {
+  using S = Shape<TN>;
+  constexpr int kStageBytes = S::kStageBytes;
+  constexpr int kAccs = S::kAccs;
+  constexpr int kTilesN = TN;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* stages = smem;
   TileRecord* rec_smem = reinterpret_cast<TileRecord*>(smem + kStages * kStageBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + kRecBytes);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + S::kRecBytes);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + S::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -256,10 +274,10 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
   const uint32_t bar0 = smem_u32(bars);
   auto ready = [&](int s) { return bar0 + 8u * s; };
   auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
-  auto packed = [&](int s, int t) { return bar0 + 8u * (2 * kStages + 4 * s + t); };
-  auto acc_full = [&](int b) { return bar0 + 8u * (6 * kStages + b); };
-  auto acc_empty = [&](int b) { return bar0 + 8u * (6 * kStages + 2 + b); };
-  const uint32_t final_bar = bar0 + 8u * (6 * kStages + 4);
+  auto packed = [&](int s, int t) { return bar0 + 8u * (2 * kStages + TN * s + t); };
+  auto acc_full = [&](int b) { return bar0 + 8u * ((2 + TN) * kStages + b); };
+  auto acc_empty = [&](int b) { return bar0 + 8u * ((2 + TN) * kStages + kAccs + b); };
+  const uint32_t final_bar = bar0 + 8u * ((2 + TN) * kStages + 2 * kAccs);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -267,9 +285,9 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       mbar_init(empty(s), 1);
       for (int t = 0; t < kTilesN; ++t) mbar_init(packed(s, t), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kAccs; ++b) {
       mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), kDrainThreads / 32);  // one arrival per drain warp
+      mbar_init(acc_empty(b), kDrainWarps);  // one arrival per drain warp
     }
     mbar_init(final_bar, 1);
     *abort_flag = 0;
@@ -283,7 +301,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"(512u)
+                 "r"(static_cast<uint32_t>(kTmemColumns))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -298,101 +316,78 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
   if (warp < kFirstDrainWarp) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     if (warp < tiles_here) {
-      // ---------------- weight stream of tile row j0 + warp ---------------------------
-      // Two cursors over the K steps: `issue` requests tiles up to a ring ahead, `done`
-      // hands landed tiles (widened, if W4) to the MMA thread.  Neither blocks the other:
-      // barriers are probed, not waited on.
+      // ---------------- W4 widening of tile row j0 + warp -------------------------------
+      // W8 tiles need no work here: their copy completes "ready" by itself.
       const int t = warp;
       const TileRecord* recs = rec_smem + t * kMaxNk;
-      int issue = 0, done = 0;
       uint32_t packed_parity = 0;  // bit s: phase the next wait on packed(s, t) looks for
-      uint32_t idle = 0;
-      while (done < n_k) {
-        bool progressed = false;
-        if (issue < n_k && issue < done + kStages) {
-          const int s = issue % kStages;
-          int free_now = 1;
-          if (issue >= kStages) {
-            free_now = (lane == 0 && mbar_test_wait(empty(s), ((issue / kStages) - 1) & 1)) ? 1 : 0;
-            free_now = __shfl_sync(0xffffffffu, free_now, 0);
-          }
-          if (free_now) {
-            if (lane == 0) {
-              const uint32_t of = recs[issue].offset_flag;
-              const uint8_t* src = p.payload + static_cast<int64_t>(of & ~kW4Flag) * kW4TileBytes;
-              const uint32_t dst = smem_u32(stages + s * kStageBytes + kABytes + t * kW8TileBytes);
-              if (of & kW4Flag) {
-                mbar_expect_tx(packed(s, t), kW4TileBytes);
-                bulk_copy(dst, src, kW4TileBytes, packed(s, t));
-              } else {
-                mbar_expect_tx(ready(s), kW8TileBytes);
-                bulk_copy(dst, src, kW8TileBytes, ready(s));
-              }
-            }
-            ++issue;
-            progressed = true;
-          }
-        }
-        if (done < issue) {
-          const int s = done % kStages;
-          if ((recs[done].offset_flag & kW4Flag) == 0) {
-            ++done;  // the copy of a W8 tile completes "ready" by itself
-            progressed = true;
-          } else {
-            int landed = (lane == 0 && mbar_test_wait(packed(s, t), (packed_parity >> s) & 1u)) ? 1 : 0;
-            landed = __shfl_sync(0xffffffffu, landed, 0);
-            if (landed) {
-              packed_parity ^= 1u << s;
-              // Widen in place.  Packed chunk q = 2*n + h (16 bytes) holds the k16 blocks 2h
-              // (low nibbles) and 2h+1 (high nibbles) of row n; the widened row n takes bytes
-              // 64n..64n+63 of the slot, so every lane reads its four chunks before any
-              // lane writes.
-              uint8_t* tile = stages + s * kStageBytes + kABytes + t * kW8TileBytes;
-              uint4 pk[4];
+      for (int kt = 0; kt < n_k; ++kt) {
+        if ((recs[kt].offset_flag & kW4Flag) == 0) continue;
+        const int s = kt % kStages;
+        int landed = 1;
+        if (lane == 0) landed = mbar_wait(packed(s, t), (packed_parity >> s) & 1u, abort_flag, &g_gemm_status, 6) ? 1 : 0;
+        if (__shfl_sync(0xffffffffu, landed, 0) == 0) break;
+        if (t == 0 && lane == 0) AQ_GT(1024 + 4 * kt + 1);
+        packed_parity ^= 1u << s;
+        // Widen in place.  Packed chunk q = 2*n + h (16 bytes) holds the k16 blocks 2h (low
+        // nibbles) and 2h+1 (high nibbles) of row n; the widened row n takes bytes 64n..64n+63
+        // of the slot, so every lane reads its four chunks before any lane writes.
+        uint8_t* tile = stages + s * kStageBytes + kABytes + t * kW8TileBytes;
+        uint4 pk[4];
 #pragma unroll
-              for (int r = 0; r < 4; ++r) pk[r] = *reinterpret_cast<const uint4*>(tile + (r * 32 + lane) * 16);
-              __syncwarp();
+        for (int r = 0; r < 4; ++r) pk[r] = *reinterpret_cast<const uint4*>(tile + (r * 32 + lane) * 16);
+        __syncwarp();
 #pragma unroll
-              for (int r = 0; r < 4; ++r) {
-                const int q = r * 32 + lane;
-                const int n = q >> 1, h = q & 1;
-                uint4 lo, hi;
-                lo.x = (pk[r].x << 4) & 0xf0f0f0f0u;
-                lo.y = (pk[r].y << 4) & 0xf0f0f0f0u;
-                lo.z = (pk[r].z << 4) & 0xf0f0f0f0u;
-                lo.w = (pk[r].w << 4) & 0xf0f0f0f0u;
-                hi.x = pk[r].x & 0xf0f0f0f0u;
-                hi.y = pk[r].y & 0xf0f0f0f0u;
-                hi.z = pk[r].z & 0xf0f0f0f0u;
-                hi.w = pk[r].w & 0xf0f0f0f0u;
-                uint8_t* row = tile + n * 64;
-                const int swz = (n >> 1) & 3;
-                *reinterpret_cast<uint4*>(row + (((2 * h) ^ swz) << 4)) = lo;
-                *reinterpret_cast<uint4*>(row + (((2 * h + 1) ^ swz) << 4)) = hi;
-              }
-              fence_proxy_async();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(ready(s));
-              ++done;
-              progressed = true;
-            }
-          }
+        for (int r = 0; r < 4; ++r) {
+          const int q = r * 32 + lane;
+          const int n = q >> 1, h = q & 1;
+          uint4 lo, hi;
+          lo.x = (pk[r].x << 4) & 0xf0f0f0f0u;
+          lo.y = (pk[r].y << 4) & 0xf0f0f0f0u;
+          lo.z = (pk[r].z << 4) & 0xf0f0f0f0u;
+          lo.w = (pk[r].w << 4) & 0xf0f0f0f0u;
+          hi.x = pk[r].x & 0xf0f0f0f0u;
+          hi.y = pk[r].y & 0xf0f0f0f0u;
+          hi.z = pk[r].z & 0xf0f0f0f0u;
+          hi.w = pk[r].w & 0xf0f0f0f0u;
+          uint8_t* row = tile + n * 64;
+          const int swz = (n >> 1) & 3;
+          *reinterpret_cast<uint4*>(row + (((2 * h) ^ swz) << 4)) = lo;
+          *reinterpret_cast<uint4*>(row + (((2 * h + 1) ^ swz) << 4)) = hi;
         }
-        if (progressed) {
-          idle = 0;
-        } else {
-          __nanosleep(200);  // leave the issue slots and the shared-memory pipe to the drain warps
-          ++idle;
-          if (idle >= kSpinLimit) {
-            if (lane == 0) {
-              *abort_flag = 1;
-              atomicCAS(&g_gemm_status, 0, 1);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready(s));
+        if (t == 0 && lane == 0) AQ_GT(1024 + 4 * kt + 2);
+      }
+    } else if (warp >= kFirstCopyWarp && warp < kFirstCopyWarp + 2) {
+      // ---------------- weight copies: TN / 2 tile rows per issuing warp ------------------
+      // Issuing a bulk copy takes its warp about 150 cycles whatever the size, so the copies of
+      // a K step are spread over two warps and kept apart from the widening.
+      if (lane == 0) {
+        const int t_first = (warp - kFirstCopyWarp) * (TN / 2);
+        for (int kt = 0; kt < n_k; ++kt) {
+          const int s = kt % kStages;
+          if (kt >= kStages && !mbar_wait(empty(s), ((kt / kStages) - 1) & 1, abort_flag, &g_gemm_status, 1)) break;
+          if (warp == kFirstCopyWarp) AQ_GT(1024 + 4 * kt);
+#pragma unroll
+          for (int i = 0; i < TN / 2; ++i) {
+            const int t = t_first + i;
+            if (t >= tiles_here) break;
+            const uint32_t of = rec_smem[t * kMaxNk + kt].offset_flag;
+            const uint8_t* src = p.payload + static_cast<int64_t>(of & ~kW4Flag) * kW4TileBytes;
+            const uint32_t dst = smem_u32(stages + s * kStageBytes + kABytes + t * kW8TileBytes);
+            if (of & kW4Flag) {
+              mbar_expect_tx(packed(s, t), kW4TileBytes);
+              bulk_copy(dst, src, kW4TileBytes, packed(s, t));
+            } else {
+              mbar_expect_tx(ready(s), kW8TileBytes);
+              bulk_copy(dst, src, kW8TileBytes, ready(s));
             }
-            break;
           }
-          if ((idle & 255u) == 0 && *abort_flag != 0) break;
         }
       }
+      __syncwarp();
     } else if (warp == kMmaWarp) {
       // ---------------- MMA issuer ---------------------------------------------------
       // The whole warp walks the loop so that addresses and descriptors stay warp-uniform
@@ -402,17 +397,17 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       bool ok = true;
       for (int kt = 0; kt < n_k; ++kt) {
         const int s = kt % kStages;
-        const int b = kt & 1;
+        const int b = kt % kAccs;
         if (lane == 0) AQ_GT(4 * kt);
         ok = warp_wait(ready(s), (kt / kStages) & 1, lane, abort_flag, 2);
         if (lane == 0) AQ_GT(4 * kt + 1);
-        ok = ok && warp_wait(acc_empty(b), (kt >> 1) & 1, lane, abort_flag, 5);
+        ok = ok && warp_wait(acc_empty(b), (kt / kAccs) & 1, lane, abort_flag, 5);
         if (lane == 0) AQ_GT(4 * kt + 2);
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_addr = stage0 + static_cast<uint32_t>(s) * kStageBytes;
         const uint32_t b_addr = a_addr + kABytes;
-        const uint32_t d = tmem_base + static_cast<uint32_t>(b) * 256u;
+        const uint32_t d = tmem_base + static_cast<uint32_t>(b * S::kCols);
         if (elect_one()) {
           // Both operands: rows of 64 bytes, the second K32 half of a row starts 32 bytes in.
           // Every K step starts a fresh integer sum: the first MMA overwrites the accumulator.
@@ -437,6 +432,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         for (int kt = 0; kt < n_k; ++kt) {
           const int s = kt % kStages;
           if (kt >= kStages && !mbar_wait(empty(s), ((kt / kStages) - 1) & 1, abort_flag, &g_gemm_status, 3)) break;
+          AQ_GT(1024 + 4 * kt + 3);
           mbar_expect_tx(ready(s), kABytes);
           tensor_copy_2d(smem_u32(stages + s * kStageBytes), &x_map, kt * kTile, static_cast<int>(m0), ready(s));
         }
@@ -452,35 +448,35 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ---------------- drain: int32 accumulator -> scaled FP32 registers -------------
     const int quarter = warp & 3;       // tensor-memory lane quarter this warp may read
-    const int half = (warp - kFirstDrainWarp) >> 2;   // column half: weight tile rows 2*half, 2*half+1
+    constexpr int kTH = S::kTilesPerHalf;
+    constexpr int kChunks = S::kChunks;
+    const int half = (warp - kFirstDrainWarp) >> 2;  // column half: weight tile rows kTH*half ...
     const int row = quarter * 32 + lane;
     const int64_t grow = m0 + row;
     const bool row_valid = grow < p.m;
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                           static_cast<uint32_t>(half * 128);
-    uint64_t acc[64];  // 128 FP32 sums as packed pairs
+                           static_cast<uint32_t>(half * kTH * kTile);
+    uint64_t acc[32 * kTH];  // 64 * kTH FP32 sums as packed pairs
 #pragma unroll
-    for (int i = 0; i < 64; ++i) acc[i] = 0ull;
+    for (int i = 0; i < 32 * kTH; ++i) acc[i] = 0ull;
     const float token_scale =
         (p.scale_mode == AQ_SCALE_TOKEN && row_valid) ? p.act_scales[grow] : 0.0f;
     const float* tile_scales =
         (p.scale_mode == AQ_SCALE_TILE && row_valid) ? p.act_scales + (grow >> 4) * n_k : nullptr;
-    const TileRecord* rec_lo = rec_smem + (2 * half) * kMaxNk;
-    const TileRecord* rec_hi = rec_lo + kMaxNk;
+    const TileRecord* recs = rec_smem + (kTH * half) * kMaxNk;
 
-    // Software pipeline over 16-column chunks (four per weight tile, eight per K step) with
-    // two register buffers: while the arithmetic of one chunk runs, the tensor-memory load of
-    // the next one is in flight.  The accumulator goes back to the MMA thread as soon as its
-    // last chunk has been loaded, before that chunk's arithmetic.
+    // Software pipeline over 16-column chunks (four per weight tile) with two register
+    // buffers: while the arithmetic of one chunk runs, the tensor-memory load of the next one
+    // is in flight.  The accumulator goes back to the MMA thread as soon as its last chunk
+    // has been loaded, before that chunk's arithmetic.
     int va[16], vb[16];
 #ifdef AQ_TRACE
     long long aq_sums[4] = {0, 0, 0, 0};
 #endif
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) {  // both accumulators start out free
-      mbar_arrive(acc_empty(0));
-      mbar_arrive(acc_empty(1));
+    if (lane == 0) {  // every accumulator starts out free
+      for (int b = 0; b < kAccs; ++b) mbar_arrive(acc_empty(b));
     }
     bool ok = warp_wait(acc_full(0), 0, lane, abort_flag);
     if (ok) {
@@ -488,56 +484,50 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       tc_ld16(taddr, va);
     }
     for (int kt = 0; kt < n_k && ok; ++kt) {
-      const int b = kt & 1;
-      const uint32_t col = taddr + static_cast<uint32_t>(b * 256);
+      const int b = kt % kAccs;
+      const int b_next = (kt + 1) % kAccs;
+      const uint32_t col = taddr + static_cast<uint32_t>(b * S::kCols);
       AQ_SUM_BEGIN();
       const float a_scale = tile_scales != nullptr ? tile_scales[kt] : token_scale;
-      const TileRecord r0 = rec_lo[kt];
-      const TileRecord r1 = rec_hi[kt];
-      const float s0 = __fmul_rn(a_scale, r0.scale);
-      const float s1 = __fmul_rn(a_scale, r1.scale);
-      int32_t* dump0 = nullptr;
-      int32_t* dump1 = nullptr;
-      if (kDump && row_valid) {
-        if (2 * half < tiles_here) dump0 = p.acc_dump + ((grow * p.n_j + (j0 + 2 * half)) * n_k + kt) * kTile;
-        if (2 * half + 1 < tiles_here) dump1 = p.acc_dump + ((grow * p.n_j + (j0 + 2 * half + 1)) * n_k + kt) * kTile;
+      TileRecord rec[kTH];
+      float scale[kTH];
+      int32_t* dump[kTH];
+#pragma unroll
+      for (int t = 0; t < kTH; ++t) {
+        rec[t] = recs[t * kMaxNk + kt];
+        scale[t] = __fmul_rn(a_scale, rec[t].scale);
+        dump[t] = nullptr;
+        if (kDump && row_valid && kTH * half + t < tiles_here) {
+          dump[t] = p.acc_dump + ((grow * p.n_j + (j0 + kTH * half + t)) * n_k + kt) * kTile;
+        }
       }
-#define AQ_DRAIN_STEP(C, CUR, NEXT, SCALE, DUMP, REC)                 \
-      tc_wait_ld(CUR);                                               \
-      tc_ld16(col + ((C) + 1) * 16, NEXT);                           \
-      drain_chunk<C>(acc, CUR, SCALE);                               \
-      if (kDump) dump_chunk(DUMP, ((C) & 3) * 16, CUR, REC);
-      AQ_DRAIN_STEP(0, va, vb, s0, dump0, r0)
-      AQ_DRAIN_STEP(1, vb, va, s0, dump0, r0)
-      AQ_DRAIN_STEP(2, va, vb, s0, dump0, r0)
-      AQ_DRAIN_STEP(3, vb, va, s0, dump0, r0)
-      AQ_DRAIN_STEP(4, va, vb, s1, dump1, r1)
-      AQ_DRAIN_STEP(5, vb, va, s1, dump1, r1)
-      // The wait for the next accumulator sits here, inside the arithmetic, where the other
-      // drain warp of the scheduler fills the issue slots; it cannot dead-lock because the
-      // MMA of step kt+1 only needs the accumulator that step kt-1 gave back.  A poll made
-      // right after this step's hand-over would queue behind the MMA thread, which starts
-      // issuing at that very moment.
-      AQ_SUM_MARK(0);
-      if (kt + 1 < n_k) ok = warp_wait(acc_full(b ^ 1), ((kt + 1) >> 1) & 1, lane, abort_flag);
-      AQ_SUM_MARK(3);
-      if (threadIdx.x == kFirstDrainWarp * 32) AQ_GT(2048 + 2 * kt);  // next accumulator seen full
-      AQ_DRAIN_STEP(6, va, vb, s1, dump1, r1)
-#undef AQ_DRAIN_STEP
-      if (!ok) break;
-      tc_wait_ld(vb);  // chunk 7 in vb: this accumulator has been read completely
-      AQ_SUM_MARK(0);
-      if (kt + 1 < n_k) {
-        tc_fence_after();
-        tc_ld16(taddr + static_cast<uint32_t>((b ^ 1) * 256), va);
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        int (&cur)[16] = (c & 1) ? vb : va;
+        int (&next)[16] = (c & 1) ? va : vb;
+        tc_wait_ld(cur);
+        if (c + 1 < kChunks) {
+          tc_ld16(col + (c + 1) * 16, next);
+        } else {
+          // The last chunk has been loaded: this accumulator has been read completely.  The
+          // next one is waited for before this one is handed back: a poll made after the
+          // hand-over would queue behind the MMA thread, which starts issuing at that moment.
+          // There is no dead-lock: the MMA of step kt+1 never needs the accumulator of step kt.
+          AQ_SUM_MARK(0);
+          if (kt + 1 < n_k) ok = warp_wait(acc_full(b_next), ((kt + 1) / kAccs) & 1, lane, abort_flag);
+          AQ_SUM_MARK(3);
+          if (kt + 1 < n_k && ok) {
+            tc_fence_after();
+            tc_ld16(taddr + static_cast<uint32_t>(b_next * S::kCols), next);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty(b));
+          AQ_SUM_MARK(1);
+        }
+        drain_chunk(acc, c, cur, scale[c >> 2]);
+        if (kDump) dump_chunk(dump[c >> 2], (c & 3) * 16, cur, rec[c >> 2]);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty(b));
-      if (threadIdx.x == kFirstDrainWarp * 32) AQ_GT(2048 + 2 * kt + 1);  // accumulator handed back
-      AQ_SUM_MARK(1);
-      drain_chunk<7>(acc, vb, s1);
-      if (kDump) dump_chunk(dump1, 48, vb, r1);
       AQ_SUM_MARK(2);
     }
     AQ_SUM_WRITE(3500 + (warp - kFirstDrainWarp) * 4);
@@ -547,8 +537,8 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       float* region = reinterpret_cast<float*>(stages) + (warp - kFirstDrainWarp) * (32 * kEpiRowFloats);
       const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        const int tl = 2 * half + t;
+      for (int t = 0; t < kTH; ++t) {
+        const int tl = kTH * half + t;
         if (tl < tiles_here) {
           const int j = j0 + tl;
 #pragma unroll
@@ -582,12 +572,11 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(kTmemColumns))
                  : "memory");
   }
 }
-
-std::once_flag g_attr_once[64];
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -626,9 +615,44 @@ int encode_activation_map(CUtensorMap* map, const int8_t* xq, int64_t m, int64_t
   return AQ_OK;
 }
 
+template <int TN>
+int launch_shape(const CUtensorMap& x_map, const GemmParams& p, bool dump, int device, cudaStream_t stream) {
+  static std::once_flag once[64];
+  cudaError_t attr_status = cudaSuccess;
+  std::call_once(once[device & 63], [&] {
+    attr_status = cudaFuncSetAttribute(tmem_gemm_kernel<TN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Shape<TN>::kSmemBytes);
+    if (attr_status == cudaSuccess) {
+      attr_status = cudaFuncSetAttribute(tmem_gemm_kernel<TN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Shape<TN>::kSmemBytes);
+    }
+  });
+  int rc = check_cuda(attr_status, "cudaFuncSetAttribute(tmem_gemm_kernel)");
+  if (rc != AQ_OK) return rc;
+  const dim3 grid(static_cast<unsigned>((p.n_j + TN - 1) / TN), static_cast<unsigned>((p.m + kBM - 1) / kBM));
+  if (dump) {
+    tmem_gemm_kernel<TN, true><<<grid, kThreads, Shape<TN>::kSmemBytes, stream>>>(x_map, p);
+  } else {
+    tmem_gemm_kernel<TN, false><<<grid, kThreads, Shape<TN>::kSmemBytes, stream>>>(x_map, p);
+  }
+  return check_cuda(cudaGetLastError(), "tensor-memory GEMM launch");
+}
+
 }  // namespace
 
 int64_t tmem_gemm_workspace_bytes(int64_t, int, int) { return 0; }
+
+// Width of the CTA tile in weight tile rows: 256 columns, or 128 columns where the wider
+// grid would occupy at most half of the SMs (measured cross-over on the decoder shapes).
+// ALIGNQUANT_B200_GEMM_TILE=2|4 forces one of them (for tests and measurements).
+int tmem_gemm_tile_rows(int64_t m, int n_j, int sm_count) {
+  if (const char* forced = std::getenv("ALIGNQUANT_B200_GEMM_TILE")) {
+    if (forced[0] == '2') return 2;
+    if (forced[0] == '4') return 4;
+  }
+  const int64_t wide_ctas = ((m + kBM - 1) / kBM) * ((n_j + 3) / 4);
+  return 2 * wide_ctas <= sm_count ? 2 : 4;
+}
 
 int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   if (a.n_k > kMaxNk) {
@@ -638,17 +662,13 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   int device = 0;
   int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
   if (rc != AQ_OK) return rc;
-  cudaError_t attr_status = cudaSuccess;
-  std::call_once(g_attr_once[device & 63], [&] {
-    attr_status = cudaFuncSetAttribute(tmem_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kSmemBytes);
-    if (attr_status == cudaSuccess) {
-      attr_status = cudaFuncSetAttribute(tmem_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemBytes);
-    }
-  });
-  rc = check_cuda(attr_status, "cudaFuncSetAttribute(tmem_gemm_kernel)");
-  if (rc != AQ_OK) return rc;
+  static int sm_counts[64] = {0};
+  if (sm_counts[device & 63] == 0) {
+    int count = 0;
+    rc = check_cuda(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute");
+    if (rc != AQ_OK) return rc;
+    sm_counts[device & 63] = count;
+  }
   if (a.m >= (1LL << 31)) return fail(AQ_ERR_INVALID, "the GEMM kernel supports fewer than 2^31 rows");
   alignas(64) CUtensorMap x_map;
   rc = encode_activation_map(&x_map, a.xq, a.m, static_cast<int64_t>(a.n_k) * kTile);
@@ -665,14 +685,10 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   p.n_k = a.n_k;
   p.scale_mode = a.scale_mode;
   p.out_dtype = a.out_dtype;
-  const dim3 grid(static_cast<unsigned>((a.n_j + kTilesN - 1) / kTilesN),
-                  static_cast<unsigned>((a.m + kBM - 1) / kBM));
-  if (a.acc_dump != nullptr) {
-    tmem_gemm_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(x_map, p);
-  } else {
-    tmem_gemm_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(x_map, p);
-  }
-  return check_cuda(cudaGetLastError(), "tensor-memory GEMM launch");
+  const bool dump = a.acc_dump != nullptr;
+  return tmem_gemm_tile_rows(a.m, a.n_j, sm_counts[device & 63]) == 4
+             ? launch_shape<4>(x_map, p, dump, device, stream)
+             : launch_shape<2>(x_map, p, dump, device, stream);
 }
 
 #ifdef AQ_TRACE

@@ -97,3 +97,20 @@ def test_gemm_agrees_with_streaming_kernel_bit_for_bit(ext):
     b = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill", decode_splits=1)
     ext.device_status()
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("tile_rows", ["2", "4"])
+def test_gemm_both_cta_tile_widths(ext, monkeypatch, tile_rows):
+    """The 128- and the 256-column CTA tile give the same bits (K long enough to wrap the stage ring)."""
+    monkeypatch.setenv("ALIGNQUANT_B200_GEMM_TILE", tile_rows)
+    m, n, k = 260, 448, 1280
+    weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "tile", seed=31)
+    dump = torch.zeros((m, n // 64, k // 64, 64), dtype=torch.int32, device="cuda")
+    out = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill_m64", acc_dump=dump)
+    plain = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill_m64")
+    ext.device_status()
+    xq_np = xq.cpu().numpy()
+    assert np.array_equal(dump.cpu().numpy(), oc.tile_accumulators_c(xq_np, tiles))
+    want = oc.linear_fp32_c(xq_np, a_mk, tiles, scales, 1)
+    assert np.array_equal(out.cpu().numpy(), want)
+    assert np.array_equal(plain.cpu().numpy(), want)
