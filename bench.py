@@ -295,15 +295,21 @@ def run_native(args) -> None:
             seconds = float(t.item())
         return seconds
 
-    # ---- device-resident step: CUDA graph on one GPU, eager with NCCL otherwise
+    # ---- device-resident step: one CUDA graph per rank (kernels and, for N > 1, the all-reduces)
     sweep(True, True)
     barrier()
-    if world == 1:
+    launch_mode = "cuda graph replay"
+    try:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            sweep(True, False)
+            sweep(True, True)
         step = graph.replay
-    else:
+    except Exception as error:  # a collective that cannot be captured: run the step eagerly
+        if world == 1:
+            raise
+        print(f"[bench] graph capture of the tensor-parallel step failed ({error}); running eagerly", file=sys.stderr)
+        launch_mode = "eager"
+        torch.cuda.synchronize()
         step = lambda: sweep(True, True)  # noqa: E731
     with ClockSampler(local_rank) as clocks:
         seconds = timed(step, args.steps, max(args.warmup, 3))
@@ -360,7 +366,7 @@ def run_native(args) -> None:
             "workload": WORKLOAD,
             "l2": "2 GB of distinct weights per step exceed the 126 MB L2; no flush between steps",
             "parallelism": f"tp{world}",
-            "launch": "cuda graph replay" if world == 1 else "eager + NCCL all-reduce",
+            "launch": launch_mode + ("" if world == 1 else " + NCCL all-reduce"),
         },
         "clocks": clocks.result,
         "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s",
@@ -384,7 +390,13 @@ def run_native(args) -> None:
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Tearing down a communicator whose collectives live in captured graphs was seen to
+        # block for ever; the step is finished and reported, so every rank synchronises and
+        # leaves without running finalizers.
+        barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main() -> None:
