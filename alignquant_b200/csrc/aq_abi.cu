@@ -274,6 +274,29 @@ int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int decode
   return AQ_OK;
 }
 
+int64_t aq_allreduce_buffer_bytes(int32_t world, int64_t max_count) {
+  if (world < 2 || world > allreduce_max_ranks() || max_count < 4 || (max_count & 3) != 0) {
+    fail(AQ_ERR_INVALID, "aq_allreduce_buffer_bytes: world must be 2..%d and max_count a positive multiple of 4",
+         allreduce_max_ranks());
+    return AQ_ERR_INVALID;
+  }
+  return allreduce_buffer_bytes(world, max_count);
+}
+
+int aq_allreduce_f32(const float* partial, float* out, int64_t count, int32_t rank, int32_t world,
+                     void* const* peer_buffers, int64_t max_count, void* stream) {
+  AQ_REQUIRE(partial != nullptr && out != nullptr && peer_buffers != nullptr, "partial, out and peer_buffers must not be NULL");
+  AQ_REQUIRE(world >= 2 && world <= allreduce_max_ranks(), "world must be 2..%d, got %d", allreduce_max_ranks(), world);
+  AQ_REQUIRE(rank >= 0 && rank < world, "rank must be in [0, world)");
+  AQ_REQUIRE(max_count >= 4 && (max_count & 3) == 0, "max_count must be a positive multiple of 4");
+  AQ_REQUIRE(count >= 4 && (count & 3) == 0 && count <= max_count, "count must be a multiple of 4 in [4, max_count]");
+  AQ_REQUIRE(aligned(partial, 16) && aligned(out, 16), "partial and out must be 16-byte aligned");
+  for (int r = 0; r < world; ++r) {
+    AQ_REQUIRE(peer_buffers[r] != nullptr && aligned(peer_buffers[r], 16), "peer_buffers[%d] must be a 16-byte aligned device pointer", r);
+  }
+  return launch_allreduce(partial, out, count, rank, world, peer_buffers, max_count, static_cast<cudaStream_t>(stream));
+}
+
 int aq_device_status(void* stream) {
   const int rc = check_cuda(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)), "cudaStreamSynchronize");
   if (rc != AQ_OK) return rc;
@@ -281,7 +304,11 @@ int aq_device_status(void* stream) {
   const int gemm_status = take_gemm_status();
   const int decode_status = take_decode_status();
   const int cluster_decode_status = take_cluster_decode_status();
-  if (stream_status < 0 || gemm_status < 0 || decode_status < 0 || cluster_decode_status < 0) {
+  const int allreduce_status = take_allreduce_status();
+  if (allreduce_status > 0) {
+    return fail(AQ_ERR_DEVICE, "the peer all-reduce gave up waiting for rank %d; its output is invalid", allreduce_status - 1);
+  }
+  if (stream_status < 0 || gemm_status < 0 || decode_status < 0 || cluster_decode_status < 0 || allreduce_status < 0) {
     return fail(AQ_ERR_CUDA, "could not read the device status words");
   }
   if (stream_status != 0 || gemm_status != 0 || decode_status != 0 || cluster_decode_status != 0) {

@@ -94,6 +94,12 @@ int64_t decode_static_scratch_bytes();
 // Tensor-memory GEMM (tcgen05) for large m.
 int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream);
 int64_t tmem_gemm_workspace_bytes(int64_t m, int n_j, int n_k);
+// Sum of per-rank partial outputs through peer memory (one node, one process per GPU).
+int launch_allreduce(const float* partial, float* out, int64_t count, int rank, int world, void* const* peer_buffers,
+                     int64_t max_count, cudaStream_t stream);
+int64_t allreduce_buffer_bytes(int world, int64_t max_count);
+int allreduce_max_ranks();
+int take_allreduce_status();
 // Read and clear the device-side time-out word of each kernel family (0 = none,
 // -1 = the word could not be read).
 int take_stream_status();

@@ -289,11 +289,12 @@ class AlignQuantLinear(nn.Module):
     """A frozen artifact-backed linear running on the native W4/W8A8 kernels."""
 
     def __init__(self, linear: nn.Linear, *, layer_name: str, runtime: _ProjectionGroupRuntime,
-                 process_group: Any = None) -> None:
+                 process_group: Any = None, peer_allreduce: Any = None) -> None:
         super().__init__()
         self.layer_name = str(layer_name)
         object.__setattr__(self, "runtime", runtime)
         object.__setattr__(self, "process_group", process_group)
+        object.__setattr__(self, "peer_allreduce", peer_allreduce)
         self.in_features = int(linear.in_features)
         self.out_features = int(linear.out_features)
         start, stop = runtime.member_slices[self.layer_name]
@@ -308,7 +309,12 @@ class AlignQuantLinear(nn.Module):
             import torch.distributed as dist
 
             result = result.contiguous()
-            dist.all_reduce(result, group=self.process_group)  # sum of the K-shard partials
+            reducer = self.peer_allreduce
+            if (reducer is not None and result.dtype == torch.float32 and result.numel() % 4 == 0
+                    and result.numel() <= reducer.max_count):
+                reducer(result)  # decode-sized partials: one kernel over peer memory
+            else:
+                dist.all_reduce(result, group=self.process_group)  # sum of the K-shard partials
         if self.bias is not None:
             result = result + self.bias.to(dtype=result.dtype)
         result = result.reshape(*original_shape[:-1], self.out_features)
@@ -325,12 +331,15 @@ def install_alignquant(
     tp_rank: int = 0,
     tp_size: int = 1,
     process_group: Any = None,
+    peer_allreduce: Any = None,
 ) -> tuple[list[AlignQuantLinear], dict[str, Any]]:
     """Replace exactly the artifact-covered decoder projections of ``model``.
 
     With ``tp_size > 1`` the model's linears must already have the per-rank shapes
     (output features / tp for q, k, v, gate, up; input features / tp for o, down) while the
-    artifact holds the full layers; each rank keeps its tile-aligned shard.
+    artifact holds the full layers; each rank keeps its tile-aligned shard.  ``peer_allreduce``
+    (a ``kernels.cuda.allreduce.PeerAllReduce``) takes over the sum of the row-parallel
+    partials for FP32 results that fit its buffer; larger ones go through ``dist.all_reduce``.
     Returns the installed modules and a metadata dict, like the reference
     (alignquant/quantization/model.py:419-539).
     """
@@ -393,7 +402,8 @@ def install_alignquant(
         runtimes[group_id] = runtime
         for name in members:
             parent, attr, _ = records.pop(name)
-            module = AlignQuantLinear(getattr(parent, attr), layer_name=name, runtime=runtime, process_group=process_group)
+            module = AlignQuantLinear(getattr(parent, attr), layer_name=name, runtime=runtime, process_group=process_group,
+                                      peer_allreduce=peer_allreduce)
             setattr(parent, attr, module)
             installed.append(module)
     model._alignquant_projection_groups = tuple(runtimes.values())

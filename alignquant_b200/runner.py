@@ -87,7 +87,13 @@ def run(args) -> dict:
     ext.load_extension()
     model = build_model(args.model, world, device, layers=args.layers)
     artifact = synthetic_artifact(model, args.model, world, seed=7, device=device)
-    installed, _ = install_alignquant(model, artifact, device, scale_mode=args.scale_mode, tp_rank=rank, tp_size=world)
+    reducer = None
+    if world > 1 and os.environ.get("ALIGNQUANT_B200_ALLREDUCE", "peer") == "peer":
+        from alignquant_b200.kernels.cuda.allreduce import PeerAllReduce
+
+        reducer = PeerAllReduce(64 * SHAPES[args.model][0], device)  # up to 64 rows of hidden-size partials
+    installed, _ = install_alignquant(model, artifact, device, scale_mode=args.scale_mode, tp_rank=rank, tp_size=world,
+                                      peer_allreduce=reducer)
     del artifact
     torch.cuda.empty_cache()
 

@@ -221,6 +221,17 @@ def run_native(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     ext.load_extension()
+    reducer = None
+    if world > 1 and os.environ.get("ALIGNQUANT_B200_ALLREDUCE", "peer") == "peer":
+        from alignquant_b200.kernels.cuda.allreduce import PeerAllReduce
+
+        reducer = PeerAllReduce(max(ROW_COUNTS) * max(n for n, _, axis in GROUPS.values() if axis == "k"), device)
+
+    def all_reduce(tensor) -> None:
+        if reducer is not None:
+            reducer(tensor)
+        else:
+            dist.all_reduce(tensor)
 
     # ---- build the sharded model: prepared weight images only (raw arenas are freed)
     layers = []
@@ -260,6 +271,7 @@ def run_native(args) -> None:
                 step_bytes += call_bytes(m, n, k, weight_bytes[(layer, name)])
                 linear_bytes += weight_bytes[(layer, name)] + m * k + 4 * m + m * n * 4
     pairs_per_step = len(ROW_COUNTS) * LAYERS * len(GROUPS)
+    allreduces_per_step = len(ROW_COUNTS) * LAYERS * sum(1 for _, _, axis in GROUPS.values() if axis == "k")
 
     def sweep(with_quantizer: bool, with_allreduce: bool) -> None:
         for m in ROW_COUNTS:
@@ -270,7 +282,7 @@ def run_native(args) -> None:
                     xq, a_s = qbuf[(m, name)]
                     ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", out=outs[(m, name)])
                     if with_allreduce and world > 1 and axis == "k":
-                        dist.all_reduce(outs[(m, name)])
+                        all_reduce(outs[(m, name)])
 
     def barrier():
         if world > 1:
@@ -342,7 +354,7 @@ def run_native(args) -> None:
                     xq, a_s = ext.alignquant_activation_quantize_cuda(x, None, scale_mode="token")
                     y = ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token")
                     if world > 1 and axis == "k":
-                        dist.all_reduce(y)
+                        all_reduce(y)
                     host_out[(m, name)].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
@@ -366,12 +378,13 @@ def run_native(args) -> None:
             "workload": WORKLOAD,
             "l2": "2 GB of distinct weights per step exceed the 126 MB L2; no flush between steps",
             "parallelism": f"tp{world}",
-            "launch": launch_mode + ("" if world == 1 else " + NCCL all-reduce"),
+            "launch": launch_mode + ("" if world == 1 else
+                                     " + peer-memory all-reduce kernel" if reducer is not None else " + NCCL all-reduce"),
         },
         "clocks": clocks.result,
         "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": 2 * pairs_per_step * args.steps,
+        "gpu_launches": (2 * pairs_per_step + (allreduces_per_step if reducer is not None else 0)) * args.steps,
         "roofline": {
             "kernel": "cluster_decode_kernel (packed W4/W8 GEMV, M<=16)", "bound": "hbm",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -192,6 +192,29 @@ AQ_API int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int
                           int32_t* kernel, int32_t* splits, int32_t* workers);
 
 /*
+ * Sum of the partial outputs of a row-parallel (K-sharded) projection over the ranks of
+ * one node, through peer memory.  Replaces the dist.all_reduce that follows o_proj and
+ * down_proj under tensor parallelism (alignquant/quantization/model.py:352-356) for the
+ * small messages of decode; one process per GPU.
+ *   Every rank allocates an exchange buffer of aq_allreduce_buffer_bytes(world, max_count)
+ *   bytes that all ranks of the node can address (peer-mapped: a CUDA IPC / VMM mapping,
+ *   torch symmetric memory ...), zeroes it once, and all ranks synchronise on the host
+ *   before the first call.  peer_buffers[r] is rank r's buffer as seen from this process
+ *   (a HOST array of `world` device pointers, peer_buffers[rank] being the own one).
+ *   partial, out: FP32 [count] in ordinary device memory, 16-byte aligned; count a multiple
+ *   of 4, count <= max_count, max_count a multiple of 4; 2 <= world <= 8.  All ranks must
+ *   issue the same sequence of calls with the same count and max_count.  The ranks' partials
+ *   are added in rank order, so every rank receives the same bits; `out` may alias `partial`.
+ *   The call is one asynchronous kernel launch on `stream` (it can be captured and replayed:
+ *   the call counter lives in the exchange buffer).  The kernel waits for the peers' data
+ *   with a bounded poll; when a peer never arrives the wait gives up, the output is invalid
+ *   and aq_device_status reports AQ_ERR_DEVICE.
+ */
+AQ_API int64_t aq_allreduce_buffer_bytes(int32_t world, int64_t max_count);
+AQ_API int aq_allreduce_f32(const float* partial, float* out, int64_t count, int32_t rank, int32_t world,
+                            void* const* peer_buffers, int64_t max_count, void* stream);
+
+/*
  * Synchronises `stream`, then returns AQ_ERR_DEVICE if a kernel of this library gave
  * up a bounded device-side wait since the last call (the outputs of that launch are
  * invalid), clearing the condition; AQ_OK otherwise.  The reference has no such
