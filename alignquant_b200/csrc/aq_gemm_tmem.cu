@@ -102,30 +102,6 @@ struct GemmParams {
   int out_dtype;
 };
 
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait by polling (mbarrier.test_wait never suspends the thread).  Returns false
-// when the CTA is aborting; a wait that runs out of polls raises the abort flag and records
-// `code` in the status word.
-__device__ __forceinline__ bool mbar_poll_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                               int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *abort_flag != 0) return false;
-  }
-  *abort_flag = 1;
-  atomicCAS(&g_gemm_status, 0, code);
-  return false;
-}
 // One box of a 2-D tensor map, global -> shared; x counts elements of the inner
 // dimension and x * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tensor_copy_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -179,7 +155,7 @@ __device__ __forceinline__ void tc_wait_ld(int (&v)[16]) {
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, int lane, volatile uint32_t* abort_flag,
                                           int code = 7) {
   int ok = 1;
-  if (lane == 0) ok = mbar_poll_wait(bar, parity, abort_flag, code) ? 1 : 0;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, &g_gemm_status, code) ? 1 : 0;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 // True in exactly one lane of a converged warp.

@@ -1,0 +1,73 @@
+"""Run one packed W4/W8-A8 projection on synthetic weights and report its time.
+
+    python -m alignquant_b200.layer_run --n 5120 --k 3072 --rows 2048 --repeat 20
+    python -m alignquant_b200.layer_run --n 3072 --k 8192 --rows 1 --scale-mode token --flush-l2
+
+A seeded 60 % W4 layer of the given shape is packed into the artifact format, prepared
+once, and the quantize -> linear pair is launched ``--repeat`` times; CUDA events around the
+linear calls give the mean kernel time, from which the line reports integer TOPS
+(2*M*N*K) and the weight stream in GB/s.  The same command is the small case used for
+profiler captures of a single kernel.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--n", type=int, required=True, help="output features (multiple of 64)")
+    ap.add_argument("--k", type=int, required=True, help="input features (multiple of 64)")
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--repeat", type=int, default=20)
+    ap.add_argument("--w4-fraction", type=float, default=0.6)
+    ap.add_argument("--scale-mode", choices=("tile", "token"), default="token")
+    ap.add_argument("--out-dtype", choices=("float32", "bfloat16", "float16"), default="bfloat16")
+    ap.add_argument("--schedule", default="auto")
+    ap.add_argument("--flush-l2", action="store_true", help="overwrite a 512 MB buffer before every launch")
+    args = ap.parse_args()
+
+    from alignquant_b200.kernels.cuda import extension as ext
+    from alignquant_b200.synthetic import algorithmic_weight_bytes, synthetic_activation, synthetic_module_tensors
+
+    ext.load_extension()
+    device = torch.device("cuda", 0)
+    tensors = synthetic_module_tensors(args.n, args.k, seed=1, w4_fraction=args.w4_fraction, device=device)
+    weight_bytes = algorithmic_weight_bytes(tensors)
+    weights = ext.prepare_weights(
+        tensors["state_bits"], tensors["w4_payload"], tensors["w4_scales"], tensors["w8_payload"], tensors["w8_scales"],
+        tensors["w4_row_offsets"], tensors["w8_row_offsets"], n_k=args.k // 64,
+    )
+    x = synthetic_activation(args.rows, args.k, seed=2, device=device)
+    out_dtype = getattr(torch, args.out_dtype)
+    out = torch.empty((args.rows, args.n), dtype=out_dtype, device=device)
+    junk = torch.empty(512 << 20, dtype=torch.uint8, device=device) if args.flush_l2 else None
+    xq, scales = ext.alignquant_activation_quantize_cuda(x, None, scale_mode=args.scale_mode)
+    plan = ext.linear_plan(args.rows, args.n // 64, args.k // 64, schedule=args.schedule)
+    total_ms = 0.0
+    for index in range(args.repeat + 2):
+        if junk is not None:
+            junk.fill_(index & 0xFF)
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        ext.alignquant_linear_prepared(xq, scales, weights, None, schedule=args.schedule, scale_mode=args.scale_mode,
+                                       output_dtype=out_dtype, out=out)
+        end.record()
+        torch.cuda.synchronize()
+        if index >= 2:
+            total_ms += begin.elapsed_time(end)
+    ext.device_status(device)
+    seconds = total_ms / 1e3 / args.repeat
+    print(json.dumps({
+        "n": args.n, "k": args.k, "rows": args.rows, "plan": plan,
+        "us": seconds * 1e6, "tops": 2.0 * args.rows * args.n * args.k / seconds / 1e12,
+        "weight_gbs": weight_bytes / seconds / 1e9, "scale_mode": args.scale_mode, "out_dtype": args.out_dtype,
+    }))
+
+
+if __name__ == "__main__":
+    main()
