@@ -34,6 +34,22 @@ namespace aq {
 
 __device__ int g_cluster_decode_status = 0;
 
+#ifdef AQ_TRACE
+// Development aid: %globaltimer time stamps (ns) of a few CTAs, slot = 16 * sample + event.
+__device__ long long g_cluster_trace[1024];
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define AQ_CT(event)                                                                                   \
+  do {                                                                                                 \
+    if ((threadIdx.x & 31) == 0 && trace_sample >= 0) g_cluster_trace[16 * trace_sample + (event)] = global_ns(); \
+  } while (0)
+#else
+#define AQ_CT(event) do { } while (0)
+#endif
+
 namespace {
 
 struct Params {
@@ -64,13 +80,19 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;
 
 // Shared memory: [ring kSlots x 32 KiB][slabs 8 x (8*NT) x 64 f32][tile (8*NT) x 64 f32]
 //                [records kMaxCount][barriers][abort flag]
+// With 16 rows (NT = 2) the slabs reuse the ring's memory once the last tile has been
+// consumed (measured 4-5 % faster at M = 16: more shared memory left for the L1); with up to
+// 8 rows the extra barrier that this needs costs more than it gives, so the slabs keep their
+// own 16 KiB.
 template <int NT>
 __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kRows = 8 * NT;
+  constexpr bool kSlabsInRing = NT == 2;
+  static_assert(kConsumerWarps * kRows * kTile * 4 <= kSlots * kSlotBytes, "slabs must fit into the ring");
   uint8_t* ring = smem;
-  float* slabs = reinterpret_cast<float*>(smem + kSlots * kSlotBytes);
-  float* tile = slabs + kConsumerWarps * kRows * kTile;
+  float* slabs = reinterpret_cast<float*>(smem + (kSlabsInRing ? 0 : kSlots * kSlotBytes));
+  float* tile = reinterpret_cast<float*>(smem + kSlots * kSlotBytes) + (kSlabsInRing ? 0 : kConsumerWarps * kRows * kTile);
   TileRecord* recs = reinterpret_cast<TileRecord*>(tile + kRows * kTile);
   uint64_t* bars = reinterpret_cast<uint64_t*>(recs + kMaxCount);
   volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(bars + kNumBars);
@@ -88,6 +110,12 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
   const int groups = (count + kGroupTiles - 1) / kGroupTiles;
   const int rows = p.m < kRows ? static_cast<int>(p.m) : kRows;
 
+#ifdef AQ_TRACE
+  const int cta_linear = blockIdx.x * gridDim.y + blockIdx.y;
+  const int cta_total = gridDim.x * gridDim.y;
+  const int trace_sample = (threadIdx.x >> 5) != 0 ? -1 : cta_linear == 0 ? 0 : cta_linear == cta_total / 2 ? 1 : cta_linear == cta_total - 1 ? 2 : -1;
+  AQ_CT(0);
+#endif
   const uint32_t bar0 = smem_u32(bars);
   auto full = [&](int s) { return bar0 + 8u * s; };
   auto empty = [&](int s) { return bar0 + 8u * (kSlots + s); };
@@ -118,8 +146,10 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
               p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(lane));
   }
   for (int i = threadIdx.x; i < count; i += kThreads) recs[i] = my_records[i];
+  AQ_CT(1);
   grid_launch_dependents();
   grid_dependency_wait();  // activations and their scales come from the preceding kernel
+  AQ_CT(2);
   __syncthreads();
 
   if (producer) {
@@ -185,6 +215,7 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
       for (int nt = 0; nt < NT; ++nt) x[nt] = x_next[nt];
       if (i + kConsumerWarps < count) load_x(i + kConsumerWarps, x_next);
       if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_cluster_decode_status, 32)) break;
+      if (i == warp) AQ_CT(3);
       const TileRecord rec = recs[i];
       const TileRecord rec0 = recs[gi * kGroupTiles];
       const bool is_w4 = (rec.offset_flag & kW4Flag) != 0;
@@ -241,7 +272,9 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
         }
       }
     }
+    AQ_CT(4);
     // ---- combine the eight warp sums in warp order -----------------------------------------
+    if (kSlabsInRing) consumer_sync();  // every warp has consumed its last tile: the ring becomes the slabs
     float* slab = slabs + warp * kRows * kTile;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -264,7 +297,9 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
   }
 
   // ---- split-K exchange through cluster shared memory ------------------------------------
+  AQ_CT(5);
   cluster.sync();
+  AQ_CT(6);
   if (!producer) {
     const int32_t* meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
     const bool has_u = meta != nullptr && meta[0] != 0;
@@ -285,11 +320,14 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
       store_any(p.out, p.out_dtype, o + 32, hi);
     }
   }
+  AQ_CT(7);
   cluster.sync();  // peers may still be reading this CTA's tile
+  AQ_CT(8);
 }
 
 int smem_bytes(int nt) {
-  return kSlots * kSlotBytes + (kConsumerWarps + 1) * 8 * nt * kTile * 4 + kMaxCount * 8 + kNumBars * 8 + 16;
+  const int slabs = nt == 2 ? 0 : kConsumerWarps * 8 * nt * kTile * 4;  // NT = 2 keeps them in the ring
+  return kSlots * kSlotBytes + slabs + 8 * nt * kTile * 4 + kMaxCount * 8 + kNumBars * 8 + 16;
 }
 
 template <int NT>
@@ -360,14 +398,22 @@ int max_active_clusters(int nt, int split) {
 
 }  // namespace
 
-// Largest split (cluster size, at most 8) for which all n_j clusters are resident at
-// once, so that every CTA streams from the start; never shorter than one tile per CTA
-// and never longer than the record buffer.
+// Largest split (cluster size, at most 8) for which the grid is at most two CTAs per SM and
+// all n_j clusters are resident at once, so that every CTA streams from the start; never
+// shorter than one tile per CTA and never longer than the record buffer.
 int cluster_decode_split(int64_t m, int n_j, int n_k) {
   const int nt = m <= 8 ? 1 : 2;
+  static int sm_count[64] = {0};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) device = 0;
+  if (sm_count[device] == 0) {
+    int count = 0;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = 148;
+    sm_count[device] = count;
+  }
   int split = 1;
   for (int s = 2; s <= 8 && s <= n_k; ++s) {
-    if (max_active_clusters(nt, s) >= n_j) split = s;
+    if (static_cast<int64_t>(n_j) * s <= 2LL * sm_count[device] && max_active_clusters(nt, s) >= n_j) split = s;
   }
   while (split < 8 && (n_k + split - 1) / split > kMaxCount) ++split;
   return split;
@@ -392,6 +438,12 @@ int launch_cluster_decode(const LinearArgs& a, cudaStream_t stream) {
   const int split = cluster_decode_split(a.m, a.n_j, a.n_k);
   return a.m <= 8 ? launch_nt<1>(p, split, stream) : launch_nt<2>(p, split, stream);
 }
+
+#ifdef AQ_TRACE
+extern "C" __attribute__((visibility("default"))) int aq_debug_read_cluster_trace(long long* dst) {
+  return static_cast<int>(cudaMemcpyFromSymbol(dst, g_cluster_trace, sizeof(long long) * 1024));
+}
+#endif
 
 int take_cluster_decode_status() {
   int status = 0;
