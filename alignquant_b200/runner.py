@@ -8,7 +8,8 @@ The model is built from a Hugging Face config with the named shape (no checkpoin
 tokenizer: random weights, random token ids), every decoder projection is replaced by
 the packed W4/W8-A8 format with a seeded 60 % W4 map, and greedy decoding is timed with
 CUDA events: prefill tokens/s over the prompt pass, decode tokens/s over the generated
-tokens.  Under ``torch.distributed.run`` the decoder is built per rank with 1/tp of the
+tokens (KV cache of fixed size, the decode step captured once into a CUDA graph and
+replayed).  Under ``torch.distributed.run`` the decoder is built per rank with 1/tp of the
 heads and of the MLP width (tile-aligned tensor parallelism, all-reduce after o_proj and
 down_proj); embeddings, norms and the LM head are replicated.
 """
@@ -30,6 +31,44 @@ SHAPES = {
 }
 
 
+def _register_grouped_decode_attention() -> str:
+    """Attention for the decode step that reads each KV head once.
+
+    With a fixed-size KV cache the stock SDPA path needs a mask and therefore materialises K and V
+    once per query head of a group (``repeat_kv``), which dominated the decode step.  Here the
+    query heads of one KV group are stacked as rows of one batched matmul against the cached K
+    and V; prompts (more than one query position) go through the stock SDPA function.  This is
+    runner plumbing around the quantized projections, not part of them.
+    """
+    from transformers import AttentionInterface
+    from transformers.integrations.sdpa_attention import sdpa_attention_forward
+    from transformers.masking_utils import AttentionMaskInterface, sdpa_mask
+
+    def grouped_decode_attention(module, query, key, value, attention_mask, dropout=0.0, scaling=None,
+                                 is_causal=None, **kwargs):
+        batch, q_heads, q_len, head_dim = query.shape
+        kv_heads = key.shape[1]
+        if q_len != 1 or q_heads % kv_heads != 0:
+            return sdpa_attention_forward(module, query, key, value, attention_mask, dropout=dropout,
+                                          scaling=scaling, is_causal=is_causal, **kwargs)
+        scale = head_dim ** -0.5 if scaling is None else scaling
+        q = query.reshape(batch, kv_heads, q_heads // kv_heads, head_dim)
+        scores = torch.matmul(q, key.transpose(-1, -2)).float() * scale  # [B, kv heads, group, cache length]
+        if attention_mask is not None:
+            mask = attention_mask[:, :, :, : key.shape[2]]
+            if mask.dtype == torch.bool:  # True = attend
+                scores = scores.masked_fill(~mask, float("-inf"))
+            else:
+                scores = scores + mask.float()
+        probs = torch.softmax(scores, dim=-1).to(query.dtype)
+        out = torch.matmul(probs, value)  # [B, kv heads, group, head_dim]
+        return out.reshape(batch, q_heads, 1, head_dim).transpose(1, 2).contiguous(), None
+
+    AttentionInterface.register("grouped_decode", grouped_decode_attention)
+    AttentionMaskInterface.register("grouped_decode", sdpa_mask)  # same masks as the stock SDPA path
+    return "grouped_decode"
+
+
 def build_model(name: str, tp: int, device: torch.device, layers: int | None = None):
     """Random-init decoder of the named shape with 1/tp of the heads and MLP width."""
     import transformers
@@ -43,7 +82,7 @@ def build_model(name: str, tp: int, device: torch.device, layers: int | None = N
         vocab_size=vocab, max_position_embeddings=8192, tie_word_embeddings=False,
     )
     config = (transformers.LlamaConfig if family == "llama" else transformers.Qwen3Config)(**common)
-    config._attn_implementation = "sdpa"
+    config._attn_implementation = _register_grouped_decode_attention()
     torch.manual_seed(1234)  # same embeddings / norms / head on every rank
     with torch.device(device):
         model = transformers.AutoModelForCausalLM.from_config(config, dtype=torch.bfloat16)
@@ -102,38 +141,73 @@ def run(args) -> dict:
     prompt = torch.randint(0, vocab, (args.batch, args.prompt_len), generator=gen, device=device)
 
     def generate():
+        """Greedy decoding on a static KV cache; the decode step is replayed from a CUDA graph."""
+        from transformers import StaticCache
+
         reset_alignquant_state(model)
-        events = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        cache = StaticCache(config=model.config, max_cache_len=args.prompt_len + args.new_tokens)
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        token = torch.empty((args.batch, 1), dtype=torch.long, device=device)
+        position = torch.empty((1,), dtype=torch.long, device=device)
+
+        def step():
+            out = model(input_ids=token, past_key_values=cache, cache_position=position, use_cache=True)
+            token.copy_(out.logits[:, -1].argmax(dim=-1, keepdim=True))
+            position.add_(1)
+
+        mode = "eager"
         with torch.inference_mode():
             events[0].record()
-            out = model(input_ids=prompt, use_cache=True)
-            token = out.logits[:, -1].argmax(dim=-1, keepdim=True)
+            out = model(input_ids=prompt, past_key_values=cache,
+                        cache_position=torch.arange(args.prompt_len, device=device), use_cache=True)
+            token.copy_(out.logits[:, -1].argmax(dim=-1, keepdim=True))
+            position.fill_(args.prompt_len)
             events[1].record()
-            cache = out.past_key_values
-            for _ in range(args.new_tokens - 1):
-                out = model(input_ids=token, past_key_values=cache, use_cache=True)
-                cache = out.past_key_values
-                token = out.logits[:, -1].argmax(dim=-1, keepdim=True)
+            steps = args.new_tokens - 1
+            eager_steps = min(2, steps) if args.decode_graph else steps
+            for _ in range(eager_steps):
+                step()
+            graph = None
+            if steps > eager_steps:
+                try:
+                    torch.cuda.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        step()
+                    mode = "cuda graph replay"
+                except Exception as error:  # an op of the model that cannot be captured
+                    if rank == 0:
+                        print(f"[runner] decode step not captured ({type(error).__name__}: {error}); eager", flush=True)
+                    graph = None
+                    torch.cuda.synchronize()
             events[2].record()
+            for _ in range(steps - eager_steps):
+                if graph is not None:
+                    graph.replay()
+                else:
+                    step()
+            events[3].record()
         torch.cuda.synchronize()
-        return events[0].elapsed_time(events[1]) / 1e3, events[1].elapsed_time(events[2]) / 1e3
+        timed_steps = steps - eager_steps if steps > eager_steps else steps
+        decode_seconds = (events[2].elapsed_time(events[3]) if steps > eager_steps else events[1].elapsed_time(events[2])) / 1e3
+        return events[0].elapsed_time(events[1]) / 1e3, decode_seconds, timed_steps, mode
 
     if args.warmup:
         generate()
-    prefill_s, decode_s = generate()
+    prefill_s, decode_s, decode_steps, decode_mode = generate()
     ext.device_status(device)
     if world > 1:
         t = torch.tensor([prefill_s, decode_s], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         prefill_s, decode_s = (float(v) for v in t)
-        dist.destroy_process_group()
     return {
         "model": args.model, "layers": args.layers or SHAPES[args.model][2], "tp": world, "batch": args.batch,
         "prompt_len": args.prompt_len, "new_tokens": args.new_tokens, "scale_mode": args.scale_mode,
         "quantized_modules": len(installed),
         "prefill_tokens_per_s": args.batch * args.prompt_len / prefill_s,
-        "decode_tokens_per_s": args.batch * (args.new_tokens - 1) / decode_s,
-        "prefill_s": prefill_s, "decode_s": decode_s, "rank": rank,
+        "decode_tokens_per_s": args.batch * decode_steps / decode_s, "decode_steps_timed": decode_steps,
+        "decode_launch": decode_mode, "decode_ms_per_step": decode_s * 1e3 / max(decode_steps, 1),
+        "prefill_s": prefill_s, "decode_s": decode_s, "rank": rank, "world": world,
     }
 
 
@@ -146,9 +220,18 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=None, help="override the number of decoder layers")
     ap.add_argument("--scale-mode", choices=("tile", "token"), default="token")
     ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--no-decode-graph", dest="decode_graph", action="store_false",
+                    help="run every decode step eagerly instead of replaying a CUDA graph")
     result = run(ap.parse_args())
     if result["rank"] == 0:
         print(json.dumps(result), flush=True)
+    if result["world"] > 1:
+        # communicators whose collectives live in captured graphs are not torn down (that was
+        # seen to block); every rank has synchronised and leaves
+        import sys
+
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
