@@ -57,20 +57,21 @@ bool use_dependent_launch() {
 
 namespace {
 
-constexpr int64_t kStreamMaxRows = 128;  // above this the automatic schedule uses the GEMM
+constexpr int64_t kStreamMaxRows = 128;  // most rows of the streaming cluster kernel (explicit schedules)
+constexpr int64_t kAutoGemmRows = 32;    // above this the automatic schedule uses the GEMM (split-K for few rows)
 constexpr int64_t kDecodeMaxRows = 16;   // the persistent decode kernel handles up to this many rows
 
 bool valid_split(int s) { return s == 0 || s == 1 || s == 2 || s == 4 || s == 8 || s == 16; }
 
 // Kernel families (also the values aq_linear_plan reports):
 //   0 cluster kernel, eight warps per tile, tiles of a split added in increasing k
-//     (explicit split counts and 17..128 rows)
-//   1 tensor-memory GEMM
+//     (explicit split counts, 17..32 rows, forced non-GEMM schedules up to 128 rows)
+//   1 tensor-memory GEMM (K ranges over a cluster where few rows leave SMs idle)
 //   2 persistent stream-K kernel (at most 16 rows, layers with very few tile rows)
 //   3 cluster kernel, one warp per tile (at most 16 rows; the default decode kernel)
 int choose_kernel(int64_t m, int n_j, int n_k, int schedule, int decode_splits) {
   if (schedule == AQ_SCHEDULE_PREFILL_M64) return 1;
-  if (schedule == AQ_SCHEDULE_AUTO && m > kStreamMaxRows) return 1;
+  if (schedule == AQ_SCHEDULE_AUTO && (m > kStreamMaxRows || (decode_splits == 0 && m > kAutoGemmRows))) return 1;
   if (decode_splits != 0 || m > kDecodeMaxRows) return 0;
   if (8 * n_j < num_sms() || !cluster_decode_supported(n_j, n_k)) return 2;
   return 3;
@@ -264,6 +265,8 @@ int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int decode
     if (s > 8) s = 8;
     while (s > n_k) s /= 2;
     *splits = s;  // the launcher may raise it further for very long K; see aq_stream.cu
+  } else if (k == 1) {
+    *splits = tmem_gemm_split(m, n_j, n_k);
   } else if (k == 2) {
     *splits = decode_ctas(n_j, n_k);
     *workers = 16;

@@ -27,6 +27,7 @@
 // Every mbarrier wait is bounded; on a time-out the CTA raises a device status word
 // (read by aq_device_status), stops issuing, gives copies in flight time to land,
 // frees its tensor memory and returns.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include <cstdlib>
@@ -35,6 +36,8 @@
 #include "aq_common.cuh"
 #include "aq_ptx.cuh"
 #include "aq_tile_math.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace aq {
 
@@ -243,6 +246,12 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_k = p.n_k;
+  // split-K over a thread-block cluster along z: this CTA walks K steps [k_begin, k_begin + steps)
+  cg::cluster_group cluster = cg::this_cluster();
+  const int split_k = static_cast<int>(cluster.num_blocks());
+  const int split = static_cast<int>(cluster.block_rank());
+  const int k_begin = static_cast<int>(static_cast<int64_t>(n_k) * split / split_k);
+  const int steps = static_cast<int>(static_cast<int64_t>(n_k) * (split + 1) / split_k) - k_begin;
   const int j0 = blockIdx.x * kTilesN;
   const int tiles_here = min(kTilesN, p.n_j - j0);
   const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kBM;
@@ -270,9 +279,9 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
     mbar_init_fence();
     fence_proxy_async();
   }
-  for (int i = threadIdx.x; i < tiles_here * n_k; i += kThreads) {
-    const int t = i / n_k, kt = i % n_k;
-    rec_smem[t * kMaxNk + kt] = p.records[static_cast<int64_t>(j0 + t) * n_k + kt];
+  for (int i = threadIdx.x; i < tiles_here * steps; i += kThreads) {
+    const int t = i / steps, kt = i % steps;  // kt counts from k_begin everywhere below
+    rec_smem[t * kMaxNk + kt] = p.records[static_cast<int64_t>(j0 + t) * n_k + k_begin + kt];
   }
   if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -297,7 +306,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       const int t = warp;
       const TileRecord* recs = rec_smem + t * kMaxNk;
       uint32_t packed_parity = 0;  // bit s: phase the next wait on packed(s, t) looks for
-      for (int kt = 0; kt < n_k; ++kt) {
+      for (int kt = 0; kt < steps; ++kt) {
         if ((recs[kt].offset_flag & kW4Flag) == 0) continue;
         const int s = kt % kStages;
         int landed = 1;
@@ -342,7 +351,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       // a K step are spread over two warps and kept apart from the widening.
       if (lane == 0) {
         const int t_first = (warp - kFirstCopyWarp) * (TN / 2);
-        for (int kt = 0; kt < n_k; ++kt) {
+        for (int kt = 0; kt < steps; ++kt) {
           const int s = kt % kStages;
           if (kt >= kStages && !mbar_wait(empty(s), ((kt / kStages) - 1) & 1, abort_flag, &g_gemm_status, 1)) break;
           if (warp == kFirstCopyWarp) AQ_GT(1024 + 4 * kt);
@@ -371,7 +380,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       const uint32_t idesc = instr_desc_i8(64 * tiles_here);
       const uint32_t stage0 = smem_u32(stages);
       bool ok = true;
-      for (int kt = 0; kt < n_k; ++kt) {
+      for (int kt = 0; kt < steps; ++kt) {
         const int s = kt % kStages;
         const int b = kt % kAccs;
         if (lane == 0) AQ_GT(4 * kt);
@@ -405,12 +414,12 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
     } else if (warp == kActWarp) {
       // ---------------- activation stream ----------------------------------------------
       if (lane == 0) {
-        for (int kt = 0; kt < n_k; ++kt) {
+        for (int kt = 0; kt < steps; ++kt) {
           const int s = kt % kStages;
           if (kt >= kStages && !mbar_wait(empty(s), ((kt / kStages) - 1) & 1, abort_flag, &g_gemm_status, 3)) break;
           AQ_GT(1024 + 4 * kt + 3);
           mbar_expect_tx(ready(s), kABytes);
-          tensor_copy_2d(smem_u32(stages + s * kStageBytes), &x_map, kt * kTile, static_cast<int>(m0), ready(s));
+          tensor_copy_2d(smem_u32(stages + s * kStageBytes), &x_map, (k_begin + kt) * kTile, static_cast<int>(m0), ready(s));
         }
       }
       __syncwarp();
@@ -459,12 +468,12 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       tc_fence_after();
       tc_ld16(taddr, va);
     }
-    for (int kt = 0; kt < n_k && ok; ++kt) {
+    for (int kt = 0; kt < steps && ok; ++kt) {
       const int b = kt % kAccs;
       const int b_next = (kt + 1) % kAccs;
       const uint32_t col = taddr + static_cast<uint32_t>(b * S::kCols);
       AQ_SUM_BEGIN();
-      const float a_scale = tile_scales != nullptr ? tile_scales[kt] : token_scale;
+      const float a_scale = tile_scales != nullptr ? tile_scales[k_begin + kt] : token_scale;
       TileRecord rec[kTH];
       float scale[kTH];
       int32_t* dump[kTH];
@@ -474,7 +483,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         scale[t] = __fmul_rn(a_scale, rec[t].scale);
         dump[t] = nullptr;
         if (kDump && row_valid && kTH * half + t < tiles_here) {
-          dump[t] = p.acc_dump + ((grow * p.n_j + (j0 + kTH * half + t)) * n_k + kt) * kTile;
+          dump[t] = p.acc_dump + ((grow * p.n_j + (j0 + kTH * half + t)) * n_k + k_begin + kt) * kTile;
         }
       }
 #pragma unroll
@@ -490,9 +499,9 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
           // hand-over would queue behind the MMA thread, which starts issuing at that moment.
           // There is no dead-lock: the MMA of step kt+1 never needs the accumulator of step kt.
           AQ_SUM_MARK(0);
-          if (kt + 1 < n_k) ok = warp_wait(acc_full(b_next), ((kt + 1) / kAccs) & 1, lane, abort_flag);
+          if (kt + 1 < steps) ok = warp_wait(acc_full(b_next), ((kt + 1) / kAccs) & 1, lane, abort_flag);
           AQ_SUM_MARK(3);
-          if (kt + 1 < n_k && ok) {
+          if (kt + 1 < steps && ok) {
             tc_fence_after();
             tc_ld16(taddr + static_cast<uint32_t>(b_next * S::kCols), next);
           }
@@ -509,7 +518,22 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
     AQ_SUM_WRITE(3500 + (warp - kFirstDrainWarp) * 4);
 
     // ---------------- epilogue: rows through shared memory, coalesced stores --------
-    if (ok) {
+    if (split_k > 1) {
+      // split-K: the CTA's FP32 tile goes to shared memory (over the stage ring, rows padded by
+      // one float so that a warp writing one row per lane hits 32 banks) for the exchange below
+      float* xchg = reinterpret_cast<float*>(stages);
+#pragma unroll
+      for (int t = 0; t < kTH; ++t) {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          float lo, hi;
+          unpack2(acc[t * 32 + c], lo, hi);
+          float* dst = xchg + row * (S::kCols + 1) + (kTH * half + t) * kTile + 2 * c;
+          dst[0] = lo;
+          dst[1] = hi;
+        }
+      }
+    } else if (ok) {
       float* region = reinterpret_cast<float*>(stages) + (warp - kFirstDrainWarp) * (32 * kEpiRowFloats);
       const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
 #pragma unroll
@@ -542,6 +566,56 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         }
       }
     }
+  }
+
+  if (split_k > 1) {
+    // ---------------- split-K exchange through cluster shared memory ------------------------
+    // CTA r of the cluster finishes rows r, r + split_k, ...: it adds the split sums in split
+    // order (the reference reducer's order, linear.cu:1339-1343), applies the inverse output
+    // transform and stores.  The second barrier keeps every CTA's tile alive until read.
+    cluster.sync();
+    if (warp >= kFirstDrainWarp) {
+      const float* xchg = reinterpret_cast<const float*>(stages);
+      const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
+      const float* remote[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s) remote[s] = cluster.map_shared_rank(xchg, s < split_k ? s : 0);
+      const int64_t rows_left = p.m - m0 - split;  // owned rows: split, split + split_k, ... below p.m
+      const int owned = rows_left <= 0 ? 0
+                        : static_cast<int>(((rows_left < kBM - split ? rows_left : kBM - split) + split_k - 1) / split_k);
+      const int pairs = owned * tiles_here;  // (row, weight tile row) pairs, dealt to the drain warps
+      for (int q = warp - kFirstDrainWarp; q < pairs; q += kDrainWarps) {
+        const int row = split + split_k * (q / tiles_here);
+        const int tl = q % tiles_here;
+        const int offset = row * (S::kCols + 1) + tl * kTile + lane;
+        // all remote loads of the pair are issued before the first add
+        float a[8], b[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          a[s] = 0.0f;
+          b[s] = 0.0f;
+          if (s < split_k) {
+            a[s] = remote[s][offset];
+            b[s] = remote[s][offset + 32];
+          }
+        }
+        float lo = a[0], hi = b[0];
+#pragma unroll
+        for (int s = 1; s < 8; ++s) {
+          if (s < split_k) {
+            lo = __fadd_rn(lo, a[s]);
+            hi = __fadd_rn(hi, b[s]);
+          }
+        }
+        const int j = j0 + tl;
+        const int32_t* meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
+        if (meta != nullptr && meta[0] != 0) inverse_u_row(lo, hi, meta, lane);
+        const int64_t o = (m0 + row) * n_cols + static_cast<int64_t>(j) * kTile + lane;
+        store_any(p.out, p.out_dtype, o, lo);
+        store_any(p.out, p.out_dtype, o + 32, hi);
+      }
+    }
+    cluster.sync();
   }
 
   tc_fence_before();
@@ -592,7 +666,7 @@ int encode_activation_map(CUtensorMap* map, const int8_t* xq, int64_t m, int64_t
 }
 
 template <int TN>
-int launch_shape(const CUtensorMap& x_map, const GemmParams& p, bool dump, int device, cudaStream_t stream) {
+int launch_shape(const CUtensorMap& x_map, const GemmParams& p, bool dump, int split, int device, cudaStream_t stream) {
   static std::once_flag once[64];
   cudaError_t attr_status = cudaSuccess;
   std::call_once(once[device & 63], [&] {
@@ -605,29 +679,72 @@ int launch_shape(const CUtensorMap& x_map, const GemmParams& p, bool dump, int d
   });
   int rc = check_cuda(attr_status, "cudaFuncSetAttribute(tmem_gemm_kernel)");
   if (rc != AQ_OK) return rc;
-  const dim3 grid(static_cast<unsigned>((p.n_j + TN - 1) / TN), static_cast<unsigned>((p.m + kBM - 1) / kBM));
-  if (dump) {
-    tmem_gemm_kernel<TN, true><<<grid, kThreads, Shape<TN>::kSmemBytes, stream>>>(x_map, p);
-  } else {
-    tmem_gemm_kernel<TN, false><<<grid, kThreads, Shape<TN>::kSmemBytes, stream>>>(x_map, p);
-  }
-  return check_cuda(cudaGetLastError(), "tensor-memory GEMM launch");
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>((p.n_j + TN - 1) / TN), static_cast<unsigned>((p.m + kBM - 1) / kBM),
+                        static_cast<unsigned>(split));
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = static_cast<size_t>(Shape<TN>::kSmemBytes);
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = static_cast<unsigned>(split);
+  config.attrs = attr;
+  config.numAttrs = 1;
+  const cudaError_t status = dump ? cudaLaunchKernelEx(&config, tmem_gemm_kernel<TN, true>, x_map, p)
+                                  : cudaLaunchKernelEx(&config, tmem_gemm_kernel<TN, false>, x_map, p);
+  return check_cuda(status, "tensor-memory GEMM launch");
 }
 
-}  // namespace
-
-int64_t tmem_gemm_workspace_bytes(int64_t, int, int) { return 0; }
+int device_sm_count(int* count) {
+  int device = 0;
+  int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
+  if (rc != AQ_OK) return rc;
+  static int sm_counts[64] = {0};
+  if (sm_counts[device & 63] == 0) {
+    int value = 0;
+    rc = check_cuda(cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute");
+    if (rc != AQ_OK) return rc;
+    sm_counts[device & 63] = value;
+  }
+  *count = sm_counts[device & 63];
+  return AQ_OK;
+}
 
 // Width of the CTA tile in weight tile rows: 256 columns, or 128 columns where the wider
 // grid would occupy at most half of the SMs (measured cross-over on the decoder shapes).
 // ALIGNQUANT_B200_GEMM_TILE=2|4 forces one of them (for tests and measurements).
-int tmem_gemm_tile_rows(int64_t m, int n_j, int sm_count) {
+int tile_rows(int64_t m, int n_j, int sm_count) {
   if (const char* forced = std::getenv("ALIGNQUANT_B200_GEMM_TILE")) {
     if (forced[0] == '2') return 2;
     if (forced[0] == '4') return 4;
   }
   const int64_t wide_ctas = ((m + kBM - 1) / kBM) * ((n_j + 3) / 4);
   return 2 * wide_ctas <= sm_count ? 2 : 4;
+}
+
+}  // namespace
+
+int64_t tmem_gemm_workspace_bytes(int64_t, int, int) { return 0; }
+
+// Number of K ranges (cluster size along z): more than one only where the output tiles alone
+// would leave at least half of the SMs idle (few rows), at least four K steps per range.
+// ALIGNQUANT_B200_GEMM_SPLIT=1..8 forces a value (for tests and measurements).
+int tmem_gemm_split(int64_t m, int n_j, int n_k) {
+  int sm_count = 148;
+  if (device_sm_count(&sm_count) != AQ_OK) sm_count = 148;
+  int split = 1;
+  if (const char* forced = std::getenv("ALIGNQUANT_B200_GEMM_SPLIT")) {
+    split = forced[0] - '0';
+    if (split < 1 || split > 8) split = 1;
+  } else {
+    const int tn = tile_rows(m, n_j, sm_count);
+    const int64_t ctas = ((m + kBM - 1) / kBM) * ((n_j + tn - 1) / tn);
+    if (2 * ctas <= sm_count) split = static_cast<int>(sm_count / ctas < 8 ? sm_count / ctas : 8);
+  }
+  while (split > 1 && n_k / split < 4) --split;
+  return split;
 }
 
 int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
@@ -638,13 +755,9 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   int device = 0;
   int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
   if (rc != AQ_OK) return rc;
-  static int sm_counts[64] = {0};
-  if (sm_counts[device & 63] == 0) {
-    int count = 0;
-    rc = check_cuda(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device), "cudaDeviceGetAttribute");
-    if (rc != AQ_OK) return rc;
-    sm_counts[device & 63] = count;
-  }
+  int sm_count = 0;
+  rc = device_sm_count(&sm_count);
+  if (rc != AQ_OK) return rc;
   if (a.m >= (1LL << 31)) return fail(AQ_ERR_INVALID, "the GEMM kernel supports fewer than 2^31 rows");
   alignas(64) CUtensorMap x_map;
   rc = encode_activation_map(&x_map, a.xq, a.m, static_cast<int64_t>(a.n_k) * kTile);
@@ -662,9 +775,9 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   p.scale_mode = a.scale_mode;
   p.out_dtype = a.out_dtype;
   const bool dump = a.acc_dump != nullptr;
-  return tmem_gemm_tile_rows(a.m, a.n_j, sm_counts[device & 63]) == 4
-             ? launch_shape<4>(x_map, p, dump, device, stream)
-             : launch_shape<2>(x_map, p, dump, device, stream);
+  const int split = tmem_gemm_split(a.m, a.n_j, a.n_k);
+  return tile_rows(a.m, a.n_j, sm_count) == 4 ? launch_shape<4>(x_map, p, dump, split, device, stream)
+                                             : launch_shape<2>(x_map, p, dump, split, device, stream);
 }
 
 #ifdef AQ_TRACE

@@ -178,7 +178,8 @@ AQ_API int aq_linear_decode_static(const int8_t* xq, const float* act_scales, in
  *               [n_k*s/splits, n_k*(s+1)/splits), tiles of a range added in increasing k,
  *               range sums added in range order (the reference's split-K order,
  *               alignquant/kernels/cuda/linear.cu:1237-1238, 1339-1343)
- *            1  tensor-memory GEMM: one range, increasing k
+ *            1  tensor-memory GEMM: like 0 (K tiles cut into *splits ranges, split sums added in
+ *               split order); *splits is 1 unless few rows would leave most SMs idle
  *            2  persistent stream-K kernel: the (j, k)-ordered tile sequence cut into
  *               *splits contiguous ranges [i*T/splits, (i+1)*T/splits); inside a range
  *               tile t goes to accumulator (t - range begin) % *workers

@@ -89,7 +89,7 @@ def _run_linear(ext, xq, a_s, weights, u_meta, m, n_j, n_k, **kw):
 
 
 @pytest.mark.parametrize("scale_mode", ["tile", "token"])
-@pytest.mark.parametrize("m", [1, 4, 16, 17, 64, 128])
+@pytest.mark.parametrize("m", [1, 4, 16, 17, 32, 33, 64, 128])
 @pytest.mark.parametrize("n,k", [(64, 64), (128, 192), (192, 512)])
 def test_stream_linear_matches_oracle(ext, n, k, m, scale_mode):
     n_j, n_k = n // 64, k // 64
@@ -116,13 +116,13 @@ def test_stream_linear_matches_oracle(ext, n, k, m, scale_mode):
         if split:
             want = oc.linear_fp32_c(xq_np, a_mk, tiles, scales, split)
             assert np.array_equal(got, want), f"fp32 result not in reference operation order (split {split})"
-        elif m <= 16:  # automatic schedule: decode kernels, sums grouped as the library's plan says
+        elif m <= 32:  # automatic schedule: decode kernels, sums grouped as the library's plan says
             want = helpers.planned_fp32(ext, xq_np, a_mk, tiles, scales, m, n_j, n_k, schedule=schedule)
             assert np.array_equal(got, want), "fp32 result differs from the planned summation order"
         assert np.allclose(got, y64, rtol=REL, atol=ABS)
 
 
-@pytest.mark.parametrize("m", [1, 7, 8, 16])
+@pytest.mark.parametrize("m", [1, 7, 8, 16, 24, 32])
 @pytest.mark.parametrize("n,k", [(3072, 3072), (1024, 8192), (5120, 256), (16384, 1024), (640, 4096)])
 def test_decode_kernel_many_ranges(ext, n, k, m):
     """Layers with more tiles than SMs through both decode kernels (few tile rows: the

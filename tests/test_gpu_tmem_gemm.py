@@ -49,7 +49,8 @@ def test_gemm_matches_oracle(ext, n, k, m, scale_mode):
     xq_np = xq.cpu().numpy()
     assert np.array_equal(dump.cpu().numpy(), oc.tile_accumulators_c(xq_np, tiles)), "int32 tile accumulators differ"
     got = out.cpu().numpy()
-    assert np.array_equal(got, oc.linear_fp32_c(xq_np, a_mk, tiles, scales, 1)), "fp32 not in reference operation order"
+    want = helpers.planned_fp32(ext, xq_np, a_mk, tiles, scales, m, n_j, n_k, schedule="forced_prefill_m64")
+    assert np.array_equal(got, want), "fp32 not in reference operation order"
     assert np.allclose(got, oc.dequant_matmul_fp64(xq_np, a_mk, tiles, scales), rtol=REL, atol=ABS)
 
 
@@ -59,7 +60,8 @@ def test_gemm_uniform_precision_layers(ext, fraction):
     weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "token", seed=3, fraction=fraction)
     out = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill_m64", scale_mode="token")
     ext.device_status()
-    assert np.array_equal(out.cpu().numpy(), oc.linear_fp32_c(xq.cpu().numpy(), a_mk, tiles, scales, 1))
+    want = helpers.planned_fp32(ext, xq.cpu().numpy(), a_mk, tiles, scales, m, n // 64, k // 64, schedule="forced_prefill_m64")
+    assert np.array_equal(out.cpu().numpy(), want)
 
 
 def test_gemm_auto_schedule_bf16_output_and_bounds(ext):
@@ -70,7 +72,7 @@ def test_gemm_auto_schedule_bf16_output_and_bounds(ext):
                                          output_dtype=torch.bfloat16, out=canvas[1 : m + 1])
     ext.device_status()
     assert bool((canvas[0] == 77.0).all()) and bool((canvas[m + 1] == 77.0).all())
-    want = torch.from_numpy(oc.linear_fp32_c(xq.cpu().numpy(), a_mk, tiles, scales, 1)).to(torch.bfloat16)
+    want = torch.from_numpy(helpers.planned_fp32(ext, xq.cpu().numpy(), a_mk, tiles, scales, m, n // 64, k // 64)).to(torch.bfloat16)
     assert torch.equal(out.cpu(), want)
 
 
@@ -93,8 +95,12 @@ def test_gemm_reference_fixture_with_output_transform(ext, golden_dir):
 def test_gemm_agrees_with_streaming_kernel_bit_for_bit(ext):
     m, n, k = 96, 256, 384
     weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "tile", seed=8)
+    splits = ext.linear_plan(m, n // 64, k // 64, schedule="forced_prefill_m64")["splits"]
     a = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill_m64")
-    b = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill", decode_splits=1)
+    b = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill",
+                                       decode_splits=splits if splits in (1, 2, 4, 8) else 1)
+    if splits not in (1, 2, 4, 8):
+        pytest.skip(f"the GEMM chose {splits} K ranges, which the streaming kernel cannot be forced to")
     ext.device_status()
     assert torch.equal(a, b)
 
@@ -111,6 +117,24 @@ def test_gemm_both_cta_tile_widths(ext, monkeypatch, tile_rows):
     ext.device_status()
     xq_np = xq.cpu().numpy()
     assert np.array_equal(dump.cpu().numpy(), oc.tile_accumulators_c(xq_np, tiles))
-    want = oc.linear_fp32_c(xq_np, a_mk, tiles, scales, 1)
+    want = helpers.planned_fp32(ext, xq_np, a_mk, tiles, scales, m, n // 64, k // 64, schedule="forced_prefill_m64")
     assert np.array_equal(out.cpu().numpy(), want)
     assert np.array_equal(plain.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("split", ["2", "3", "8"])
+@pytest.mark.parametrize("m", [40, 128, 200])
+def test_gemm_split_k_clusters(ext, monkeypatch, m, split):
+    """K ranges over a thread-block cluster: integer sums exact, FP32 in split order, output transform applied."""
+    monkeypatch.setenv("ALIGNQUANT_B200_GEMM_SPLIT", split)
+    n, k = 320, 2048
+    weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "tile", seed=77 + m)
+    n_j, n_k = n // 64, k // 64
+    plan = ext.linear_plan(m, n_j, n_k, schedule="forced_prefill_m64")
+    assert plan["kernel"] == 1 and plan["splits"] == int(split)
+    dump = torch.zeros((m, n_j, n_k, 64), dtype=torch.int32, device="cuda")
+    out = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill_m64", acc_dump=dump)
+    ext.device_status()
+    xq_np = xq.cpu().numpy()
+    assert np.array_equal(dump.cpu().numpy(), oc.tile_accumulators_c(xq_np, tiles))
+    assert np.array_equal(out.cpu().numpy(), oc.linear_fp32_c(xq_np, a_mk, tiles, scales, int(split)))
