@@ -60,21 +60,23 @@ namespace {
 constexpr int64_t kStreamMaxRows = 128;  // most rows of the streaming cluster kernel (explicit schedules)
 constexpr int64_t kAutoGemmRows = 32;    // above this the automatic schedule uses the GEMM (split-K for few rows)
 constexpr int64_t kDecodeMaxRows = 16;   // the persistent decode kernel handles up to this many rows
+constexpr int64_t kClusterMaxRows = 32;  // the warp-per-tile cluster kernel handles up to this many rows
 
 bool valid_split(int s) { return s == 0 || s == 1 || s == 2 || s == 4 || s == 8 || s == 16; }
 
 // Kernel families (also the values aq_linear_plan reports):
 //   0 cluster kernel, eight warps per tile, tiles of a split added in increasing k
-//     (explicit split counts, 17..32 rows, forced non-GEMM schedules up to 128 rows)
+//     (explicit split counts, forced non-GEMM schedules up to 128 rows)
 //   1 tensor-memory GEMM (K ranges over a cluster where few rows leave SMs idle)
 //   2 persistent stream-K kernel (at most 16 rows, layers with very few tile rows)
-//   3 cluster kernel, one warp per tile (at most 16 rows; the default decode kernel)
+//   3 cluster kernel, one warp (two for 17..32 rows) per tile; the default decode kernel
 int choose_kernel(int64_t m, int n_j, int n_k, int schedule, int decode_splits) {
   if (schedule == AQ_SCHEDULE_PREFILL_M64) return 1;
   if (schedule == AQ_SCHEDULE_AUTO && (m > kStreamMaxRows || (decode_splits == 0 && m > kAutoGemmRows))) return 1;
-  if (decode_splits != 0 || m > kDecodeMaxRows) return 0;
-  if (8 * n_j < num_sms() || !cluster_decode_supported(n_j, n_k)) return 2;
-  return 3;
+  if (decode_splits != 0 || m > kClusterMaxRows) return 0;
+  const bool cluster_ok = cluster_decode_supported(n_j, n_k);
+  if (m <= kDecodeMaxRows && (8 * n_j < num_sms() || !cluster_ok)) return 2;
+  return cluster_ok ? 3 : 0;
 }
 
 }  // namespace

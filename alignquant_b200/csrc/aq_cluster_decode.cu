@@ -1,4 +1,4 @@
-// Decode kernel for at most 16 rows: one CTA per (tile row j, K split), split-K partial
+// Decode kernel for at most 32 rows: one CTA per (tile row j, K split), split-K partial
 // sums exchanged through the distributed shared memory of a thread-block cluster.
 //
 // This is the default small-M kernel.  It combines the two things that matter at decode
@@ -70,13 +70,14 @@ struct Params {
 constexpr int kGroupTiles = 8;  // tiles per ring slot
 constexpr int kSlots = 2;
 constexpr int kSlotBytes = kGroupTiles * kW8TileBytes;
-constexpr int kConsumerWarps = 8;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kTileWorkers = 8;  // tiles in progress per CTA; WPT warps share one tile (16 rows each)
 constexpr int kMaxCount = 512;  // tiles of one CTA's K range
 constexpr int kNumBars = 2 * kSlots;
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+template <int kConsumerThreads>
+__device__ __forceinline__ void consumer_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
 
 // Shared memory: [ring kSlots x 32 KiB][slabs 8 x (8*NT) x 64 f32][tile (8*NT) x 64 f32]
 //                [records kMaxCount][barriers][abort flag]
@@ -84,15 +85,21 @@ __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;
 // consumed (measured 4-5 % faster at M = 16: more shared memory left for the L1); with up to
 // 8 rows the extra barrier that this needs costs more than it gives, so the slabs keep their
 // own 16 KiB.
-template <int NT>
-__global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Params p) {
+// For 17..32 rows two warps share every tile (WPT = 2): warp 2t takes rows 0..15 and warp
+// 2t+1 rows 16..31 of tile worker t, so the weights are still streamed once.
+template <int NT, int WPT>
+__global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 1) cluster_decode_kernel(const Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int kRows = 8 * NT;
+  constexpr int kConsumerWarps = kTileWorkers * WPT;
+  constexpr int kConsumerThreads = kConsumerWarps * 32;
+  constexpr int kThreads = kConsumerThreads + 32;
+  constexpr int kWarpRows = 8 * NT;      // rows one warp accumulates
+  constexpr int kRows = kWarpRows * WPT;  // rows of the CTA
   constexpr bool kSlabsInRing = NT == 2;
-  static_assert(kConsumerWarps * kRows * kTile * 4 <= kSlots * kSlotBytes, "slabs must fit into the ring");
+  static_assert(kTileWorkers * kRows * kTile * 4 <= kSlots * kSlotBytes, "slabs must fit into the ring");
   uint8_t* ring = smem;
   float* slabs = reinterpret_cast<float*>(smem + (kSlabsInRing ? 0 : kSlots * kSlotBytes));
-  float* tile = reinterpret_cast<float*>(smem + kSlots * kSlotBytes) + (kSlabsInRing ? 0 : kConsumerWarps * kRows * kTile);
+  float* tile = reinterpret_cast<float*>(smem + kSlots * kSlotBytes) + (kSlabsInRing ? 0 : kTileWorkers * kRows * kTile);
   TileRecord* recs = reinterpret_cast<TileRecord*>(tile + kRows * kTile);
   uint64_t* bars = reinterpret_cast<uint64_t*>(recs + kMaxCount);
   volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(bars + kNumBars);
@@ -103,6 +110,8 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
   const int j = blockIdx.x;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int worker = warp / WPT;                  // which of the eight tiles in progress
+  const int row0 = (warp % WPT) * kWarpRows;      // first row this warp accumulates
   const int n_k = p.n_k;
   const int k_begin = static_cast<int>(static_cast<int64_t>(n_k) * split / split_k);
   const int k_end = static_cast<int>(static_cast<int64_t>(n_k) * (split + 1) / split_k);
@@ -124,7 +133,7 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(full(s), 1);
-      mbar_init(empty(s), kGroupTiles);
+      mbar_init(empty(s), kGroupTiles * WPT);  // every warp working on a tile arrives
     }
     *abort_flag = 0;
     mbar_init_fence();
@@ -133,7 +142,7 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
   __syncthreads();
 
   const TileRecord* my_records = p.records + static_cast<int64_t>(j) * n_k + k_begin;
-  const bool producer = warp == kConsumerWarps;
+  const bool producer = warp == kConsumerWarps;  // the last warp
 
   // First ring fill before the grid dependency is resolved: weights are static.
   if (producer && lane < kSlots && lane < groups) {
@@ -182,16 +191,16 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
     const int8_t* x_lane[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const int tok = nt * 8 + 2 * c;
+      const int tok = row0 + nt * 8 + 2 * c;
       token_scale[nt][0] = (p.scale_mode == AQ_SCALE_TOKEN && tok < rows) ? p.act_scales[tok] : 0.0f;
       token_scale[nt][1] = (p.scale_mode == AQ_SCALE_TOKEN && tok + 1 < rows) ? p.act_scales[tok + 1] : 0.0f;
-      x_lane[nt] = p.xq + static_cast<int64_t>(nt * 8 + g) * k_bytes + static_cast<int64_t>(k_begin) * kTile + c * 16;
+      x_lane[nt] = p.xq + static_cast<int64_t>(row0 + nt * 8 + g) * k_bytes + static_cast<int64_t>(k_begin) * kTile + c * 16;
     }
     auto load_x = [&](int i, uint4 (&x)[NT]) {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         x[nt] = make_uint4(0, 0, 0, 0);
-        if (nt * 8 + g < rows) x[nt] = ldg_x(x_lane[nt] + static_cast<int64_t>(i) * kTile);
+        if (row0 + nt * 8 + g < rows) x[nt] = ldg_x(x_lane[nt] + static_cast<int64_t>(i) * kTile);
       }
     };
 
@@ -205,17 +214,17 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
       }
     }
     uint4 x_next[NT];
-    if (warp < count) load_x(warp, x_next);  // activation vectors are requested one tile ahead
-    for (int i = warp; i < count; i += kConsumerWarps) {
+    if (worker < count) load_x(worker, x_next);  // activation vectors are requested one tile ahead
+    for (int i = worker; i < count; i += kTileWorkers) {
       const int gi = i / kGroupTiles;
       const int slot = gi % kSlots;
       const int kt = k_begin + i;
       uint4 x[NT];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) x[nt] = x_next[nt];
-      if (i + kConsumerWarps < count) load_x(i + kConsumerWarps, x_next);
+      if (i + kTileWorkers < count) load_x(i + kTileWorkers, x_next);
       if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_cluster_decode_status, 32)) break;
-      if (i == warp) AQ_CT(3);
+      if (i == worker) AQ_CT(3);
       const TileRecord rec = recs[i];
       const TileRecord rec0 = recs[gi * kGroupTiles];
       const bool is_w4 = (rec.offset_flag & kW4Flag) != 0;
@@ -245,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
           s1 = __fmul_rn(token_scale[nt][1], rec.scale);
         } else {
           // tokens 8*nt .. 8*nt+7 share the scale of their 16-row group
-          const float a_s = (nt * 8 < rows) ? p.act_scales[static_cast<int64_t>(nt >> 1) * n_k + kt] : 0.0f;
+          const float a_s = (row0 + nt * 8 < rows) ? p.act_scales[static_cast<int64_t>((row0 + nt * 8) >> 4) * n_k + kt] : 0.0f;
           s0 = s1 = __fmul_rn(a_s, rec.scale);
         }
 #pragma unroll
@@ -257,7 +266,7 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
         }
         if (p.acc_dump != nullptr) {
           const int shift = is_w4 ? 4 : 0;
-          const int tok = nt * 8 + 2 * c;
+          const int tok = row0 + nt * 8 + 2 * c;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
 #pragma unroll
@@ -274,11 +283,11 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
     }
     AQ_CT(4);
     // ---- combine the eight warp sums in warp order -----------------------------------------
-    if (kSlabsInRing) consumer_sync();  // every warp has consumed its last tile: the ring becomes the slabs
-    float* slab = slabs + warp * kRows * kTile;
+    if (kSlabsInRing) consumer_sync<kConsumerThreads>();  // every warp has consumed its last tile: the ring becomes the slabs
+    float* slab = slabs + worker * kRows * kTile;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      const int tok = nt * 8 + 2 * c;
+      const int tok = row0 + nt * 8 + 2 * c;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         slab[tok * kTile + q * 16 + g] = acc[nt][q][0];
@@ -287,11 +296,11 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
         slab[(tok + 1) * kTile + q * 16 + g + 8] = acc[nt][q][3];
       }
     }
-    consumer_sync();
+    consumer_sync<kConsumerThreads>();
     for (int e = threadIdx.x; e < kRows * kTile; e += kConsumerThreads) {
       float v = slabs[e];
 #pragma unroll
-      for (int w = 1; w < kConsumerWarps; ++w) v = __fadd_rn(v, slabs[w * kRows * kTile + e]);
+      for (int w = 1; w < kTileWorkers; ++w) v = __fadd_rn(v, slabs[w * kRows * kTile + e]);
       tile[e] = v;
     }
   }
@@ -305,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
     const bool has_u = meta != nullptr && meta[0] != 0;
     const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
     // rank r finishes rows r, r + split_k, ...; its warps take them round robin
-    for (int row = split + split_k * warp; row < rows; row += split_k * kConsumerWarps) {
+    for (int row = split + split_k * warp; row < rows; row += split_k * kConsumerWarps) {  // all consumer warps
       float lo = 0.0f, hi = 0.0f;
       for (int s = 0; s < split_k; ++s) {
         const float* remote = cluster.map_shared_rank(tile, s);
@@ -325,28 +334,42 @@ __global__ void __launch_bounds__(kThreads, 2) cluster_decode_kernel(const Param
   AQ_CT(8);
 }
 
-int smem_bytes(int nt) {
-  const int slabs = nt == 2 ? 0 : kConsumerWarps * 8 * nt * kTile * 4;  // NT = 2 keeps them in the ring
-  return kSlots * kSlotBytes + slabs + 8 * nt * kTile * 4 + kMaxCount * 8 + kNumBars * 8 + 16;
+// Kernel variants by row count: up to 8 rows <1,1>, up to 16 <2,1>, up to 32 <2,2>.
+struct Variant {
+  int nt;
+  int wpt;
+};
+Variant variant_for(int64_t m) { return m <= 8 ? Variant{1, 1} : m <= 16 ? Variant{2, 1} : Variant{2, 2}; }
+int variant_index(const Variant& v) { return v.wpt == 2 ? 2 : v.nt - 1; }
+int variant_threads(const Variant& v) { return 32 * (kTileWorkers * v.wpt + 1); }
+const void* variant_kernel(const Variant& v) {
+  if (v.wpt == 2) return reinterpret_cast<const void*>(cluster_decode_kernel<2, 2>);
+  return v.nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1, 1>)
+                   : reinterpret_cast<const void*>(cluster_decode_kernel<2, 1>);
 }
 
-template <int NT>
-int launch_nt(const Params& p, int split_k, cudaStream_t stream) {
-  static std::once_flag once[64];
+int smem_bytes(const Variant& v) {
+  const int rows = 8 * v.nt * v.wpt;
+  const int slabs = v.nt == 2 ? 0 : kTileWorkers * rows * kTile * 4;  // NT = 2 keeps them in the ring
+  return kSlots * kSlotBytes + slabs + rows * kTile * 4 + kMaxCount * 8 + kNumBars * 8 + 16;
+}
+
+int launch_variant(const Variant& v, const Params& p, int split_k, cudaStream_t stream) {
+  static std::once_flag once[64][3];
   int device = 0;
   int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
   if (rc != AQ_OK) return rc;
+  const void* kernel = variant_kernel(v);
   cudaError_t attr_status = cudaSuccess;
-  std::call_once(once[device & 63], [&] {
-    attr_status = cudaFuncSetAttribute(cluster_decode_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       smem_bytes(NT));
+  std::call_once(once[device & 63][variant_index(v)], [&] {
+    attr_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(v));
   });
   rc = check_cuda(attr_status, "cudaFuncSetAttribute(cluster_decode_kernel)");
   if (rc != AQ_OK) return rc;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(static_cast<unsigned>(p.n_j), static_cast<unsigned>(split_k), 1);
-  config.blockDim = dim3(kThreads, 1, 1);
-  config.dynamicSmemBytes = static_cast<size_t>(smem_bytes(NT));
+  config.blockDim = dim3(static_cast<unsigned>(variant_threads(v)), 1, 1);
+  config.dynamicSmemBytes = static_cast<size_t>(smem_bytes(v));
   config.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -357,30 +380,31 @@ int launch_nt(const Params& p, int split_k, cudaStream_t stream) {
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = use_dependent_launch() ? 2 : 1;
-  return check_cuda(cudaLaunchKernelEx(&config, cluster_decode_kernel<NT>, p), "cluster decode launch");
+  Params params = p;
+  void* args[] = {&params};
+  return check_cuda(cudaLaunchKernelExC(&config, kernel, args), "cluster decode launch");
 }
 
 }  // namespace
 
 namespace {
 
-// How many clusters of `split` CTAs of the NT-variant can be resident at once on the
-// current device (0 when the query fails); cached per device.
-int max_active_clusters(int nt, int split) {
+// How many clusters of `split` CTAs of a variant can be resident at once on the current
+// device (0 when the query fails); cached per device.
+int max_active_clusters(const Variant& v, int split) {
   static std::mutex mutex;
-  static int cache[64][2][9];  // [device][nt - 1][split], 0 = not queried yet, -1 = failed
+  static int cache[64][3][9];  // [device][variant][split], 0 = not queried yet, -1 = failed
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
   std::lock_guard<std::mutex> lock(mutex);
-  int& slot = cache[device][nt - 1][split];
+  int& slot = cache[device][variant_index(v)][split];
   if (slot == 0) {
-    const void* kernel = nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1>)
-                                 : reinterpret_cast<const void*>(cluster_decode_kernel<2>);
-    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(nt));
+    const void* kernel = variant_kernel(v);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(v));
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(1, static_cast<unsigned>(split), 1);
-    config.blockDim = dim3(kThreads, 1, 1);
-    config.dynamicSmemBytes = static_cast<size_t>(smem_bytes(nt));
+    config.blockDim = dim3(static_cast<unsigned>(variant_threads(v)), 1, 1);
+    config.dynamicSmemBytes = static_cast<size_t>(smem_bytes(v));
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
@@ -398,11 +422,12 @@ int max_active_clusters(int nt, int split) {
 
 }  // namespace
 
-// Largest split (cluster size, at most 8) for which the grid is at most two CTAs per SM and
-// all n_j clusters are resident at once, so that every CTA streams from the start; never
-// shorter than one tile per CTA and never longer than the record buffer.
+// Largest split (cluster size, at most 8) for which the grid is at most two CTAs per SM (one
+// for the 32-row variant, whose CTAs fill an SM) and all n_j clusters are resident at once, so
+// that every CTA streams from the start; never shorter than one tile per CTA and never longer
+// than the record buffer.
 int cluster_decode_split(int64_t m, int n_j, int n_k) {
-  const int nt = m <= 8 ? 1 : 2;
+  const Variant v = variant_for(m);
   static int sm_count[64] = {0};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) device = 0;
@@ -411,9 +436,10 @@ int cluster_decode_split(int64_t m, int n_j, int n_k) {
     if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) count = 148;
     sm_count[device] = count;
   }
+  const int64_t cta_limit = (v.wpt == 2 ? 1LL : 2LL) * sm_count[device];
   int split = 1;
   for (int s = 2; s <= 8 && s <= n_k; ++s) {
-    if (static_cast<int64_t>(n_j) * s <= 2LL * sm_count[device] && max_active_clusters(nt, s) >= n_j) split = s;
+    if (static_cast<int64_t>(n_j) * s <= cta_limit && max_active_clusters(v, s) >= n_j) split = s;
   }
   while (split < 8 && (n_k + split - 1) / split > kMaxCount) ++split;
   return split;
@@ -436,7 +462,7 @@ int launch_cluster_decode(const LinearArgs& a, cudaStream_t stream) {
   p.scale_mode = a.scale_mode;
   p.out_dtype = a.out_dtype;
   const int split = cluster_decode_split(a.m, a.n_j, a.n_k);
-  return a.m <= 8 ? launch_nt<1>(p, split, stream) : launch_nt<2>(p, split, stream);
+  return launch_variant(variant_for(a.m), p, split, stream);
 }
 
 #ifdef AQ_TRACE
