@@ -53,6 +53,26 @@ def test_token_quantizer_bit_exact(ext, m, k, dtype):
     assert np.array_equal(q.cpu().numpy(), q_ref)
 
 
+@pytest.mark.parametrize("k", [4096, 8192, 16384])
+def test_token_quantizer_rounding_boundaries(ext, k):
+    """Quotients on and next to .5 boundaries, long rows (register path and re-read path)."""
+    rng = np.random.default_rng(k)
+    rows = []
+    for amax in (127.0, 100.0, 3.1415927, 0.017, 65504.0):
+        scale = np.float32(amax) / np.float32(127.0)
+        targets = (rng.integers(-127, 127, size=k).astype(np.float32) + np.float32(0.5))
+        x = (targets * scale).astype(np.float32)
+        x += rng.choice(np.array([0.0, 1.0, -1.0, 2.0, -2.0], dtype=np.float32), size=k) * np.spacing(x)
+        x[0] = amax
+        rows.append(np.clip(x, -amax, amax))
+    x = np.stack(rows).astype(np.float32)
+    xt = torch.from_numpy(x).cuda()
+    q, s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode="token")
+    q_ref, s_ref = oc.a8_token_quantize(x)
+    assert np.array_equal(s.cpu().numpy(), s_ref)
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("m,k", [(1, 64), (4, 192), (16, 3072), (17, 128), (130, 256)])
 def test_tile_quantizer_bit_exact_identity(ext, m, k, dtype):
