@@ -95,6 +95,7 @@ int64_t decode_static_scratch_bytes();
 int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream);
 int64_t tmem_gemm_workspace_bytes(int64_t m, int n_j, int n_k);
 int tmem_gemm_split(int64_t m, int n_j, int n_k);  // K ranges (cluster size) the GEMM will use
+
 // Sum of per-rank partial outputs through peer memory (one node, one process per GPU).
 int launch_allreduce(const float* partial, float* out, int64_t count, int rank, int world, void* const* peer_buffers,
                      int64_t max_count, cudaStream_t stream);

@@ -164,18 +164,17 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
   auto acc_empty = [&](int b) { return bar0 + 8u * ((2 + TN) * kStages + kAccs + b); };
   const uint32_t final_bar = bar0 + 8u * ((2 + TN) * kStages + 2 * kAccs);
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(ready(s), static_cast<uint32_t>(tiles_here) + 1);  // one arrival per weight stream + activations
-      mbar_init(empty(s), 1);
-      for (int t = 0; t < kTilesN; ++t) mbar_init(packed(s, t), 1);
+  // one thread per barrier: the initialisations would otherwise run one after the other
+  if (threadIdx.x < S::kNumBars) {
+    const int i = threadIdx.x;
+    uint32_t count = 1;  // empty, packed, acc_full and final: one arrival (a commit or a copy's expect_tx)
+    if (i < kStages) {
+      count = static_cast<uint32_t>(tiles_here) + 1;  // ready: one arrival per weight stream + activations
+    } else if (i >= (2 + TN) * kStages + kAccs && i < (2 + TN) * kStages + 2 * kAccs) {
+      count = kDrainWarps;  // acc_empty: one arrival per drain warp
     }
-    for (int b = 0; b < kAccs; ++b) {
-      mbar_init(acc_full(b), 1);
-      mbar_init(acc_empty(b), kDrainWarps);  // one arrival per drain warp
-    }
-    mbar_init(final_bar, 1);
-    *abort_flag = 0;
+    mbar_init(bar0 + 8u * i, count);
+    if (i == 0) *abort_flag = 0;
     mbar_init_fence();
     fence_proxy_async();
   }
