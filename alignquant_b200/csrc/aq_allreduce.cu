@@ -3,21 +3,24 @@
 // (reference: dist.all_reduce after a row-parallel linear, alignquant/quantization/model.py:352-356).
 //
 // Every rank owns one "exchange buffer" that all peers have mapped:
-//   [ counters[kBlocks] | flags[kMaxRanks][kBlocks] | pad to 1024 B | recv[2][world][max_count] floats ]
-// One launch per rank and all-reduce, kBlocks CTAs, each CTA owning a contiguous slice:
-//   1. epoch = counters[b] + 1 (the number of this all-reduce; lives on the device, so a
-//      captured launch can be replayed), parity = epoch & 1;
-//   2. push: the CTA stores its slice of the partial into recv[parity][rank] of every peer
-//      (plain 16-byte stores that travel over NVLink), then one thread makes them visible
-//      (system-scope fence) and writes `epoch` into flags[rank][b] of every peer;
-//   3. wait: one thread per peer polls the local flags[peer][b] until it reaches `epoch`.
-//      The poll is bounded: on a time-out the CTA records it in a status word and goes on,
-//      so a missing peer turns into an error code instead of a hang;
-//   4. sum in rank order 0..world-1 (own slice from the partial, the others from the local
-//      recv[parity]), which gives every rank the same bits, and store the result.
-// Two recv halves are enough: a rank can only reach all-reduce e+2 after every peer has
-// signalled e+1, which a peer does after it has finished reading e.
-// Only plain peer loads/stores are used: no multicast objects, no multimem.
+//   [ call counter, CTA counter | pad to 1024 B | recv[2][world][max_count] x {float value, uint32 epoch} ]
+// One launch per rank and all-reduce, up to kBlocks CTAs (one per 1024 values), each thread
+// owning groups of four values:
+//   1. epoch = call counter + 1 (the number of this all-reduce, the same in every CTA and on
+//      every rank; it lives on the device, so a captured launch can be replayed; the last CTA
+//      to finish stores it back), parity = epoch & 1;
+//   2. push: every value travels together with the epoch in one 8-byte unit (two units per
+//      16-byte store) into recv[parity][rank] of every peer over NVLink.  There is no separate
+//      flag and no fence: a unit whose tag equals the epoch carries this all-reduce's value,
+//      because an aligned 8-byte unit is never torn;
+//   3. the same thread polls the units of its groups in its own recv[parity][peer] until
+//      their tags match (bounded: on a time-out it records the peer in a status word and goes
+//      on, so a missing peer turns into an error code instead of a hang) and adds the values in
+//      rank order 0..world-1 (its own from the partial), which gives every rank the same bits.
+// Two recv halves are enough: a rank can only reach all-reduce e+2 after it has received
+// every peer's e+1, which a peer sends after it has finished reading e.  The tag wraps after
+// 2^32 calls per buffer.
+// Only plain peer stores and local loads are used: no multicast objects, no multimem.
 #include "aq_common.cuh"
 
 namespace aq {
@@ -31,19 +34,20 @@ constexpr int kMaxRanks = 8;
 constexpr int kThreads = 256;
 constexpr int kHeaderBytes = 1024;
 constexpr uint32_t kPollLimit = 1u << 22;
-static_assert((kBlocks + kMaxRanks * kBlocks) * 4 <= kHeaderBytes, "header too small");
+static_assert(kBlocks * 4 <= kHeaderBytes, "header too small");
 
 struct Peers {
   uint8_t* buffer[kMaxRanks];
 };
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
+__device__ __forceinline__ void st_volatile_v4(uint4* p, const uint4& v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
 }
 
 __global__ void __launch_bounds__(kThreads) allreduce_push_kernel(const float* __restrict__ partial,
@@ -52,68 +56,84 @@ __global__ void __launch_bounds__(kThreads) allreduce_push_kernel(const float* _
                                                                   const Peers peers) {
   __shared__ uint32_t epoch_shared;
   const int b = blockIdx.x;
+  const int blocks = static_cast<int>(gridDim.x);
   uint8_t* mine = peers.buffer[rank];
   uint32_t* counters = reinterpret_cast<uint32_t*>(mine);
-  uint32_t* flags = counters + kBlocks;  // [kMaxRanks][kBlocks], written by the peers
-  if (threadIdx.x == 0) epoch_shared = counters[b] + 1;
+  if (threadIdx.x == 0) epoch_shared = counters[0] + 1;
   __syncthreads();
   const uint32_t epoch = epoch_shared;
-  const int64_t half = static_cast<int64_t>(epoch & 1u) * world * max_count;
+  // recv[parity][r] starts at uint4 index (parity * world + r) * max_count / 2 (8 bytes per value)
+  const int64_t half = static_cast<int64_t>(epoch & 1u) * world;
+  const int64_t rank_stride = max_count >> 1;
 
-  // slice of this CTA, in 16-byte units (count is a multiple of 4)
-  const int64_t vec_total = count >> 2;
-  const int64_t per_block = (vec_total + kBlocks - 1) / kBlocks;
-  const int64_t v_begin = b * per_block;
-  const int64_t v_end = v_begin + per_block < vec_total ? v_begin + per_block : vec_total;
+  // groups of four values; group i of a rank's area occupies uint4 2i and 2i+1
+  const int64_t groups = count >> 2;
+  const int64_t per_block = (groups + blocks - 1) / blocks;
+  const int64_t g_begin = b * per_block;
+  const int64_t g_end = g_begin + per_block < groups ? g_begin + per_block : groups;
 
   const float4* src = reinterpret_cast<const float4*>(partial);
-  for (int step = 1; step < world; ++step) {
-    const int peer = (rank + step) % world;  // every rank starts with a different peer
-    float4* dst = reinterpret_cast<float4*>(peers.buffer[peer] + kHeaderBytes) + ((half + rank * max_count) >> 2);
-    for (int64_t i = v_begin + threadIdx.x; i < v_end; i += kThreads) dst[i] = src[i];
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();
+  for (int64_t i = g_begin + threadIdx.x; i < g_end; i += kThreads) {
+    const float4 v = src[i];
+    const uint4 lo = make_uint4(__float_as_uint(v.x), epoch, __float_as_uint(v.y), epoch);
+    const uint4 hi = make_uint4(__float_as_uint(v.z), epoch, __float_as_uint(v.w), epoch);
     for (int step = 1; step < world; ++step) {
-      const int peer = (rank + step) % world;
-      uint32_t* peer_flags = reinterpret_cast<uint32_t*>(peers.buffer[peer]) + kBlocks;
-      st_release_sys(peer_flags + rank * kBlocks + b, epoch);
+      const int peer = (rank + step) % world;  // every rank starts with a different peer
+      uint4* dst = reinterpret_cast<uint4*>(peers.buffer[peer] + kHeaderBytes) + (half + rank) * rank_stride + 2 * i;
+      st_volatile_v4(dst, lo);
+      st_volatile_v4(dst + 1, hi);
     }
   }
-  if (threadIdx.x < world && threadIdx.x != rank) {
-    const uint32_t* flag = flags + threadIdx.x * kBlocks + b;
-    uint32_t polls = 0;
-    while (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) < 0) {
-      if (++polls >= kPollLimit) {
-        atomicCAS(&g_allreduce_status, 0, 1 + static_cast<int>(threadIdx.x));
-        break;
-      }
-      if (polls > 64) __nanosleep(100);
-    }
-  }
-  __syncthreads();
 
-  const float4* recv = reinterpret_cast<const float4*>(mine + kHeaderBytes) + (half >> 2);
+  const uint4* recv = reinterpret_cast<const uint4*>(mine + kHeaderBytes) + half * rank_stride;
   float4* dst = reinterpret_cast<float4*>(out);
-  for (int64_t i = v_begin + threadIdx.x; i < v_end; i += kThreads) {
-    float4 acc = rank == 0 ? src[i] : recv[i];
-    for (int r = 1; r < world; ++r) {
-      const float4 v = r == rank ? src[i] : recv[(static_cast<int64_t>(r) * max_count >> 2) + i];
-      acc.x = __fadd_rn(acc.x, v.x);
-      acc.y = __fadd_rn(acc.y, v.y);
-      acc.z = __fadd_rn(acc.z, v.z);
-      acc.w = __fadd_rn(acc.w, v.w);
+  for (int64_t i = g_begin + threadIdx.x; i < g_end; i += kThreads) {
+    const float4 own = src[i];
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int r = 0; r < world; ++r) {
+      float4 v = own;
+      if (r != rank) {
+        const uint4* unit = recv + r * rank_stride + 2 * i;
+        uint4 lo = ld_volatile_v4(unit);
+        uint4 hi = ld_volatile_v4(unit + 1);
+        uint32_t polls = 0;
+        while (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch) {
+          if (++polls >= kPollLimit) {
+            atomicCAS(&g_allreduce_status, 0, 1 + r);
+            break;
+          }
+          if (polls > 64) __nanosleep(100);
+          lo = ld_volatile_v4(unit);
+          hi = ld_volatile_v4(unit + 1);
+        }
+        v = make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z));
+      }
+      if (r == 0) {
+        acc = v;
+      } else {
+        acc.x = __fadd_rn(acc.x, v.x);
+        acc.y = __fadd_rn(acc.y, v.y);
+        acc.z = __fadd_rn(acc.z, v.z);
+        acc.w = __fadd_rn(acc.w, v.w);
+      }
     }
     dst[i] = acc;
   }
-  if (threadIdx.x == 0) counters[b] = epoch;
+  // the last CTA to finish advances the call counter (the next launch starts after this one ends)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&counters[1], 1u) == static_cast<uint32_t>(blocks - 1)) {
+      counters[1] = 0;
+      counters[0] = epoch;
+    }
+  }
 }
 
 }  // namespace
 
 int64_t allreduce_buffer_bytes(int world, int64_t max_count) {
-  return kHeaderBytes + 2 * static_cast<int64_t>(world) * max_count * static_cast<int64_t>(sizeof(float));
+  return kHeaderBytes + 2 * static_cast<int64_t>(world) * max_count * 8;  // 8 bytes per value: {value, epoch}
 }
 
 int allreduce_max_ranks() { return kMaxRanks; }
@@ -122,8 +142,18 @@ int launch_allreduce(const float* partial, float* out, int64_t count, int rank, 
                      int64_t max_count, cudaStream_t stream) {
   Peers peers;
   for (int r = 0; r < kMaxRanks; ++r) peers.buffer[r] = r < world ? static_cast<uint8_t*>(peer_buffers[r]) : nullptr;
-  allreduce_push_kernel<<<kBlocks, kThreads, 0, stream>>>(partial, out, count, rank, world, max_count, peers);
-  return check_cuda(cudaGetLastError(), "peer all-reduce launch");
+  int64_t blocks = (count / 4 + kThreads - 1) / kThreads;  // the same on every rank: count is
+  if (blocks > kBlocks) blocks = kBlocks;
+  if (blocks < 1) blocks = 1;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  config.attrs = nullptr;
+  config.numAttrs = 0;
+  return check_cuda(cudaLaunchKernelEx(&config, allreduce_push_kernel, partial, out, count, rank, world, max_count, peers),
+                    "peer all-reduce launch");
 }
 
 int take_allreduce_status() {

@@ -4,7 +4,8 @@ Replaces ``dist.all_reduce`` after o_proj / down_proj (reference:
 ``alignquant/quantization/model.py:352-356``) for the small FP32 messages of decode.  One
 process per GPU; the exchange buffers are torch symmetric-memory allocations, so every rank
 can store into every other rank's buffer over NVLink.  The kernel itself is
-``aq_allreduce_f32`` of the C library (plain peer stores, a flag per CTA, a bounded wait).
+``aq_allreduce_f32`` of the C library (plain peer stores of values tagged with the call
+number, bounded polls of the local receive area).
 """
 
 from __future__ import annotations
