@@ -30,6 +30,7 @@ SIGNATURES = {
     "aq_linear_plan": (_INT, [_I64, _I32, _I32, _INT, _INT, _P, _P, _P]),
     "aq_allreduce_buffer_bytes": (_I64, [_I32, _I64]),
     "aq_allreduce_f32": (_INT, [_P, _P, _I64, _I32, _I32, _P, _I64, _P]),
+    "aq_linear_allreduce": (_INT, [_P, _P, _INT, _I64, _P, _I32, _I32, _P, _INT, _P, _I32, _I32, _P, _I64, _P]),
     "aq_device_status": (_INT, [_P]),
 }
 

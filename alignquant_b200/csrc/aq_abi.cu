@@ -155,10 +155,19 @@ int64_t aq_linear_workspace_bytes(int64_t m, int32_t n_j, int32_t n_k, int sched
   }
 }
 
-int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
-              const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
-              int schedule, int decode_splits, int out_dtype, void* out, void* workspace,
-              int64_t workspace_bytes, int32_t* acc_dump, void* stream) {
+}  // extern "C"
+
+struct TensorParallelSum {
+  int32_t rank;
+  int32_t world;
+  void* const* peer_buffers;
+  int64_t max_count;
+};
+
+static int linear_impl(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
+                       const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
+                       int schedule, int decode_splits, int out_dtype, void* out, void* workspace,
+                       int64_t workspace_bytes, int32_t* acc_dump, const TensorParallelSum* tp, void* stream) {
   AQ_REQUIRE(xq != nullptr && act_scales != nullptr && prepared != nullptr && out != nullptr,
              "xq, act_scales, prepared and out must not be NULL");
   AQ_REQUIRE(m >= 1, "x_int8 must have at least one row");
@@ -205,6 +214,13 @@ int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   const int kernel = choose_kernel(m, n_j, n_k, schedule, decode_splits);
+  if (tp != nullptr) {
+    AQ_REQUIRE(kernel == 3, "the fused tensor-parallel sum is only available where aq_linear_plan reports kernel 3");
+    a.peer_buffers = tp->peer_buffers;
+    a.tp_rank = tp->rank;
+    a.tp_world = tp->world;
+    a.ar_max_count = tp->max_count;
+  }
   if (kernel == 3) return launch_cluster_decode(a, s);
   if (kernel == 0) {
     AQ_REQUIRE(decode_splits == 0 || m <= kStreamMaxRows,
@@ -218,6 +234,35 @@ int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t
                 static_cast<long long>(need));
   }
   return kernel == 2 ? launch_decode_linear(a, s) : launch_tmem_gemm(a, s);
+}
+
+
+extern "C" {
+
+int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
+              const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
+              int schedule, int decode_splits, int out_dtype, void* out, void* workspace,
+              int64_t workspace_bytes, int32_t* acc_dump, void* stream) {
+  return linear_impl(xq, act_scales, scale_mode, m, prepared, n_j, n_k, u_metadata, schedule, decode_splits, out_dtype,
+                     out, workspace, workspace_bytes, acc_dump, nullptr, stream);
+}
+
+int aq_linear_allreduce(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
+                        const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
+                        int out_dtype, void* out, int32_t rank, int32_t world, void* const* peer_buffers,
+                        int64_t max_count, void* stream) {
+  AQ_REQUIRE(peer_buffers != nullptr, "peer_buffers must not be NULL");
+  AQ_REQUIRE(world >= 2 && world <= allreduce_max_ranks(), "world must be 2..%d, got %d", allreduce_max_ranks(), world);
+  AQ_REQUIRE(rank >= 0 && rank < world, "rank must be in [0, world)");
+  AQ_REQUIRE(max_count >= 4 && (max_count & 3) == 0, "max_count must be a positive multiple of 4");
+  AQ_REQUIRE(m >= 1 && n_j > 0 && m * static_cast<int64_t>(n_j) * 64 <= max_count,
+             "the output (m x N values) must fit the exchange buffers (max_count)");
+  for (int r = 0; r < world; ++r) {
+    AQ_REQUIRE(peer_buffers[r] != nullptr && aligned(peer_buffers[r], 16), "peer_buffers[%d] must be a 16-byte aligned device pointer", r);
+  }
+  const TensorParallelSum tp = {rank, world, peer_buffers, max_count};
+  return linear_impl(xq, act_scales, scale_mode, m, prepared, n_j, n_k, u_metadata, AQ_SCHEDULE_AUTO, 0, out_dtype, out,
+                     nullptr, 0, nullptr, &tp, stream);
 }
 
 int aq_linear_decode_static(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,

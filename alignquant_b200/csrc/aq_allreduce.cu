@@ -30,15 +30,13 @@ __device__ int g_allreduce_status = 0;
 namespace {
 
 constexpr int kBlocks = 16;
-constexpr int kMaxRanks = 8;
+constexpr int kMaxRanks = kArMaxRanks;
 constexpr int kThreads = 256;
-constexpr int kHeaderBytes = 1024;
+constexpr int kHeaderBytes = kArHeaderBytes;
 constexpr uint32_t kPollLimit = 1u << 22;
 static_assert(kBlocks * 4 <= kHeaderBytes, "header too small");
 
-struct Peers {
-  uint8_t* buffer[kMaxRanks];
-};
+using Peers = ArPeers;
 
 __device__ __forceinline__ void st_volatile_v4(uint4* p, const uint4& v) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)

@@ -65,7 +65,21 @@ struct Params {
   int n_k;
   int scale_mode;
   int out_dtype;
+  // fused sum over tensor-parallel ranks (tp_world <= 1: off)
+  ArPeers peers;
+  int tp_rank;
+  int tp_world;
+  int64_t ar_max_count;
 };
+
+__device__ __forceinline__ void st_volatile_v2(void* p, uint32_t a, uint32_t b) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
 
 constexpr int kGroupTiles = 8;  // tiles per ring slot
 constexpr int kSlots = 2;
@@ -159,6 +173,10 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
   grid_launch_dependents();
   grid_dependency_wait();  // activations and their scales come from the preceding kernel
   AQ_CT(2);
+  __shared__ uint32_t ar_epoch_shared;
+  if (p.tp_world > 1 && threadIdx.x == 0) {
+    ar_epoch_shared = *reinterpret_cast<const volatile uint32_t*>(p.peers.buffer[p.tp_rank]) + 1;  // number of this call
+  }
   __syncthreads();
 
   if (producer) {
@@ -314,24 +332,102 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
     const bool has_u = meta != nullptr && meta[0] != 0;
     const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
     // rank r finishes rows r, r + split_k, ...; its warps take them round robin
-    for (int row = split + split_k * warp; row < rows; row += split_k * kConsumerWarps) {  // all consumer warps
-      float lo = 0.0f, hi = 0.0f;
-      for (int s = 0; s < split_k; ++s) {
-        const float* remote = cluster.map_shared_rank(tile, s);
-        const float a = remote[row * kTile + lane];
-        const float b = remote[row * kTile + lane + 32];
-        lo = (s == 0) ? a : __fadd_rn(lo, a);
-        hi = (s == 0) ? b : __fadd_rn(hi, b);
+    if (p.tp_world <= 1) {
+      for (int row = split + split_k * warp; row < rows; row += split_k * kConsumerWarps) {  // all consumer warps
+        float lo = 0.0f, hi = 0.0f;
+        for (int s = 0; s < split_k; ++s) {
+          const float* remote = cluster.map_shared_rank(tile, s);
+          const float a = remote[row * kTile + lane];
+          const float b = remote[row * kTile + lane + 32];
+          lo = (s == 0) ? a : __fadd_rn(lo, a);
+          hi = (s == 0) ? b : __fadd_rn(hi, b);
+        }
+        if (has_u) inverse_u_row(lo, hi, meta, lane);
+        const int64_t o = static_cast<int64_t>(row) * n_cols + static_cast<int64_t>(j) * kTile + lane;
+        store_any(p.out, p.out_dtype, o, lo);
+        store_any(p.out, p.out_dtype, o + 32, hi);
       }
-      if (has_u) inverse_u_row(lo, hi, meta, lane);
-      const int64_t o = static_cast<int64_t>(row) * n_cols + static_cast<int64_t>(j) * kTile + lane;
-      store_any(p.out, p.out_dtype, o, lo);
-      store_any(p.out, p.out_dtype, o + 32, hi);
+    } else {
+      // Row-parallel layer: the finished values of this rank go, each paired with the call number
+      // in one 8-byte unit, into the receive area of every peer (plain NVLink stores); the same
+      // lane then polls the peers' units of the same positions in its own receive area (bounded)
+      // and adds the ranks' values in rank order -- the protocol of aq_allreduce.cu, without a
+      // second launch.
+      const uint32_t epoch = ar_epoch_shared;
+      const int64_t area = (static_cast<int64_t>(epoch & 1u) * p.tp_world) * p.ar_max_count;  // values
+      constexpr int kMaxOwned = (kRows + kConsumerWarps - 1) / kConsumerWarps;
+      float own_lo[kMaxOwned], own_hi[kMaxOwned];
+#pragma unroll
+      for (int it = 0; it < kMaxOwned; ++it) {
+        const int row = split + split_k * (warp + it * kConsumerWarps);
+        own_lo[it] = own_hi[it] = 0.0f;
+        if (row < rows) {
+          float lo = 0.0f, hi = 0.0f;
+          for (int s = 0; s < split_k; ++s) {
+            const float* remote = cluster.map_shared_rank(tile, s);
+            const float a = remote[row * kTile + lane];
+            const float b = remote[row * kTile + lane + 32];
+            lo = (s == 0) ? a : __fadd_rn(lo, a);
+            hi = (s == 0) ? b : __fadd_rn(hi, b);
+          }
+          if (has_u) inverse_u_row(lo, hi, meta, lane);
+          own_lo[it] = lo;
+          own_hi[it] = hi;
+          const int64_t e = static_cast<int64_t>(row) * n_cols + static_cast<int64_t>(j) * kTile + lane;
+          for (int step = 1; step < p.tp_world; ++step) {
+            const int peer = (p.tp_rank + step) % p.tp_world;
+            uint8_t* units = p.peers.buffer[peer] + kArHeaderBytes + (area + p.tp_rank * p.ar_max_count + e) * 8;
+            st_volatile_v2(units, __float_as_uint(lo), epoch);
+            st_volatile_v2(units + 32 * 8, __float_as_uint(hi), epoch);
+          }
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < kMaxOwned; ++it) {
+        const int row = split + split_k * (warp + it * kConsumerWarps);
+        if (row < rows) {
+          const int64_t e = static_cast<int64_t>(row) * n_cols + static_cast<int64_t>(j) * kTile + lane;
+          float lo = 0.0f, hi = 0.0f;
+          for (int r = 0; r < p.tp_world; ++r) {
+            float a = own_lo[it], b = own_hi[it];
+            if (r != p.tp_rank) {
+              const uint8_t* units = p.peers.buffer[p.tp_rank] + kArHeaderBytes + (area + r * p.ar_max_count + e) * 8;
+              uint2 ua = ld_volatile_v2(units);
+              uint2 ub = ld_volatile_v2(units + 32 * 8);
+              uint32_t polls = 0;
+              while (ua.y != epoch || ub.y != epoch) {
+                if (++polls >= (1u << 22)) {
+                  atomicCAS(&g_cluster_decode_status, 0, 40 + r);
+                  break;
+                }
+                if (polls > 64) __nanosleep(100);
+                ua = ld_volatile_v2(units);
+                ub = ld_volatile_v2(units + 32 * 8);
+              }
+              a = __uint_as_float(ua.x);
+              b = __uint_as_float(ub.x);
+            }
+            lo = r == 0 ? a : __fadd_rn(lo, a);
+            hi = r == 0 ? b : __fadd_rn(hi, b);
+          }
+          store_any(p.out, p.out_dtype, e, lo);
+          store_any(p.out, p.out_dtype, e + 32, hi);
+        }
+      }
     }
   }
   AQ_CT(7);
   cluster.sync();  // peers may still be reading this CTA's tile
   AQ_CT(8);
+  if (p.tp_world > 1 && threadIdx.x == 0) {
+    // the last CTA of the grid advances the call counter (the next launch starts after this one ends)
+    uint32_t* counters = reinterpret_cast<uint32_t*>(p.peers.buffer[p.tp_rank]);
+    __threadfence();
+    if (atomicAdd(&counters[1], 1u) == gridDim.x * gridDim.y - 1) {
+      counters[1] = 0;
+      counters[0] = ar_epoch_shared;
+    }
+  }
 }
 
 // Kernel variants by row count: up to 8 rows <1,1>, up to 16 <2,1>, up to 32 <2,2>.
@@ -461,6 +557,12 @@ int launch_cluster_decode(const LinearArgs& a, cudaStream_t stream) {
   p.n_k = a.n_k;
   p.scale_mode = a.scale_mode;
   p.out_dtype = a.out_dtype;
+  p.tp_rank = a.tp_rank;
+  p.tp_world = a.peer_buffers != nullptr ? a.tp_world : 1;
+  p.ar_max_count = a.ar_max_count;
+  for (int r = 0; r < kArMaxRanks; ++r) {
+    p.peers.buffer[r] = (a.peer_buffers != nullptr && r < a.tp_world) ? static_cast<uint8_t*>(a.peer_buffers[r]) : nullptr;
+  }
   const int split = cluster_decode_split(a.m, a.n_j, a.n_k);
   return launch_variant(variant_for(a.m), p, split, stream);
 }

@@ -70,6 +70,21 @@ struct LinearArgs {
   int32_t* acc_dump;
   void* workspace;
   int64_t workspace_bytes;
+  // Row-parallel layer under tensor parallelism: sum the ranks' outputs inside the kernel
+  // through the peer exchange buffers of aq_allreduce_f32 (tp_world <= 1: off).
+  void* const* peer_buffers = nullptr;
+  int tp_rank = 0;
+  int tp_world = 1;
+  int64_t ar_max_count = 0;
+};
+
+// Layout of a peer exchange buffer (shared by aq_allreduce.cu and the fused decode epilogue):
+// [uint32 call counter, uint32 CTA counter | pad to kArHeaderBytes |
+//  recv[2][world][max_count] x {float value, uint32 call number}]
+constexpr int kArHeaderBytes = 1024;
+constexpr int kArMaxRanks = 8;
+struct ArPeers {
+  uint8_t* buffer[kArMaxRanks];
 };
 
 // Streaming kernel for small m (mma.sync, split-K reduced through cluster shared memory).

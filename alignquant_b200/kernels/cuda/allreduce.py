@@ -49,6 +49,10 @@ class PeerAllReduce:
             raise RuntimeError("symmetric memory returned an unexpected number of peer pointers")
         self._peer_array = (ctypes.c_void_p * self.world)(*pointers)
 
+    def peer_array_pointer(self) -> ctypes.c_void_p:
+        """Host array of the ranks' exchange buffers, as the C entry points take it."""
+        return ctypes.cast(self._peer_array, ctypes.c_void_p)
+
     def __call__(self, partial: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         if partial.dtype != torch.float32 or not partial.is_contiguous() or partial.device != self.device:
             raise RuntimeError("partial must be a contiguous float32 tensor on the all-reduce's device")

@@ -299,6 +299,49 @@ def alignquant_linear_prepared(
     return out
 
 
+def alignquant_linear_allreduce(
+    activation: torch.Tensor,
+    activation_scales: torch.Tensor,
+    weights: PreparedWeights,
+    u_metadata: torch.Tensor | None,
+    reducer,
+    *,
+    output_dtype: torch.dtype = torch.float32,
+    scale_mode: str = "tile",
+    out: torch.Tensor | None = None,
+) -> torch.Tensor | None:
+    """Row-parallel projection and the sum over the tensor-parallel ranks in ONE kernel.
+
+    ``reducer`` is a ``kernels.cuda.allreduce.PeerAllReduce``.  Returns the summed ``[M, N]``
+    result, or ``None`` when the problem does not take the decode kernel that carries the fused
+    epilogue (more than 32 rows, very few tile rows, result larger than the exchange buffers);
+    the caller then runs ``alignquant_linear_prepared`` followed by ``reducer(...)``.
+    Every rank must take the same branch: the decision depends only on the shapes.
+    """
+    mode = _scale_mode_code(scale_mode)
+    n_j, n_k = weights.n_j, weights.n_k
+    x = activation.contiguous()
+    if x.dim() != 2 or x.dtype != torch.int8 or int(x.size(1)) != n_k * 64:
+        raise RuntimeError("x_int8 must be int8 [M,K] matching the weights")
+    m = int(x.size(0))
+    if m * n_j * 64 > reducer.max_count or linear_plan(m, n_j, n_k)["kernel"] != 3:
+        return None
+    scales = activation_scales.contiguous()
+    device = x.device
+    meta = None if u_metadata is None else u_metadata.contiguous()
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        if out is None:
+            out = torch.empty((m, n_j * 64), dtype=output_dtype, device=device)
+        _lib.check(
+            lib.aq_linear_allreduce(
+                _ptr(x), _ptr(scales), mode, m, _ptr(weights.image), n_j, n_k, _ptr(meta), _DTYPE_CODES[output_dtype],
+                _ptr(out), reducer.rank, reducer.world, reducer.peer_array_pointer(), reducer.max_count, _stream(device),
+            )
+        )
+    return out
+
+
 _WORKSPACES: dict[tuple, torch.Tensor] = {}
 
 

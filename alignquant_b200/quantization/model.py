@@ -263,9 +263,19 @@ class _ProjectionGroupRuntime:
             flat = activation.reshape(rows, width)
             qx, scales = _ext.alignquant_activation_quantize_cuda(flat, self.v_metadata, scale_mode=self.scale_mode)
             out_dtype = activation.dtype if activation.dtype in (torch.bfloat16, torch.float16) and not self.row_parallel else torch.float32
-            combined = _ext.alignquant_linear_prepared(
-                qx, scales, self.weights, self.u_metadata, scale_mode=self.scale_mode, output_dtype=out_dtype
-            )
+            combined = None
+            self.sum_fused = False
+            reducer = getattr(self, "peer_allreduce", None)
+            if self.row_parallel and reducer is not None:
+                # decode sizes: projection and the sum over the ranks in one kernel
+                combined = _ext.alignquant_linear_allreduce(
+                    qx, scales, self.weights, self.u_metadata, reducer, scale_mode=self.scale_mode, output_dtype=out_dtype
+                )
+                self.sum_fused = combined is not None
+            if combined is None:
+                combined = _ext.alignquant_linear_prepared(
+                    qx, scales, self.weights, self.u_metadata, scale_mode=self.scale_mode, output_dtype=out_dtype
+                )
             if tuple(combined.shape) != (rows, self.out_features):
                 raise RuntimeError(
                     f"Projection group {self.group_id} returned {tuple(combined.shape)}, "
@@ -305,7 +315,7 @@ class AlignQuantLinear(nn.Module):
 
     def forward(self, activation: torch.Tensor) -> torch.Tensor:
         result, original_shape = self.runtime.project_member(activation, member=self.layer_name)
-        if self.runtime.row_parallel:
+        if self.runtime.row_parallel and not getattr(self.runtime, "sum_fused", False):
             import torch.distributed as dist
 
             result = result.contiguous()
@@ -402,6 +412,7 @@ def install_alignquant(
         runtimes[group_id] = runtime
         for name in members:
             parent, attr, _ = records.pop(name)
+            runtime.peer_allreduce = peer_allreduce
             module = AlignQuantLinear(getattr(parent, attr), layer_name=name, runtime=runtime, process_group=process_group,
                                       peer_allreduce=peer_allreduce)
             setattr(parent, attr, module)

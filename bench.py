@@ -280,6 +280,9 @@ def run_native(args) -> None:
                     if with_quantizer:
                         ext.alignquant_activation_quantize_cuda(acts[(m, name)], None, scale_mode="token", out=qbuf[(m, name)])
                     xq, a_s = qbuf[(m, name)]
+                    if with_allreduce and reducer is not None and axis == "k" and ext.alignquant_linear_allreduce(
+                            xq, a_s, entry[name], None, reducer, scale_mode="token", out=outs[(m, name)]) is not None:
+                        continue  # projection and the sum over the ranks ran as one kernel
                     ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", out=outs[(m, name)])
                     if with_allreduce and world > 1 and axis == "k":
                         all_reduce(outs[(m, name)])
@@ -381,9 +384,13 @@ def run_native(args) -> None:
                             arrived.record(copy_in)
                         main.wait_event(arrived)
                         xq, a_s = ext.alignquant_activation_quantize_cuda(x_dev[(li, m, name)], None, scale_mode="token")
-                        y = ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token")
-                        if world > 1 and axis == "k":
-                            all_reduce(y)
+                        y = None
+                        if reducer is not None and axis == "k":
+                            y = ext.alignquant_linear_allreduce(xq, a_s, entry[name], None, reducer, scale_mode="token")
+                        if y is None:
+                            y = ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token")
+                            if world > 1 and axis == "k":
+                                all_reduce(y)
                         computed = torch.cuda.Event()
                         computed.record(main)
                         with torch.cuda.stream(copy_out):
@@ -424,7 +431,7 @@ def run_native(args) -> None:
             "l2": "2 GB of distinct weights per step exceed the 126 MB L2; no flush between steps",
             "parallelism": f"tp{world}",
             "launch": launch_mode + ("" if world == 1 else
-                                     " + peer-memory all-reduce kernel" if reducer is not None else " + NCCL all-reduce"),
+                                     " + sum over ranks fused into the GEMV epilogue (peer memory)" if reducer is not None else " + NCCL all-reduce"),
         },
         "clocks": clocks.result,
         "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s",

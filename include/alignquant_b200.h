@@ -212,6 +212,19 @@ AQ_API int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int
  *   and aq_device_status reports AQ_ERR_DEVICE.
  */
 AQ_API int64_t aq_allreduce_buffer_bytes(int32_t world, int64_t max_count);
+/*
+ * aq_linear followed by that sum, in ONE kernel: the decode kernel's epilogue pushes the
+ * finished values of this rank to the peers' exchange buffers and adds the ranks' values in
+ * rank order (same protocol, same buffers and call sequence as aq_allreduce_f32; the two may be
+ * mixed as long as every rank issues the same sequence).  Automatic schedule only, and only
+ * where aq_linear_plan reports kernel 3 (decode sizes, at most 32 rows); otherwise
+ * AQ_ERR_INVALID, and the caller uses aq_linear + aq_allreduce_f32.  m * N <= max_count.
+ * `out` receives the summed result in out_dtype.
+ */
+AQ_API int aq_linear_allreduce(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
+                               const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
+                               int out_dtype, void* out, int32_t rank, int32_t world, void* const* peer_buffers,
+                               int64_t max_count, void* stream);
 AQ_API int aq_allreduce_f32(const float* partial, float* out, int64_t count, int32_t rank, int32_t world,
                             void* const* peer_buffers, int64_t max_count, void* stream);
 

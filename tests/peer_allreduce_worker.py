@@ -55,6 +55,38 @@ def main() -> int:
     if not bool((y == expect).all()):
         ok = False
         print(f"rank {rank}: graph replay gave {y[:4].tolist()} instead of {expect}", file=sys.stderr)
+    # projection + sum over the ranks in one kernel against projection, then all-reduce kernel
+    from alignquant_b200.synthetic import synthetic_activation, synthetic_module_tensors
+
+    n, k = 2048, 512  # this rank's K shard of a row-parallel layer (enough tile rows for the cluster decode kernel)
+    t = synthetic_module_tensors(n, k, seed=100 + rank, device=device)
+    weights = ext.prepare_weights(t["state_bits"], t["w4_payload"], t["w4_scales"], t["w8_payload"], t["w8_scales"],
+                                  t["w4_row_offsets"], t["w8_row_offsets"], n_k=k // 64)
+    for m in (1, 7, 16, 24):
+        xq, a_s = ext.alignquant_activation_quantize_cuda(synthetic_activation(m, k, seed=200 + rank + m, device=device),
+                                                          None, scale_mode="token")
+        separate = reducer(ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token"))
+        fused = ext.alignquant_linear_allreduce(xq, a_s, weights, None, reducer, scale_mode="token")
+        torch.cuda.synchronize()
+        if fused is None:
+            ok = False
+            print(f"rank {rank}: the fused path did not apply (m = {m}, plan {ext.linear_plan(m, n // 64, k // 64)})", file=sys.stderr)
+        elif not torch.equal(fused, separate):
+            ok = False
+            print(f"rank {rank}: fused projection + sum differs from the two-kernel path (m = {m})", file=sys.stderr)
+    out = torch.empty((16, n), dtype=torch.float32, device=device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ext.alignquant_linear_allreduce(xq[:16].contiguous(), a_s[:16].contiguous(), weights, None, reducer,
+                                        scale_mode="token", out=out)
+    for _ in range(4):
+        graph.replay()
+    torch.cuda.synchronize()
+    want = reducer(ext.alignquant_linear_prepared(xq[:16].contiguous(), a_s[:16].contiguous(), weights, None, scale_mode="token"))
+    torch.cuda.synchronize()
+    if not torch.equal(out, want):
+        ok = False
+        print(f"rank {rank}: replayed fused projection + sum differs", file=sys.stderr)
     ext.device_status(device)
     flag = torch.tensor([1 if ok else 0], device=device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
