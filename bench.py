@@ -273,7 +273,10 @@ def run_native(args) -> None:
     pairs_per_step = len(ROW_COUNTS) * LAYERS * len(GROUPS)
     allreduces_per_step = len(ROW_COUNTS) * LAYERS * sum(1 for _, _, axis in GROUPS.values() if axis == "k")
 
+    separate_sums = [0]  # all-reduce kernels of our own launched by the last sweep (not fused ones, not NCCL's)
+
     def sweep(with_quantizer: bool, with_allreduce: bool) -> None:
+        separate_sums[0] = 0
         for m in ROW_COUNTS:
             for entry in layers:
                 for name, (_, _, axis) in GROUPS.items():
@@ -286,6 +289,7 @@ def run_native(args) -> None:
                     ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", out=outs[(m, name)])
                     if with_allreduce and world > 1 and axis == "k":
                         all_reduce(outs[(m, name)])
+                        separate_sums[0] += 1 if reducer is not None else 0
 
     def barrier():
         if world > 1:
@@ -312,6 +316,7 @@ def run_native(args) -> None:
 
     # ---- device-resident step: one CUDA graph per rank (kernels and, for N > 1, the all-reduces)
     sweep(True, True)
+    own_sum_launches = separate_sums[0]
     barrier()
     launch_mode = "cuda graph replay"
     try:
@@ -431,12 +436,14 @@ def run_native(args) -> None:
             "l2": "2 GB of distinct weights per step exceed the 126 MB L2; no flush between steps",
             "parallelism": f"tp{world}",
             "launch": launch_mode + ("" if world == 1 else
-                                     " + sum over ranks fused into the GEMV epilogue (peer memory)" if reducer is not None else " + NCCL all-reduce"),
+                                     f" + sum over ranks fused into the GEMV epilogue (peer memory; {own_sum_launches} of "
+                                     f"{allreduces_per_step} sums per step as a separate peer-memory kernel)"
+                                     if reducer is not None else " + NCCL all-reduce"),
         },
         "clocks": clocks.result,
         "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "launch": e2e_mode},
-        "gpu_launches": (2 * pairs_per_step + (allreduces_per_step if reducer is not None else 0)) * args.steps,
+        "gpu_launches": (2 * pairs_per_step + own_sum_launches) * args.steps,
         "roofline": {
             "kernel": "cluster_decode_kernel (packed W4/W8 GEMV, M<=16)", "bound": "hbm",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
