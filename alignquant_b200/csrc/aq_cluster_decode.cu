@@ -101,7 +101,9 @@ __device__ __forceinline__ void consumer_sync() {
 // own 16 KiB.
 // For 17..32 rows two warps share every tile (WPT = 2): warp 2t takes rows 0..15 and warp
 // 2t+1 rows 16..31 of tile worker t, so the weights are still streamed once.
-template <int NT, int WPT>
+// kTp: the epilogue also sums over the tensor-parallel ranks (a separate instantiation, so that
+// the single-GPU kernel keeps its register count).
+template <int NT, int WPT, bool kTp>
 __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 1) cluster_decode_kernel(const Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kConsumerWarps = kTileWorkers * WPT;
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
   grid_dependency_wait();  // activations and their scales come from the preceding kernel
   AQ_CT(2);
   __shared__ uint32_t ar_epoch_shared;
-  if (p.tp_world > 1 && threadIdx.x == 0) {
+  if (kTp && threadIdx.x == 0) {
     ar_epoch_shared = *reinterpret_cast<const volatile uint32_t*>(p.peers.buffer[p.tp_rank]) + 1;  // number of this call
   }
   __syncthreads();
@@ -332,7 +334,7 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
     const bool has_u = meta != nullptr && meta[0] != 0;
     const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
     // rank r finishes rows r, r + split_k, ...; its warps take them round robin
-    if (p.tp_world <= 1) {
+    if (!kTp) {
       for (int row = split + split_k * warp; row < rows; row += split_k * kConsumerWarps) {  // all consumer warps
         float lo = 0.0f, hi = 0.0f;
         for (int s = 0; s < split_k; ++s) {
@@ -419,7 +421,7 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
   AQ_CT(7);
   cluster.sync();  // peers may still be reading this CTA's tile
   AQ_CT(8);
-  if (p.tp_world > 1 && threadIdx.x == 0) {
+  if (kTp && threadIdx.x == 0) {
     // the last CTA of the grid advances the call counter (the next launch starts after this one ends)
     uint32_t* counters = reinterpret_cast<uint32_t*>(p.peers.buffer[p.tp_rank]);
     __threadfence();
@@ -438,10 +440,15 @@ struct Variant {
 Variant variant_for(int64_t m) { return m <= 8 ? Variant{1, 1} : m <= 16 ? Variant{2, 1} : Variant{2, 2}; }
 int variant_index(const Variant& v) { return v.wpt == 2 ? 2 : v.nt - 1; }
 int variant_threads(const Variant& v) { return 32 * (kTileWorkers * v.wpt + 1); }
-const void* variant_kernel(const Variant& v) {
-  if (v.wpt == 2) return reinterpret_cast<const void*>(cluster_decode_kernel<2, 2>);
-  return v.nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1, 1>)
-                   : reinterpret_cast<const void*>(cluster_decode_kernel<2, 1>);
+const void* variant_kernel(const Variant& v, bool tp = false) {
+  if (tp) {
+    if (v.wpt == 2) return reinterpret_cast<const void*>(cluster_decode_kernel<2, 2, true>);
+    return v.nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1, 1, true>)
+                     : reinterpret_cast<const void*>(cluster_decode_kernel<2, 1, true>);
+  }
+  if (v.wpt == 2) return reinterpret_cast<const void*>(cluster_decode_kernel<2, 2, false>);
+  return v.nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1, 1, false>)
+                   : reinterpret_cast<const void*>(cluster_decode_kernel<2, 1, false>);
 }
 
 int smem_bytes(const Variant& v) {
@@ -451,13 +458,14 @@ int smem_bytes(const Variant& v) {
 }
 
 int launch_variant(const Variant& v, const Params& p, int split_k, cudaStream_t stream) {
-  static std::once_flag once[64][3];
+  static std::once_flag once[64][6];
   int device = 0;
   int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
   if (rc != AQ_OK) return rc;
-  const void* kernel = variant_kernel(v);
+  const bool tp = p.tp_world > 1;
+  const void* kernel = variant_kernel(v, tp);
   cudaError_t attr_status = cudaSuccess;
-  std::call_once(once[device & 63][variant_index(v)], [&] {
+  std::call_once(once[device & 63][variant_index(v) + (tp ? 3 : 0)], [&] {
     attr_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(v));
   });
   rc = check_cuda(attr_status, "cudaFuncSetAttribute(cluster_decode_kernel)");
