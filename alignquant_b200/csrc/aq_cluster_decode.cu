@@ -309,15 +309,19 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
     for (int nt = 0; nt < NT; ++nt) {
       const int tok = row0 + nt * 8 + 2 * c;
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        slab[tok * kTile + q * 16 + g] = acc[nt][q][0];
-        slab[(tok + 1) * kTile + q * 16 + g] = acc[nt][q][1];
-        slab[tok * kTile + q * 16 + g + 8] = acc[nt][q][2];
-        slab[(tok + 1) * kTile + q * 16 + g + 8] = acc[nt][q][3];
+      for (int q = 0; q < 4; ++q) {  // only the rows that exist are combined and exchanged
+        if (tok < rows) {
+          slab[tok * kTile + q * 16 + g] = acc[nt][q][0];
+          slab[tok * kTile + q * 16 + g + 8] = acc[nt][q][2];
+        }
+        if (tok + 1 < rows) {
+          slab[(tok + 1) * kTile + q * 16 + g] = acc[nt][q][1];
+          slab[(tok + 1) * kTile + q * 16 + g + 8] = acc[nt][q][3];
+        }
       }
     }
     consumer_sync<kConsumerThreads>();
-    for (int e = threadIdx.x; e < kRows * kTile; e += kConsumerThreads) {
+    for (int e = threadIdx.x; e < rows * kTile; e += kConsumerThreads) {
       float v = slabs[e];
 #pragma unroll
       for (int w = 1; w < kTileWorkers; ++w) v = __fadd_rn(v, slabs[w * kRows * kTile + e]);
