@@ -135,10 +135,10 @@ def artifact_bytes(n_j: int, n_k: int, w4_tiles: int) -> int:
     return w4_tiles * 2048 + (tiles - w4_tiles) * 4096 + 4 * tiles + (tiles + 7) // 8 + 8 * (n_j + 1)
 
 
-def call_bytes(m: int, n: int, k: int, weight_bytes: int) -> int:
-    """Algorithmic bytes of one quantize -> linear pair (fp16 in, fp32 out, per-token scales)."""
+def call_bytes(m: int, n: int, k: int, weight_bytes: int, out_bytes: int = 2) -> int:
+    """Algorithmic bytes of one quantize -> linear pair (fp16 in, per-token scales, fp16 out unless stated)."""
     quantizer = m * k * 2 + m * k + 4 * m
-    linear = weight_bytes + m * k + 4 * m + m * n * 4
+    linear = weight_bytes + m * k + 4 * m + m * n * out_bytes
     return quantizer + linear
 
 
@@ -259,7 +259,11 @@ def run_native(args) -> None:
             for m in ROW_COUNTS for i, name in enumerate(GROUPS)}
     qbuf = {key: (torch.empty(x.shape, dtype=torch.int8, device=device), torch.empty((x.shape[0],), dtype=torch.float32, device=device))
             for key, x in acts.items()}
-    outs = {(m, name): torch.empty((m, local_shape[name][0]), dtype=torch.float32, device=device)
+    # fp16 results, as the quantized module returns them; the partial results of row-parallel
+    # layers under tensor parallelism stay fp32 for the sum over the ranks
+    out_dtype = {name: torch.float32 if world > 1 and axis == "k" else torch.float16 for name, (_, _, axis) in GROUPS.items()}
+    out_bytes = {name: 4 if dtype == torch.float32 else 2 for name, dtype in out_dtype.items()}
+    outs = {(m, name): torch.empty((m, local_shape[name][0]), dtype=out_dtype[name], device=device)
             for m in ROW_COUNTS for name in GROUPS}
 
     step_bytes = 0
@@ -268,8 +272,8 @@ def run_native(args) -> None:
         for layer in range(LAYERS):
             for name in GROUPS:
                 n, k = local_shape[name]
-                step_bytes += call_bytes(m, n, k, weight_bytes[(layer, name)])
-                linear_bytes += weight_bytes[(layer, name)] + m * k + 4 * m + m * n * 4
+                step_bytes += call_bytes(m, n, k, weight_bytes[(layer, name)], out_bytes[name])
+                linear_bytes += weight_bytes[(layer, name)] + m * k + 4 * m + m * n * out_bytes[name]
     pairs_per_step = len(ROW_COUNTS) * LAYERS * len(GROUPS)
     allreduces_per_step = len(ROW_COUNTS) * LAYERS * sum(1 for _, _, axis in GROUPS.values() if axis == "k")
 
@@ -284,9 +288,9 @@ def run_native(args) -> None:
                         ext.alignquant_activation_quantize_cuda(acts[(m, name)], None, scale_mode="token", out=qbuf[(m, name)])
                     xq, a_s = qbuf[(m, name)]
                     if with_allreduce and reducer is not None and axis == "k" and ext.alignquant_linear_allreduce(
-                            xq, a_s, entry[name], None, reducer, scale_mode="token", out=outs[(m, name)]) is not None:
+                            xq, a_s, entry[name], None, reducer, scale_mode="token", output_dtype=out_dtype[name], out=outs[(m, name)]) is not None:
                         continue  # projection and the sum over the ranks ran as one kernel
-                    ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", out=outs[(m, name)])
+                    ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", output_dtype=out_dtype[name], out=outs[(m, name)])
                     if with_allreduce and world > 1 and axis == "k":
                         all_reduce(outs[(m, name)])
                         separate_sums[0] += 1 if reducer is not None else 0
@@ -352,7 +356,7 @@ def run_native(args) -> None:
     host_x = {key: x.cpu().pin_memory() for key, x in acts.items()}
     host_out = {key: torch.empty(o.shape, dtype=o.dtype).pin_memory() for key, o in outs.items()}
     h2d = sum(host_x[(m, name)].numel() * 2 for m in ROW_COUNTS for name in GROUPS) * LAYERS
-    d2h = sum(host_out[(m, name)].numel() * 4 for m in ROW_COUNTS for name in GROUPS) * LAYERS
+    d2h = sum(host_out[(m, name)].numel() * out_bytes[name] for m in ROW_COUNTS for name in GROUPS) * LAYERS
 
     def e2e_step() -> None:
         for m in ROW_COUNTS:
@@ -360,7 +364,7 @@ def run_native(args) -> None:
                 for name, (_, _, axis) in GROUPS.items():
                     x = host_x[(m, name)].to(device, non_blocking=True)
                     xq, a_s = ext.alignquant_activation_quantize_cuda(x, None, scale_mode="token")
-                    y = ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token")
+                    y = ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", output_dtype=out_dtype[name])
                     if world > 1 and axis == "k":
                         all_reduce(y)
                     host_out[(m, name)].copy_(y, non_blocking=True)
@@ -380,27 +384,38 @@ def run_native(args) -> None:
             main = torch.cuda.current_stream(device)
             copy_in.wait_stream(main)
             copy_out.wait_stream(main)
-            for m in ROW_COUNTS:
-                for li, entry in enumerate(layers):
-                    for name, (_, _, axis) in GROUPS.items():
-                        with torch.cuda.stream(copy_in):
+            # Inputs of one row count are staged (one host->device copy per call) while the calls of
+            # the previous row count run: the kernels wait for copies once per row count instead of
+            # once per call, which keeps the programmatic dependent launch between consecutive
+            # kernels of the main stream.  Results leave once per decoder layer (one copy per call).
+            staged = {}
+            with torch.cuda.stream(copy_in):
+                for m in ROW_COUNTS:
+                    for li in range(LAYERS):
+                        for name in GROUPS:
                             x_dev[(li, m, name)].copy_(host_x[(m, name)], non_blocking=True)
-                            arrived = torch.cuda.Event()
-                            arrived.record(copy_in)
-                        main.wait_event(arrived)
+                    staged[m] = torch.cuda.Event()
+                    staged[m].record(copy_in)
+            for m in ROW_COUNTS:
+                main.wait_event(staged[m])
+                for li, entry in enumerate(layers):
+                    results = []
+                    for name, (_, _, axis) in GROUPS.items():
                         xq, a_s = ext.alignquant_activation_quantize_cuda(x_dev[(li, m, name)], None, scale_mode="token")
                         y = None
                         if reducer is not None and axis == "k":
-                            y = ext.alignquant_linear_allreduce(xq, a_s, entry[name], None, reducer, scale_mode="token")
+                            y = ext.alignquant_linear_allreduce(xq, a_s, entry[name], None, reducer, scale_mode="token", output_dtype=out_dtype[name])
                         if y is None:
-                            y = ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token")
+                            y = ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", output_dtype=out_dtype[name])
                             if world > 1 and axis == "k":
                                 all_reduce(y)
-                        computed = torch.cuda.Event()
-                        computed.record(main)
-                        with torch.cuda.stream(copy_out):
-                            copy_out.wait_event(computed)
-                            host_out[(m, name)].copy_(y, non_blocking=True)
+                        results.append((name, y))
+                    computed = torch.cuda.Event()
+                    computed.record(main)
+                    with torch.cuda.stream(copy_out):
+                        copy_out.wait_event(computed)
+                        for done_name, done_y in results:
+                            host_out[(m, done_name)].copy_(done_y, non_blocking=True)
             main.wait_stream(copy_in)
             main.wait_stream(copy_out)
 
@@ -409,7 +424,7 @@ def run_native(args) -> None:
             torch.cuda.synchronize()
 
         e2e_run()
-        e2e_mode = "one CUDA graph per step (copies on side streams)"
+        e2e_mode = "one CUDA graph per step (copies on side streams: inputs staged per row count, results read back per layer)"
     except Exception as error:  # capture of pinned copies unsupported: run the calls eagerly
         print(f"[bench] graph capture of the end-to-end step failed ({error}); running eagerly", file=sys.stderr)
         torch.cuda.synchronize()
