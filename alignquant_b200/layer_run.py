@@ -2,12 +2,18 @@
 
     python -m alignquant_b200.layer_run --n 5120 --k 3072 --rows 2048 --repeat 20
     python -m alignquant_b200.layer_run --n 3072 --k 8192 --rows 1 --scale-mode token --flush-l2
+    python -m alignquant_b200.layer_run --n 5120 --k 3072 --rows 1,4,8,16 --layers 28 --with-quantizer
 
 A seeded 60 % W4 layer of the given shape is packed into the artifact format, prepared
 once, and the quantize -> linear pair is launched ``--repeat`` times; CUDA events around the
 linear calls give the mean kernel time, from which the line reports integer TOPS
 (2*M*N*K) and the weight stream in GB/s.  The same command is the small case used for
 profiler captures of a single kernel.
+
+With ``--layers L`` (L > 1) the line describes the projection as a decoder runs it: L layers of
+the shape with distinct weights (so the weights of a pass exceed the L2 when L x layer bytes does),
+launched back to back from one CUDA graph, optionally each preceded by its activation quantizer
+(``--with-quantizer``); ``--rows`` may then list several row counts, one JSON line each.
 """
 
 from __future__ import annotations
@@ -22,7 +28,9 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--n", type=int, required=True, help="output features (multiple of 64)")
     ap.add_argument("--k", type=int, required=True, help="input features (multiple of 64)")
-    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--rows", default="1", help="row count, or a comma-separated list with --layers")
+    ap.add_argument("--layers", type=int, default=1, help="distinct layers launched back to back from a CUDA graph")
+    ap.add_argument("--with-quantizer", action="store_true", help="with --layers: quantizer before every projection")
     ap.add_argument("--repeat", type=int, default=20)
     ap.add_argument("--w4-fraction", type=float, default=0.6)
     ap.add_argument("--scale-mode", choices=("tile", "token"), default="token")
@@ -36,6 +44,13 @@ def main() -> None:
 
     ext.load_extension()
     device = torch.device("cuda", 0)
+    row_counts = [int(v) for v in str(args.rows).split(",")]
+    if args.layers > 1:
+        chain(args, ext, device, row_counts, synthetic_module_tensors, synthetic_activation, algorithmic_weight_bytes)
+        return
+    if len(row_counts) != 1:
+        raise SystemExit("--rows takes a list only together with --layers")
+    args.rows = row_counts[0]
     tensors = synthetic_module_tensors(args.n, args.k, seed=1, w4_fraction=args.w4_fraction, device=device)
     weight_bytes = algorithmic_weight_bytes(tensors)
     weights = ext.prepare_weights(
@@ -67,6 +82,54 @@ def main() -> None:
         "us": seconds * 1e6, "tops": 2.0 * args.rows * args.n * args.k / seconds / 1e12,
         "weight_gbs": weight_bytes / seconds / 1e9, "scale_mode": args.scale_mode, "out_dtype": args.out_dtype,
     }))
+
+
+def chain(args, ext, device, row_counts, synthetic_module_tensors, synthetic_activation, algorithmic_weight_bytes) -> None:
+    """L distinct layers of one shape back to back from a CUDA graph; one JSON line per row count."""
+    layers, weight_bytes = [], 0
+    for index in range(args.layers):
+        tensors = synthetic_module_tensors(args.n, args.k, seed=1 + index, w4_fraction=args.w4_fraction, device=device)
+        weight_bytes += algorithmic_weight_bytes(tensors)
+        layers.append(ext.prepare_weights(
+            tensors["state_bits"], tensors["w4_payload"], tensors["w4_scales"], tensors["w8_payload"], tensors["w8_scales"],
+            tensors["w4_row_offsets"], tensors["w8_row_offsets"], n_k=args.k // 64,
+        ))
+        del tensors
+    out_dtype = getattr(torch, args.out_dtype)
+    for rows in row_counts:
+        x = synthetic_activation(rows, args.k, seed=2 + rows, device=device)
+        xq, scales = ext.alignquant_activation_quantize_cuda(x, None, scale_mode=args.scale_mode)
+        out = torch.empty((rows, args.n), dtype=out_dtype, device=device)
+
+        def sweep() -> None:
+            for weights in layers:
+                if args.with_quantizer:
+                    ext.alignquant_activation_quantize_cuda(x, None, scale_mode=args.scale_mode, out=(xq, scales))
+                ext.alignquant_linear_prepared(xq, scales, weights, None, schedule=args.schedule, scale_mode=args.scale_mode,
+                                               output_dtype=out_dtype, out=out)
+
+        sweep()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            sweep()
+        for _ in range(3):
+            graph.replay()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(args.repeat):
+            graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        ext.device_status(device)
+        seconds = begin.elapsed_time(end) / 1e3 / args.repeat / args.layers
+        print(json.dumps({
+            "n": args.n, "k": args.k, "rows": rows, "layers": args.layers, "with_quantizer": bool(args.with_quantizer),
+            "plan": ext.linear_plan(rows, args.n // 64, args.k // 64, schedule=args.schedule),
+            "us_per_layer": seconds * 1e6, "weight_gbs": weight_bytes / args.layers / seconds / 1e9,
+            "scale_mode": args.scale_mode, "out_dtype": args.out_dtype,
+        }), flush=True)
 
 
 if __name__ == "__main__":
