@@ -88,12 +88,6 @@ constexpr int kTileWorkers = 8;  // tiles in progress per CTA; WPT warps share o
 constexpr int kMaxCount = 512;  // tiles of one CTA's K range
 constexpr int kNumBars = 2 * kSlots;
 
-// The integer accumulators of a tile start at the bit pattern of 1.5 * 2^23: after the MMAs the
-// same bits, read as a float, are 12582912 + sum exactly (|sum| <= 64 * 128 * 127 < 2^22), so one
-// full-rate subtraction replaces the int-to-float conversion (half rate) and gives the same value.
-constexpr int kIntBias = 0x4B400000;
-__device__ __forceinline__ float biased_to_float(int biased) { return __fsub_rn(__int_as_float(biased), 12582912.0f); }
-
 template <int kConsumerThreads>
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
@@ -264,7 +258,7 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
         const uint4 wb = weight_vector(group + (is_w4 ? 8 * 32 : 8 * 64), is_w4, w8_off, w4_off, w4_shift);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          d[nt][q][0] = d[nt][q][1] = d[nt][q][2] = d[nt][q][3] = kIntBias;
+          d[nt][q][0] = d[nt][q][1] = d[nt][q][2] = d[nt][q][3] = 0;
           mma_s8(d[nt][q], wa.x, wb.x, wa.y, wb.y, x[nt].x, x[nt].y);
           mma_s8(d[nt][q], wa.z, wb.z, wa.w, wb.w, x[nt].z, x[nt].w);
         }
@@ -285,10 +279,10 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          acc[nt][q][0] = __fadd_rn(acc[nt][q][0], __fmul_rn(biased_to_float(d[nt][q][0]), s0));
-          acc[nt][q][1] = __fadd_rn(acc[nt][q][1], __fmul_rn(biased_to_float(d[nt][q][1]), s1));
-          acc[nt][q][2] = __fadd_rn(acc[nt][q][2], __fmul_rn(biased_to_float(d[nt][q][2]), s0));
-          acc[nt][q][3] = __fadd_rn(acc[nt][q][3], __fmul_rn(biased_to_float(d[nt][q][3]), s1));
+          acc[nt][q][0] = __fadd_rn(acc[nt][q][0], __fmul_rn(static_cast<float>(d[nt][q][0]), s0));
+          acc[nt][q][1] = __fadd_rn(acc[nt][q][1], __fmul_rn(static_cast<float>(d[nt][q][1]), s1));
+          acc[nt][q][2] = __fadd_rn(acc[nt][q][2], __fmul_rn(static_cast<float>(d[nt][q][2]), s0));
+          acc[nt][q][3] = __fadd_rn(acc[nt][q][3], __fmul_rn(static_cast<float>(d[nt][q][3]), s1));
         }
         if (p.acc_dump != nullptr) {
           const int shift = is_w4 ? 4 : 0;
@@ -300,7 +294,7 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
               const int t = tok + (e & 1);
               const int col = q * 16 + g + ((e & 2) ? 8 : 0);
               if (t < rows) {
-                p.acc_dump[((static_cast<int64_t>(t) * p.n_j + j) * n_k + kt) * kTile + col] = (d[nt][q][e] - kIntBias) >> shift;
+                p.acc_dump[((static_cast<int64_t>(t) * p.n_j + j) * n_k + kt) * kTile + col] = d[nt][q][e] >> shift;
               }
             }
           }
