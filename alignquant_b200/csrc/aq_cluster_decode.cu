@@ -331,7 +331,13 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
 
   // ---- split-K exchange through cluster shared memory ------------------------------------
   AQ_CT(5);
-  cluster.sync();
+  // A cluster barrier costs about half a microsecond even for a single CTA: without a K split
+  // (one CTA per tile row) a CTA barrier is enough, and nobody reads this CTA's tile remotely.
+  if (split_k > 1) {
+    cluster.sync();
+  } else {
+    __syncthreads();
+  }
   AQ_CT(6);
   if (!producer) {
     const int32_t* meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
@@ -423,7 +429,11 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
     }
   }
   AQ_CT(7);
-  cluster.sync();  // peers may still be reading this CTA's tile
+  if (split_k > 1) {
+    cluster.sync();  // peers may still be reading this CTA's tile
+  } else if (kTp) {
+    __syncthreads();  // every warp has finished its exchange before the call counter may advance
+  }
   AQ_CT(8);
   if (kTp && threadIdx.x == 0) {
     // the last CTA of the grid advances the call counter (the next launch starts after this one ends)
