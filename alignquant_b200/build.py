@@ -33,7 +33,7 @@ def is_stale() -> bool:
     if not LIB_PATH.exists():
         return True
     built = LIB_PATH.stat().st_mtime
-    deps = [CSRC / name for name in SOURCES] + [CSRC / "aq_common.cuh", CSRC / "aq_ptx.cuh", CSRC / "aq_tile_math.cuh", PACKAGE_DIR.parent / "include" / "alignquant_b200.h"]
+    deps = [CSRC / name for name in SOURCES] + sorted(CSRC.glob("*.cuh")) + [PACKAGE_DIR.parent / "include" / "alignquant_b200.h"]
     return any(dep.stat().st_mtime > built for dep in deps)
 
 
