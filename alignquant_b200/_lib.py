@@ -10,6 +10,9 @@ from pathlib import Path
 AQ_OK = 0
 AQ_F16, AQ_BF16, AQ_F32 = 0, 1, 2
 AQ_SCALE_TILE, AQ_SCALE_TOKEN = 0, 1
+AQ_OPT_PEER_POLL_LIMIT, AQ_OPT_GEMM_ROUNDING, AQ_OPT_GEMM_TILE, AQ_OPT_GEMM_SPLIT = 1, 2, 3, 4
+AQ_GEMM_ROUNDING_FUSED, AQ_GEMM_ROUNDING_SEPARATE = 0, 1
+GEMM_TILES = {"auto": 0, "paired": 1, "narrow": 2, "wide": 4}
 SCHEDULE_CODES = {"auto": 0, "forced_decode": 1, "forced_prefill": 2, "forced_prefill_m64": 3}
 
 _P = ctypes.c_void_p
@@ -26,11 +29,15 @@ SIGNATURES = {
     "aq_repack": (_INT, [_P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I64, _I64, _P, _I64, _P]),
     "aq_linear_workspace_bytes": (_I64, [_I64, _I32, _I32, _INT, _INT]),
     "aq_linear": (_INT, [_P, _P, _INT, _I64, _P, _I32, _I32, _P, _INT, _INT, _INT, _P, _P, _I64, _P, _P]),
+    "aq_set_option": (_INT, [_INT, _I64]),
+    "aq_get_option": (_I64, [_INT]),
+    "aq_linear_ahead": (_INT, [_P, _P, _INT, _I64, _P, _I32, _I32, _P, _INT, _INT, _INT, _P, _P, _I64, _P, _P, _I64, _P]),
     "aq_linear_decode_static": (_INT, [_P, _P, _INT, _I64, _P, _I32, _I32, _P, _INT, _P, _P]),
     "aq_linear_plan": (_INT, [_I64, _I32, _I32, _INT, _INT, _P, _P, _P]),
     "aq_allreduce_buffer_bytes": (_I64, [_I32, _I64]),
     "aq_allreduce_f32": (_INT, [_P, _P, _I64, _I32, _I32, _P, _I64, _P]),
-    "aq_linear_allreduce": (_INT, [_P, _P, _INT, _I64, _P, _I32, _I32, _P, _INT, _P, _I32, _I32, _P, _I64, _P]),
+    "aq_linear_allreduce": (_INT, [_P, _P, _INT, _I64, _P, _I32, _I32, _P, _INT, _P, _I32, _I32, _P, _I64, _P, _I64, _P]),
+    "aq_measure_int8_peak": (_INT, [_I32, _P, _P]),
     "aq_device_status": (_INT, [_P]),
 }
 

@@ -1,6 +1,7 @@
 // extern "C" entry points of libalignquant_b200.so: argument validation and dispatch.
 // The checks mirror the argument contract of the reference host functions
 // (alignquant/kernels/cuda/linear.cu:1520-1533, 1578-1672) in terms of raw pointers.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -56,6 +57,19 @@ bool use_dependent_launch() {
 }
 
 namespace {
+constexpr int64_t kDefaultPeerPollLimit = 1LL << 22;
+std::atomic<int64_t> g_peer_poll_limit{kDefaultPeerPollLimit};
+std::atomic<int64_t> g_gemm_rounding{0};
+std::atomic<int64_t> g_gemm_tile{0};
+std::atomic<int64_t> g_gemm_split{0};
+}  // namespace
+
+uint32_t peer_poll_limit() { return static_cast<uint32_t>(g_peer_poll_limit.load(std::memory_order_relaxed)); }
+bool gemm_separate_rounding() { return g_gemm_rounding.load(std::memory_order_relaxed) != 0; }
+int gemm_tile_option() { return static_cast<int>(g_gemm_tile.load(std::memory_order_relaxed)); }
+int gemm_split_option() { return static_cast<int>(g_gemm_split.load(std::memory_order_relaxed)); }
+
+namespace {
 
 constexpr int64_t kStreamMaxRows = 128;  // most rows of the streaming cluster kernel (explicit schedules)
 constexpr int64_t kAutoGemmRows = 32;    // above this the automatic schedule uses the GEMM (split-K for few rows)
@@ -86,7 +100,52 @@ using namespace aq;
 
 extern "C" {
 
-int aq_version(void) { return 100; }
+int aq_version(void) { return 200; }
+
+int aq_set_option(int option, int64_t value) {
+  switch (option) {
+    case AQ_OPT_PEER_POLL_LIMIT:
+      AQ_REQUIRE(value >= 64 && value < (1LL << 31), "AQ_OPT_PEER_POLL_LIMIT must be in [64, 2^31), got %lld",
+                 static_cast<long long>(value));
+      g_peer_poll_limit.store(value, std::memory_order_relaxed);
+      return AQ_OK;
+    case AQ_OPT_GEMM_ROUNDING:
+      AQ_REQUIRE(value == AQ_GEMM_ROUNDING_FUSED || value == AQ_GEMM_ROUNDING_SEPARATE,
+                 "AQ_OPT_GEMM_ROUNDING must be AQ_GEMM_ROUNDING_FUSED or AQ_GEMM_ROUNDING_SEPARATE, got %lld",
+                 static_cast<long long>(value));
+      g_gemm_rounding.store(value, std::memory_order_relaxed);
+      return AQ_OK;
+    case AQ_OPT_GEMM_TILE:
+      AQ_REQUIRE(value == AQ_GEMM_TILE_AUTO || value == AQ_GEMM_TILE_PAIRED || value == AQ_GEMM_TILE_NARROW ||
+                     value == AQ_GEMM_TILE_WIDE,
+                 "AQ_OPT_GEMM_TILE must be one of the AQ_GEMM_TILE_* values, got %lld", static_cast<long long>(value));
+      g_gemm_tile.store(value, std::memory_order_relaxed);
+      return AQ_OK;
+    case AQ_OPT_GEMM_SPLIT:
+      AQ_REQUIRE(value >= 0 && value <= 8, "AQ_OPT_GEMM_SPLIT must be 0 (automatic) or 1..8, got %lld",
+                 static_cast<long long>(value));
+      g_gemm_split.store(value, std::memory_order_relaxed);
+      return AQ_OK;
+    default:
+      return fail(AQ_ERR_INVALID, "unknown option %d", option);
+  }
+}
+
+int64_t aq_get_option(int option) {
+  switch (option) {
+    case AQ_OPT_PEER_POLL_LIMIT:
+      return g_peer_poll_limit.load(std::memory_order_relaxed);
+    case AQ_OPT_GEMM_ROUNDING:
+      return g_gemm_rounding.load(std::memory_order_relaxed);
+    case AQ_OPT_GEMM_TILE:
+      return g_gemm_tile.load(std::memory_order_relaxed);
+    case AQ_OPT_GEMM_SPLIT:
+      return g_gemm_split.load(std::memory_order_relaxed);
+    default:
+      fail(AQ_ERR_INVALID, "unknown option %d", option);
+      return AQ_ERR_INVALID;
+  }
+}
 
 const char* aq_last_error(void) { return last_error_storage().c_str(); }
 
@@ -164,10 +223,16 @@ struct TensorParallelSum {
   int64_t max_count;
 };
 
+struct LookAhead {
+  const void* data;
+  int64_t bytes;
+};
+
 static int linear_impl(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
                        const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
                        int schedule, int decode_splits, int out_dtype, void* out, void* workspace,
-                       int64_t workspace_bytes, int32_t* acc_dump, const TensorParallelSum* tp, void* stream) {
+                       int64_t workspace_bytes, int32_t* acc_dump, const TensorParallelSum* tp,
+                       const LookAhead* ahead, void* stream) {
   AQ_REQUIRE(xq != nullptr && act_scales != nullptr && prepared != nullptr && out != nullptr,
              "xq, act_scales, prepared and out must not be NULL");
   AQ_REQUIRE(m >= 1, "x_int8 must have at least one row");
@@ -211,6 +276,12 @@ static int linear_impl(const int8_t* xq, const float* act_scales, int scale_mode
   a.acc_dump = acc_dump;
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;
+  if (ahead != nullptr && ahead->data != nullptr && ahead->bytes > 0) {
+    AQ_REQUIRE(aligned(ahead->data, 16) && (ahead->bytes & 15) == 0,
+               "the look-ahead range must be 16-byte aligned and a multiple of 16 bytes long");
+    a.prefetch = ahead->data;
+    a.prefetch_bytes = ahead->bytes;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   const int kernel = choose_kernel(m, n_j, n_k, schedule, decode_splits);
@@ -244,13 +315,25 @@ int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, int64_t
               int schedule, int decode_splits, int out_dtype, void* out, void* workspace,
               int64_t workspace_bytes, int32_t* acc_dump, void* stream) {
   return linear_impl(xq, act_scales, scale_mode, m, prepared, n_j, n_k, u_metadata, schedule, decode_splits, out_dtype,
-                     out, workspace, workspace_bytes, acc_dump, nullptr, stream);
+                     out, workspace, workspace_bytes, acc_dump, nullptr, nullptr, stream);
+}
+
+int aq_linear_ahead(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
+                    const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
+                    int schedule, int decode_splits, int out_dtype, void* out, void* workspace,
+                    int64_t workspace_bytes, int32_t* acc_dump, const void* next_prepared,
+                    int64_t next_bytes, void* stream) {
+  AQ_REQUIRE(next_bytes >= 0, "next_bytes must not be negative");
+  const LookAhead ahead = {next_prepared, next_bytes};
+  return linear_impl(xq, act_scales, scale_mode, m, prepared, n_j, n_k, u_metadata, schedule, decode_splits, out_dtype,
+                     out, workspace, workspace_bytes, acc_dump, nullptr, &ahead, stream);
 }
 
 int aq_linear_allreduce(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
                         const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
                         int out_dtype, void* out, int32_t rank, int32_t world, void* const* peer_buffers,
-                        int64_t max_count, void* stream) {
+                        int64_t max_count, const void* next_prepared, int64_t next_bytes, void* stream) {
+  AQ_REQUIRE(next_bytes >= 0, "next_bytes must not be negative");
   AQ_REQUIRE(peer_buffers != nullptr, "peer_buffers must not be NULL");
   AQ_REQUIRE(world >= 2 && world <= allreduce_max_ranks(), "world must be 2..%d, got %d", allreduce_max_ranks(), world);
   AQ_REQUIRE(rank >= 0 && rank < world, "rank must be in [0, world)");
@@ -261,8 +344,9 @@ int aq_linear_allreduce(const int8_t* xq, const float* act_scales, int scale_mod
     AQ_REQUIRE(peer_buffers[r] != nullptr && aligned(peer_buffers[r], 16), "peer_buffers[%d] must be a 16-byte aligned device pointer", r);
   }
   const TensorParallelSum tp = {rank, world, peer_buffers, max_count};
+  const LookAhead ahead = {next_prepared, next_bytes};
   return linear_impl(xq, act_scales, scale_mode, m, prepared, n_j, n_k, u_metadata, AQ_SCHEDULE_AUTO, 0, out_dtype, out,
-                     nullptr, 0, nullptr, &tp, stream);
+                     nullptr, 0, nullptr, &tp, &ahead, stream);
 }
 
 int aq_linear_decode_static(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
@@ -345,6 +429,12 @@ int aq_allreduce_f32(const float* partial, float* out, int64_t count, int32_t ra
     AQ_REQUIRE(peer_buffers[r] != nullptr && aligned(peer_buffers[r], 16), "peer_buffers[%d] must be a 16-byte aligned device pointer", r);
   }
   return launch_allreduce(partial, out, count, rank, world, peer_buffers, max_count, static_cast<cudaStream_t>(stream));
+}
+
+int aq_measure_int8_peak(int32_t pairs, double* tops, void* stream) {
+  AQ_REQUIRE(tops != nullptr, "tops must not be NULL");
+  AQ_REQUIRE(pairs >= 16 && pairs <= (1 << 20), "pairs must be in [16, 2^20], got %d", pairs);
+  return measure_int8_peak(pairs, tops, static_cast<cudaStream_t>(stream));
 }
 
 int aq_device_status(void* stream) {

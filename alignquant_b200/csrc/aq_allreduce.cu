@@ -1,6 +1,7 @@
 // Sum of the partial outputs of a row-parallel projection over the ranks of one node,
-// through peer memory (NVLink / NVSwitch), for the small messages of decode
-// (reference: dist.all_reduce after a row-parallel linear, alignquant/quantization/model.py:352-356).
+// through peer memory (NVLink / NVSwitch), for the small messages of decode.  The reference has
+// no counterpart: it runs on one GPU and contains no collective; this replaces the
+// dist.all_reduce that tensor parallelism needs after a row-parallel projection.
 //
 // Every rank owns one "exchange buffer" that all peers have mapped:
 //   [ call counter, CTA counter | pad to 1024 B | recv[2][world][max_count] x {float value, uint32 epoch} ]
@@ -33,7 +34,6 @@ constexpr int kBlocks = 16;
 constexpr int kMaxRanks = kArMaxRanks;
 constexpr int kThreads = 256;
 constexpr int kHeaderBytes = kArHeaderBytes;
-constexpr uint32_t kPollLimit = 1u << 22;
 static_assert(kBlocks * 4 <= kHeaderBytes, "header too small");
 
 using Peers = ArPeers;
@@ -51,7 +51,7 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
 __global__ void __launch_bounds__(kThreads) allreduce_push_kernel(const float* __restrict__ partial,
                                                                   float* __restrict__ out, int64_t count,
                                                                   int rank, int world, int64_t max_count,
-                                                                  const Peers peers) {
+                                                                  uint32_t poll_limit, const Peers peers) {
   __shared__ uint32_t epoch_shared;
   const int b = blockIdx.x;
   const int blocks = static_cast<int>(gridDim.x);
@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_push_kernel(const float* _
         uint4 hi = ld_volatile_v4(unit + 1);
         uint32_t polls = 0;
         while (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch) {
-          if (++polls >= kPollLimit) {
+          if (++polls >= poll_limit) {
             atomicCAS(&g_allreduce_status, 0, 1 + r);
             break;
           }
@@ -150,7 +150,8 @@ int launch_allreduce(const float* partial, float* out, int64_t count, int rank, 
   config.stream = stream;
   config.attrs = nullptr;
   config.numAttrs = 0;
-  return check_cuda(cudaLaunchKernelEx(&config, allreduce_push_kernel, partial, out, count, rank, world, max_count, peers),
+  return check_cuda(cudaLaunchKernelEx(&config, allreduce_push_kernel, partial, out, count, rank, world, max_count,
+                                       peer_poll_limit(), peers),
                     "peer all-reduce launch");
 }
 

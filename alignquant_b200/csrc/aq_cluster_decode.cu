@@ -34,22 +34,6 @@ namespace aq {
 
 __device__ int g_cluster_decode_status = 0;
 
-#ifdef AQ_TRACE
-// Development aid: %globaltimer time stamps (ns) of a few CTAs, slot = 16 * sample + event.
-__device__ long long g_cluster_trace[1024];
-__device__ __forceinline__ long long global_ns() {
-  long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define AQ_CT(event)                                                                                   \
-  do {                                                                                                 \
-    if ((threadIdx.x & 31) == 0 && trace_sample >= 0) g_cluster_trace[16 * trace_sample + (event)] = global_ns(); \
-  } while (0)
-#else
-#define AQ_CT(event) do { } while (0)
-#endif
-
 namespace {
 
 struct Params {
@@ -70,6 +54,10 @@ struct Params {
   int tp_rank;
   int tp_world;
   int64_t ar_max_count;
+  uint32_t ar_poll_limit;
+  // look-ahead prefetch of the next projection's image into L2 (prefetch_bytes == 0: none)
+  const uint8_t* prefetch;
+  int64_t prefetch_bytes;
 };
 
 __device__ __forceinline__ void st_volatile_v2(void* p, uint32_t a, uint32_t b) {
@@ -135,12 +123,6 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
   const int groups = (count + kGroupTiles - 1) / kGroupTiles;
   const int rows = p.m < kRows ? static_cast<int>(p.m) : kRows;
 
-#ifdef AQ_TRACE
-  const int cta_linear = blockIdx.x * gridDim.y + blockIdx.y;
-  const int cta_total = gridDim.x * gridDim.y;
-  const int trace_sample = (threadIdx.x >> 5) != 0 ? -1 : cta_linear == 0 ? 0 : cta_linear == cta_total / 2 ? 1 : cta_linear == cta_total - 1 ? 2 : -1;
-  AQ_CT(0);
-#endif
   const uint32_t bar0 = smem_u32(bars);
   auto full = [&](int s) { return bar0 + 8u * s; };
   auto empty = [&](int s) { return bar0 + 8u * (kSlots + s); };
@@ -170,11 +152,16 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
     bulk_copy(ring_addr + lane * kSlotBytes,
               p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(lane));
   }
+  // Look-ahead: while this projection runs, the L2 cache fetches the image of the next one, so
+  // that HBM keeps streaming through this kernel's start-up and split-K hand-over and the next
+  // kernel finds its weights on chip.  Requested after this CTA's own first fill.
+  if (producer && lane == 0 && p.prefetch_bytes > 0) {
+    prefetch_slice_l2(p.prefetch, p.prefetch_bytes, static_cast<int64_t>(blockIdx.x) * gridDim.y + blockIdx.y,
+                      static_cast<int64_t>(gridDim.x) * gridDim.y);
+  }
   for (int i = threadIdx.x; i < count; i += kThreads) recs[i] = my_records[i];
-  AQ_CT(1);
   grid_launch_dependents();
   grid_dependency_wait();  // activations and their scales come from the preceding kernel
-  AQ_CT(2);
   __shared__ uint32_t ar_epoch_shared;
   if (kTp && threadIdx.x == 0) {
     ar_epoch_shared = *reinterpret_cast<const volatile uint32_t*>(p.peers.buffer[p.tp_rank]) + 1;  // number of this call
@@ -244,7 +231,6 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
       for (int nt = 0; nt < NT; ++nt) x[nt] = x_next[nt];
       if (i + kTileWorkers < count) load_x(i + kTileWorkers, x_next);
       if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_cluster_decode_status, 32)) break;
-      if (i == worker) AQ_CT(3);
       const TileRecord rec = recs[i];
       const TileRecord rec0 = recs[gi * kGroupTiles];
       const bool is_w4 = (rec.offset_flag & kW4Flag) != 0;
@@ -301,7 +287,6 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
         }
       }
     }
-    AQ_CT(4);
     // ---- combine the eight warp sums in warp order -----------------------------------------
     if (kSlabsInRing) consumer_sync<kConsumerThreads>();  // every warp has consumed its last tile: the ring becomes the slabs
     float* slab = slabs + worker * kRows * kTile;
@@ -330,7 +315,6 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
   }
 
   // ---- split-K exchange through cluster shared memory ------------------------------------
-  AQ_CT(5);
   // A cluster barrier costs about half a microsecond even for a single CTA: without a K split
   // (one CTA per tile row) a CTA barrier is enough, and nobody reads this CTA's tile remotely.
   if (split_k > 1) {
@@ -338,7 +322,6 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
   } else {
     __syncthreads();
   }
-  AQ_CT(6);
   if (!producer) {
     const int32_t* meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
     const bool has_u = meta != nullptr && meta[0] != 0;
@@ -408,7 +391,7 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
               uint2 ub = ld_volatile_v2(units + 32 * 8);
               uint32_t polls = 0;
               while (ua.y != epoch || ub.y != epoch) {
-                if (++polls >= (1u << 22)) {
+                if (++polls >= p.ar_poll_limit) {
                   atomicCAS(&g_cluster_decode_status, 0, 40 + r);
                   break;
                 }
@@ -428,13 +411,11 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
       }
     }
   }
-  AQ_CT(7);
   if (split_k > 1) {
     cluster.sync();  // peers may still be reading this CTA's tile
   } else if (kTp) {
     __syncthreads();  // every warp has finished its exchange before the call counter may advance
   }
-  AQ_CT(8);
   if (kTp && threadIdx.x == 0) {
     // the last CTA of the grid advances the call counter (the next launch starts after this one ends)
     uint32_t* counters = reinterpret_cast<uint32_t*>(p.peers.buffer[p.tp_rank]);
@@ -582,18 +563,15 @@ int launch_cluster_decode(const LinearArgs& a, cudaStream_t stream) {
   p.tp_rank = a.tp_rank;
   p.tp_world = a.peer_buffers != nullptr ? a.tp_world : 1;
   p.ar_max_count = a.ar_max_count;
+  p.ar_poll_limit = peer_poll_limit();
+  p.prefetch = static_cast<const uint8_t*>(a.prefetch);
+  p.prefetch_bytes = a.prefetch != nullptr ? a.prefetch_bytes : 0;
   for (int r = 0; r < kArMaxRanks; ++r) {
     p.peers.buffer[r] = (a.peer_buffers != nullptr && r < a.tp_world) ? static_cast<uint8_t*>(a.peer_buffers[r]) : nullptr;
   }
   const int split = cluster_decode_split(a.m, a.n_j, a.n_k);
   return launch_variant(variant_for(a.m), p, split, stream);
 }
-
-#ifdef AQ_TRACE
-extern "C" __attribute__((visibility("default"))) int aq_debug_read_cluster_trace(long long* dst) {
-  return static_cast<int>(cudaMemcpyFromSymbol(dst, g_cluster_trace, sizeof(long long) * 1024));
-}
-#endif
 
 int take_cluster_decode_status() {
   int status = 0;

@@ -76,6 +76,10 @@ struct LinearArgs {
   int tp_rank = 0;
   int tp_world = 1;
   int64_t ar_max_count = 0;
+  // Look-ahead: bytes of this GPU's memory (the prepared image of the projection that runs
+  // next) that the decode kernels ask the L2 cache to fetch while they run; nullptr: none.
+  const void* prefetch = nullptr;
+  int64_t prefetch_bytes = 0;
 };
 
 // Layout of a peer exchange buffer (shared by aq_allreduce.cu and the fused decode epilogue):
@@ -111,6 +115,9 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream);
 int64_t tmem_gemm_workspace_bytes(int64_t m, int n_j, int n_k);
 int tmem_gemm_split(int64_t m, int n_j, int n_k);  // K ranges (cluster size) the GEMM will use
 
+// Rate of back-to-back tcgen05.mma kind::i8 on all SMs (measurement aid; synchronises).
+int measure_int8_peak(int pairs, double* tops, cudaStream_t stream);
+
 // Sum of per-rank partial outputs through peer memory (one node, one process per GPU).
 int launch_allreduce(const float* partial, float* out, int64_t count, int rank, int world, void* const* peer_buffers,
                      int64_t max_count, cudaStream_t stream);
@@ -121,6 +128,12 @@ int take_allreduce_status();
 // -1 = the word could not be read).
 int take_stream_status();
 int take_gemm_status();
+// Library options (aq_set_option): polls of a peer's data before a tensor-parallel sum gives
+// up, and whether the GEMM rounds multiply and add separately.
+uint32_t peer_poll_limit();
+bool gemm_separate_rounding();
+int gemm_tile_option();   // AQ_GEMM_TILE_*
+int gemm_split_option();  // 0 = automatic, 1..8 forced
 // Whether kernels are launched with programmatic stream serialization (dependent
 // launch); on by default, ALIGNQUANT_B200_PDL=0 turns it off.
 bool use_dependent_launch();

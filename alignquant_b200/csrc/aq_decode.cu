@@ -39,15 +39,6 @@ namespace aq {
 
 __device__ int g_decode_status = 0;
 
-#ifdef AQ_TRACE
-// Development aid: timestamps of CTA 0 (consumer warp 0 and the producer), 4096 slots.
-__device__ long long g_trace[4096];
-#define AQ_TRACE_MARK(slot) \
-  do { if (blockIdx.x == 0 && lane == 0 && (slot) < 4096) g_trace[(slot)] = clock64(); } while (0)
-#else
-#define AQ_TRACE_MARK(slot) do { } while (0)
-#endif
-
 namespace {
 
 struct DecodeParams {
@@ -67,6 +58,9 @@ struct DecodeParams {
   int ctas;
   int scale_mode;
   int out_dtype;
+  // look-ahead prefetch of the next projection's image into L2 (prefetch_bytes == 0: none)
+  const uint8_t* prefetch;
+  int64_t prefetch_bytes;
 };
 
 constexpr int kGroupTiles = 8;  // tiles per ring slot: one copy and one full/empty barrier pair per slot
@@ -106,6 +100,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
   uint64_t* bars = reinterpret_cast<uint64_t*>(recs + kMaxRecords);
   volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(bars + kNumBars);
   volatile uint32_t* last_flag = abort_flag + 1;
+  volatile uint32_t* segment_abort = abort_flag + 2;  // the abort flag as thread 0 saw it between two barriers
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -121,7 +116,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
   auto empty = [&](int s) { return bar0 + 8u * (kSlots + s); };
   const uint32_t ring_addr = smem_u32(ring);
 
-  if (warp == 0) AQ_TRACE_MARK(4000);
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(full(s), 1);
@@ -148,11 +142,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
     bulk_copy(ring_addr + lane * kSlotBytes,
               p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(lane));
   }
+  // Look-ahead: the L2 cache fetches the image of the projection that runs next while this one
+  // streams; requested after this CTA's own first fill.
+  if (producer && lane == 0 && p.prefetch_bytes > 0) prefetch_slice_l2(p.prefetch, p.prefetch_bytes, blockIdx.x, gridDim.x);
   for (int i = threadIdx.x; i < count; i += kThreads) recs[i] = my_records[i];
   grid_launch_dependents();
   grid_dependency_wait();  // activations, scales, workspace and output belong to earlier kernels
   __syncthreads();
-  if (warp == 0) AQ_TRACE_MARK(4001);
 
   if (producer) {
     // ---- refills: one copy per slot -----------------------------------------------------
@@ -160,7 +156,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
       for (int gi = kSlots; gi < groups; ++gi) {
         const int slot = gi % kSlots;
         if (!mbar_wait(empty(slot), ((gi / kSlots) - 1) & 1, abort_flag, &g_decode_status, 21)) break;
-        AQ_TRACE_MARK(2048 + 2 * gi);
         const int first = gi * kGroupTiles;
         const int last = (first + kGroupTiles < count ? first + kGroupTiles : count) - 1;
         const TileRecord rf = recs[first];
@@ -168,7 +163,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
         mbar_expect_tx(full(slot), bytes);
         bulk_copy(ring_addr + slot * kSlotBytes,
                   p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(slot));
-        AQ_TRACE_MARK(2048 + 2 * gi + 1);
       }
     }
     return;
@@ -213,7 +207,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
     }
   }
 
-  bool ok = true;
   bool first_segment = true;
   int pos = 0;  // first tile (index inside the range) of the current row segment
   // this warp's next tile and its activation vectors, requested one tile ahead
@@ -221,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
   uint4 x_next[NT];
   if (mine < count) load_x(mine, x_next);
 
-  while (pos < count && ok) {
+  while (pos < count) {
     const int64_t t_first = t0 + pos;
     const int j = static_cast<int>(t_first / n_k);
     const int k_lo = static_cast<int>(t_first - static_cast<int64_t>(j) * n_k);
@@ -239,12 +232,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) x[nt] = x_next[nt];
       if (i + kConsumerWarps < count) load_x(i + kConsumerWarps, x_next);
-      if (warp == 0) AQ_TRACE_MARK(100 + 2 * (i / kConsumerWarps));
-      if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_decode_status, 22)) {
-        ok = false;
-        break;
-      }
-      if (warp == 0) AQ_TRACE_MARK(101 + 2 * (i / kConsumerWarps));
+      // A wait that gives up (or sees another thread's abort) only leaves the tile loop: the warp
+      // still goes to the barriers below, where all sixteen warps leave together.
+      if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_decode_status, 22)) break;
       const TileRecord rec = recs[i];
       const TileRecord rec0 = recs[gi * kGroupTiles];
       const bool is_w4 = (rec.offset_flag & kW4Flag) != 0;
@@ -301,10 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
         }
       }
     }
-    if (!ok) break;
-
     // ---- finish the segment: combine the sixteen warp sums in warp order --------------------
-    if (warp == 0) AQ_TRACE_MARK(3000 + 8 * (first_segment ? 0 : 1));
     {
       float* slab = slabs + warp * kRows * kTile;
 #pragma unroll
@@ -322,6 +309,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
       }
     }
     consumer_sync();
+    // One thread samples the abort flag between the two barriers and every warp reads that sample
+    // after the second one, so the decision to leave is the same in all sixteen warps whenever the
+    // flag was raised (the producer may raise it at any time).
+    if (threadIdx.x == 0) *segment_abort = *abort_flag;
     for (int e = threadIdx.x; e < kRows * kTile; e += kConsumerThreads) {
       float v = slabs[e];
 #pragma unroll
@@ -329,7 +320,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
       tile[e] = v;
     }
     consumer_sync();
-    if (warp == 0) AQ_TRACE_MARK(3001 + 8 * (first_segment ? 0 : 1));
+    // Aborting: nothing of this segment is published, counted or stored.  The workspace
+    // counters of rows already counted stay as they are (zero it again after AQ_ERR_DEVICE).
+    if (*segment_abort != 0) break;
     const int32_t* meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
     const bool has_u = meta != nullptr && meta[0] != 0;
     int first_cta = blockIdx.x, last_cta = blockIdx.x;
@@ -352,7 +345,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
       consumer_sync();
       finish = *last_flag != 0;
       if (finish) __threadfence();
-      if (warp == 0) AQ_TRACE_MARK(3002 + 8 * (first_segment ? 0 : 1));
     }
     if (finish) {
       for (int row = warp; row < rows; row += kConsumerWarps) {
@@ -380,14 +372,13 @@ __global__ void __launch_bounds__(kThreads, 1) decode_linear_kernel(const Decode
       }
     }
     consumer_sync();  // slabs, tile and the last-arriver flag are reused by the next segment
-    if (warp == 0) AQ_TRACE_MARK(3003 + 8 * (first_segment ? 0 : 1));
     first_segment = false;
     pos = seg_end;
   }
 }
 
 int smem_bytes(int mt) {
-  return kSlots * kSlotBytes + (kConsumerWarps + 1) * 8 * mt * kTile * 4 + kMaxRecords * 8 + kNumBars * 8 + 16;
+  return kSlots * kSlotBytes + (kConsumerWarps + 1) * 8 * mt * kTile * 4 + kMaxRecords * 8 + kNumBars * 8 + 16;  // 16: three flag words
 }
 
 template <int MT>
@@ -454,14 +445,10 @@ int launch_decode_linear(const LinearArgs& a, cudaStream_t stream) {
   p.ctas = decode_ctas(a.n_j, a.n_k);
   p.scale_mode = a.scale_mode;
   p.out_dtype = a.out_dtype;
+  p.prefetch = static_cast<const uint8_t*>(a.prefetch);
+  p.prefetch_bytes = a.prefetch != nullptr ? a.prefetch_bytes : 0;
   return a.m <= 8 ? launch_mt<1>(p, stream) : launch_mt<2>(p, stream);
 }
-
-#ifdef AQ_TRACE
-extern "C" __attribute__((visibility("default"))) int aq_debug_read_trace(long long* dst) {
-  return static_cast<int>(cudaMemcpyFromSymbol(dst, g_trace, sizeof(long long) * 4096));
-}
-#endif
 
 // ---- allocation-free variant ------------------------------------------------------------
 // Scratch for callers that cannot hand over a workspace (see aq_linear_decode_static in
@@ -474,6 +461,19 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 int64_t decode_static_scratch_bytes() { return kStaticScratchBytes; }
 
 int launch_decode_linear_static(const LinearArgs& args, cudaStream_t stream) {
+  // Everything that can be refused is refused first: no stream work and no symbol look-up on an
+  // error path.
+  if (args.n_j > kMaxCounterRows) {
+    return fail(AQ_ERR_INVALID, "the decode kernel supports N up to %d, got %lld", kMaxCounterRows * kTile,
+                static_cast<long long>(args.n_j) * kTile);
+  }
+  const int64_t need = decode_workspace_bytes(args.m, args.n_j, args.n_k);
+  if (need > kStaticScratchBytes) {
+    return fail(AQ_ERR_WORKSPACE,
+                "this layer needs %lld bytes of scratch, the built-in scratch holds %lld; use aq_linear with a "
+                "caller-owned workspace",
+                static_cast<long long>(need), static_cast<long long>(kStaticScratchBytes));
+  }
   // In host code `g_static_scratch` is only a handle for the symbol; the device address
   // has to be looked up, once per device, with that device current.
   static std::mutex mutex;
@@ -492,13 +492,6 @@ int launch_decode_linear_static(const LinearArgs& args, cudaStream_t stream) {
       device_address[device] = address;
     }
     scratch = device_address[device];
-  }
-  const int64_t need = decode_workspace_bytes(args.m, args.n_j, args.n_k);
-  if (need > kStaticScratchBytes) {
-    return fail(AQ_ERR_WORKSPACE,
-                "this layer needs %lld bytes of scratch, the built-in scratch holds %lld; use aq_linear with a "
-                "caller-owned workspace",
-                static_cast<long long>(need), static_cast<long long>(kStaticScratchBytes));
   }
   // The array keeps whatever the previous call left behind; only the arrival counters of
   // the rows this call touches have to start at zero.

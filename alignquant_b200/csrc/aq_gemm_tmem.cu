@@ -1,7 +1,8 @@
 // Mixed W4/W8 x A8 GEMM for large row counts on the Blackwell tensor cores (sm_100a).
 //
 // One CTA computes a 128-row x 256-column output tile (four 64-column weight tile
-// rows) and walks K in 64-wide steps through an 8-stage shared-memory ring.  Roles:
+// rows) and walks K in 64-wide steps through an 8-stage shared-memory ring.  Roles of the
+// sixteen warps of that layout (the 128-column layouts are described at struct Layout):
 //   * warps 6-7 stream the weights: one bulk asynchronous copy (cp.async.bulk) per tile
 //     of the prepared image and K step.  A W8 tile is stored in the K-major 64-byte-swizzle
 //     operand layout, so its copy signals the stage's "ready" mbarrier directly; a W4 tile
@@ -17,10 +18,12 @@
 //   * warp 4: one thread issues tcgen05.mma kind::i8 (M=128, N<=256, K=32, twice per
 //     step) into one of two 256-column tensor-memory accumulators and commits to
 //     mbarriers (stage free, accumulator full);
-//   * warps 8-15 drain: tcgen05.ld the int32 accumulator, scale by
-//     (activation scale * tile scale) and add into FP32 registers -- integer
+//   * warps 8-15 drain: tcgen05.ld the int32 accumulator, convert, and add
+//     float(int32) * (activation scale * tile scale) into FP32 registers -- integer
 //     accumulation never spans two K64 tiles because every tile has its own scale
-//     (operation order of alignquant/kernels/cuda/linear.cu:951-963).
+//     (alignquant/kernels/cuda/linear.cu:951-963).  By default a tile is added with one
+//     packed fused multiply-add; the reference kernels' separately rounded multiply and add
+//     is a library option (AQ_OPT_GEMM_ROUNDING).
 // The epilogue stages rows through shared memory so that global stores are coalesced
 // and applies the inverse output transform (linear.cu:983-1040) where a tile has one.
 //
@@ -30,7 +33,6 @@
 #include <cooperative_groups.h>
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "aq_common.cuh"
@@ -44,42 +46,40 @@ namespace aq {
 
 __device__ int g_gemm_status = 0;
 
-#ifdef AQ_TRACE
-// Development aid: timestamps of CTA (0,0).
-__device__ long long g_gemm_trace[4096];
-#define AQ_GT(slot) \
-  do { if (blockIdx.x == 0 && blockIdx.y == 0 && (slot) < 4096) g_gemm_trace[(slot)] = clock64(); } while (0)
-#define AQ_SUM_BEGIN() long long aq_t = clock64()
-#define AQ_SUM_MARK(i) do { const long long n = clock64(); aq_sums[i] += n - aq_t; aq_t = n; } while (0)
-#define AQ_SUM_WRITE(slot) \
-  do { if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) for (int i = 0; i < 4; ++i) g_gemm_trace[(slot) + i] = aq_sums[i]; } while (0)
-#else
-#define AQ_GT(slot) do { } while (0)
-#define AQ_SUM_BEGIN() do { } while (0)
-#define AQ_SUM_MARK(i) do { } while (0)
-#define AQ_SUM_WRITE(slot) do { } while (0)
-#endif
-
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kStages = 8;
 constexpr int kABytes = kBM * kTile;  // 8192
 constexpr int kMaxNk = 512;
-constexpr int kThreads = 512;
-constexpr int kDrainWarps = 8;
-constexpr int kFirstDrainWarp = 8;
-constexpr int kMmaWarp = 4;
-constexpr int kActWarp = 5;
-constexpr int kFirstCopyWarp = 6;
 constexpr int kEpiRowFloats = 65;
-constexpr int kTmemColumns = 512;
 
-// Sizes that depend on the width of the CTA tile: TN weight tile rows (64 columns each).
-// The 512 tensor-memory columns hold 512 / (64 * TN) accumulators: two for the 256-column
-// tile, four for the 128-column tile, which is used where the wider one would leave SMs idle.
-template <int TN>
-struct Shape {
+// Geometry and warp roles of a kernel variant.  TN = weight tile rows (64 columns each) of the
+// CTA tile; kPaired = two small CTAs per SM instead of one large one.
+//   large CTA (512 threads, one per SM): warps 0..TN-1 widen, 4 issues the MMAs, 5 streams the
+//     activations, 6-7 the weights, 8-15 drain (lane quarter x column half); 512 tensor-memory
+//     columns = 512 / (64 TN) accumulators.  TN = 4 is the default tile, TN = 2 is used where
+//     the wider grid would leave SMs idle.
+//   paired CTA (256 threads, TN = 2, two per SM): warp 0 issues the MMAs, warp 1 streams
+//     activations and weights, warps 2-3 widen, warps 4-7 drain (one per lane quarter, all 128
+//     columns); 256 tensor-memory columns = two accumulators; six stages of 16 KiB.  The step
+//     of one CTA (wait, load, convert, hand the accumulator back) is a chain of latencies; the
+//     second CTA of the SM fills the gaps of the first.
+template <int TN, bool kPaired>
+struct Layout {
+  static_assert(!kPaired || TN == 2, "the paired layout is 128 columns wide");
+  static constexpr int kThreads = kPaired ? 256 : 512;
+  static constexpr int kCtasPerSm = kPaired ? 2 : 1;
+  static constexpr int kStages = kPaired ? 6 : 8;
+  static constexpr int kTmemColumns = kPaired ? 256 : 512;
+  static constexpr int kMmaWarp = kPaired ? 0 : 4;
+  static constexpr int kActWarp = kPaired ? 1 : 5;
+  static constexpr int kFirstCopyWarp = kPaired ? 1 : 6;
+  static constexpr int kCopyWarps = kPaired ? 1 : 2;
+  static constexpr int kFirstWidenWarp = kPaired ? 2 : 0;
+  static constexpr int kFirstDrainWarp = kPaired ? 4 : 8;
+  static constexpr int kDrainWarps = kPaired ? 4 : 8;
+  static constexpr int kIdleRegs = 40;
+  static constexpr int kDrainRegs = 216;
   static constexpr int kCols = TN * kTile;
   static constexpr int kBBytes = TN * kW8TileBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;  // a multiple of the 1024-byte operand alignment
@@ -88,8 +88,12 @@ struct Shape {
   // ready[S], empty[S], packed[S][TN], acc_full[kAccs], acc_empty[kAccs], final
   static constexpr int kNumBars = (2 + TN) * kStages + 2 * kAccs + 1;
   static constexpr int kSmemBytes = kStages * kStageBytes + kRecBytes + kNumBars * 8 + 16;
-  static constexpr int kTilesPerHalf = TN / 2;       // weight tile rows drained by one warp
-  static constexpr int kChunks = 4 * kTilesPerHalf;  // 16-column chunks per drain warp and K step
+  static constexpr int kHalves = kDrainWarps / 4;        // column groups of the drain warps
+  static constexpr int kTilesPerHalf = TN / kHalves;     // weight tile rows drained by one warp
+  static constexpr int kChunks = 4 * kTilesPerHalf;      // 16-column chunks per drain warp and K step
+  static constexpr int kTilesPerCopyWarp = TN / kCopyWarps;
+  static_assert(kBM * (kCols + 1) * 4 <= kStages * kStageBytes, "the split-K exchange tile must fit into the ring");
+  static_assert(kDrainWarps * 32 * kEpiRowFloats * 4 <= kStages * kStageBytes, "the epilogue rows must fit into the ring");
 };
 
 struct GemmParams {
@@ -118,6 +122,17 @@ __device__ __forceinline__ void drain_chunk(uint64_t (&acc)[NACC], int c, const 
   }
 }
 
+// acc[16*c .. 16*c+15] = fma(float(v), scale, acc): one rounding per tile, two sums per
+// instruction (fma.rn.f32x2).
+template <int NACC>
+__device__ __forceinline__ void drain_chunk_fused(uint64_t (&acc)[NACC], int c, const int (&v)[16], uint64_t scale2) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint64_t f = pack2(__float_as_uint(__int2float_rn(v[2 * i])), __float_as_uint(__int2float_rn(v[2 * i + 1])));
+    acc[c * 8 + i] = fma2(f, scale2, acc[c * 8 + i]);
+  }
+}
+
 // Debug aid: the exact integer tile sums (W4 tiles were fed 16*w to the MMA).
 __device__ __forceinline__ void dump_chunk(int32_t* tile_dump, int first_col, const int (&v)[16], const TileRecord& r) {
   if (tile_dump == nullptr) return;
@@ -129,13 +144,17 @@ __device__ __forceinline__ void dump_chunk(int32_t* tile_dump, int first_col, co
   }
 }
 
-template <int TN, bool kDump>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int TN, bool kPaired, bool kDump, bool kFused>
+__global__ void __launch_bounds__(Layout<TN, kPaired>::kThreads, Layout<TN, kPaired>::kCtasPerSm)
 tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) {
-  using S = Shape<TN>;
+  using S = Layout<TN, kPaired>;
+  constexpr int kStages = S::kStages;
   constexpr int kStageBytes = S::kStageBytes;
   constexpr int kAccs = S::kAccs;
   constexpr int kTilesN = TN;
+  constexpr int kThreads = S::kThreads;
+  constexpr int kDrainWarps = S::kDrainWarps;
+  constexpr int kFirstDrainWarp = S::kFirstDrainWarp;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* stages = smem;
   TileRecord* rec_smem = reinterpret_cast<TileRecord*>(smem + kStages * kStageBytes);
@@ -182,10 +201,10 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
     const int t = i / steps, kt = i % steps;  // kt counts from k_begin everywhere below
     rec_smem[t * kMaxNk + kt] = p.records[static_cast<int64_t>(j0 + t) * n_k + k_begin + kt];
   }
-  if (warp == kMmaWarp) {
+  if (warp == S::kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"(static_cast<uint32_t>(kTmemColumns))
+                 "r"(static_cast<uint32_t>(S::kTmemColumns))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -193,16 +212,16 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-#ifdef AQ_TRACE
-  if (lane == 0) AQ_GT(3900 + warp);  // clock of every warp right after the barrier
-#endif
 
   if (warp < kFirstDrainWarp) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-    if (warp < tiles_here) {
-      // ---------------- W4 widening of tile row j0 + warp -------------------------------
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(S::kIdleRegs));
+    // the warp that streams the activations may also stream weight tiles (paired layout)
+    const bool copies_weights = warp >= S::kFirstCopyWarp && warp < S::kFirstCopyWarp + S::kCopyWarps;
+    const bool copies_acts = warp == S::kActWarp;
+    if (warp >= S::kFirstWidenWarp && warp < S::kFirstWidenWarp + tiles_here) {
+      // ---------------- W4 widening of tile row j0 + t -----------------------------------
       // W8 tiles need no work here: their copy completes "ready" by itself.
-      const int t = warp;
+      const int t = warp - S::kFirstWidenWarp;
       const TileRecord* recs = rec_smem + t * kMaxNk;
       uint32_t packed_parity = 0;  // bit s: phase the next wait on packed(s, t) looks for
       for (int kt = 0; kt < steps; ++kt) {
@@ -211,7 +230,6 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         int landed = 1;
         if (lane == 0) landed = mbar_wait(packed(s, t), (packed_parity >> s) & 1u, abort_flag, &g_gemm_status, 6) ? 1 : 0;
         if (__shfl_sync(0xffffffffu, landed, 0) == 0) break;
-        if (t == 0 && lane == 0) AQ_GT(1024 + 4 * kt + 1);
         packed_parity ^= 1u << s;
         // Widen in place.  Packed chunk q = 2*n + h (16 bytes) holds the k16 blocks 2h (low
         // nibbles) and 2h+1 (high nibbles) of row n; the widened row n takes bytes 64n..64n+63
@@ -242,37 +260,44 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(ready(s));
-        if (t == 0 && lane == 0) AQ_GT(1024 + 4 * kt + 2);
       }
-    } else if (warp >= kFirstCopyWarp && warp < kFirstCopyWarp + 2) {
-      // ---------------- weight copies: TN / 2 tile rows per issuing warp ------------------
-      // Issuing a bulk copy takes its warp about 150 cycles whatever the size, so the copies of
-      // a K step are spread over two warps and kept apart from the widening.
+    } else if (copies_weights || copies_acts) {
+      // ---------------- operand copies ------------------------------------------------------
+      // Issuing a bulk copy takes its warp about 150 cycles whatever the size, so in the large
+      // layout the copies of a K step are spread over three warps (activations, two weight
+      // streams) and kept apart from the widening.  Activations: one tensor-map copy per step
+      // brings the 128 x 64 int8 block into the operand layout; rows past M read as zero.
       if (lane == 0) {
-        const int t_first = (warp - kFirstCopyWarp) * (TN / 2);
+        const int t_first = copies_weights ? (warp - S::kFirstCopyWarp) * S::kTilesPerCopyWarp : 0;
+        const int wait_code = copies_acts ? 3 : 1;
         for (int kt = 0; kt < steps; ++kt) {
           const int s = kt % kStages;
-          if (kt >= kStages && !mbar_wait(empty(s), ((kt / kStages) - 1) & 1, abort_flag, &g_gemm_status, 1)) break;
-          if (warp == kFirstCopyWarp) AQ_GT(1024 + 4 * kt);
+          if (kt >= kStages && !mbar_wait(empty(s), ((kt / kStages) - 1) & 1, abort_flag, &g_gemm_status, wait_code)) break;
+          if (copies_acts) {
+            mbar_expect_tx(ready(s), kABytes);
+            tensor_copy_2d(smem_u32(stages + s * kStageBytes), &x_map, (k_begin + kt) * kTile, static_cast<int>(m0), ready(s));
+          }
+          if (copies_weights) {
 #pragma unroll
-          for (int i = 0; i < TN / 2; ++i) {
-            const int t = t_first + i;
-            if (t >= tiles_here) break;
-            const uint32_t of = rec_smem[t * kMaxNk + kt].offset_flag;
-            const uint8_t* src = p.payload + static_cast<int64_t>(of & ~kW4Flag) * kW4TileBytes;
-            const uint32_t dst = smem_u32(stages + s * kStageBytes + kABytes + t * kW8TileBytes);
-            if (of & kW4Flag) {
-              mbar_expect_tx(packed(s, t), kW4TileBytes);
-              bulk_copy(dst, src, kW4TileBytes, packed(s, t));
-            } else {
-              mbar_expect_tx(ready(s), kW8TileBytes);
-              bulk_copy(dst, src, kW8TileBytes, ready(s));
+            for (int i = 0; i < S::kTilesPerCopyWarp; ++i) {
+              const int t = t_first + i;
+              if (t >= tiles_here) break;
+              const uint32_t of = rec_smem[t * kMaxNk + kt].offset_flag;
+              const uint8_t* src = p.payload + static_cast<int64_t>(of & ~kW4Flag) * kW4TileBytes;
+              const uint32_t dst = smem_u32(stages + s * kStageBytes + kABytes + t * kW8TileBytes);
+              if (of & kW4Flag) {
+                mbar_expect_tx(packed(s, t), kW4TileBytes);
+                bulk_copy(dst, src, kW4TileBytes, packed(s, t));
+              } else {
+                mbar_expect_tx(ready(s), kW8TileBytes);
+                bulk_copy(dst, src, kW8TileBytes, ready(s));
+              }
             }
           }
         }
       }
       __syncwarp();
-    } else if (warp == kMmaWarp) {
+    } else if (warp == S::kMmaWarp) {
       // ---------------- MMA issuer ---------------------------------------------------
       // The whole warp walks the loop so that addresses and descriptors stay warp-uniform
       // values (the MMA takes them from uniform registers); one elected lane issues.
@@ -282,11 +307,8 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       for (int kt = 0; kt < steps; ++kt) {
         const int s = kt % kStages;
         const int b = kt % kAccs;
-        if (lane == 0) AQ_GT(4 * kt);
         ok = warp_wait(ready(s), (kt / kStages) & 1, lane, abort_flag, &g_gemm_status, 2);
-        if (lane == 0) AQ_GT(4 * kt + 1);
         ok = ok && warp_wait(acc_empty(b), (kt / kAccs) & 1, lane, abort_flag, &g_gemm_status, 5);
-        if (lane == 0) AQ_GT(4 * kt + 2);
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_addr = stage0 + static_cast<uint32_t>(s) * kStageBytes;
@@ -301,24 +323,11 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
           tc_commit(acc_full(b));
         }
         __syncwarp();
-        if (lane == 0) AQ_GT(4 * kt + 3);
       }
       if (!ok && lane == 0) {
         // make sure nothing issued is still running before tensor memory is freed
         tc_commit(final_bar);
         for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(final_bar, 0); ++i) {
-        }
-      }
-      __syncwarp();
-    } else if (warp == kActWarp) {
-      // ---------------- activation stream ----------------------------------------------
-      if (lane == 0) {
-        for (int kt = 0; kt < steps; ++kt) {
-          const int s = kt % kStages;
-          if (kt >= kStages && !mbar_wait(empty(s), ((kt / kStages) - 1) & 1, abort_flag, &g_gemm_status, 3)) break;
-          AQ_GT(1024 + 4 * kt + 3);
-          mbar_expect_tx(ready(s), kABytes);
-          tensor_copy_2d(smem_u32(stages + s * kStageBytes), &x_map, (k_begin + kt) * kTile, static_cast<int>(m0), ready(s));
         }
       }
       __syncwarp();
@@ -329,12 +338,12 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       for (int i = 0; i < 64; ++i) __nanosleep(2000);
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(S::kDrainRegs));
     // ---------------- drain: int32 accumulator -> scaled FP32 registers -------------
     const int quarter = warp & 3;       // tensor-memory lane quarter this warp may read
     constexpr int kTH = S::kTilesPerHalf;
     constexpr int kChunks = S::kChunks;
-    const int half = (warp - kFirstDrainWarp) >> 2;  // column half: weight tile rows kTH*half ...
+    const int half = (warp - kFirstDrainWarp) >> 2;  // column group: weight tile rows kTH*half ...
     const int row = quarter * 32 + lane;
     const int64_t grow = m0 + row;
     const bool row_valid = grow < p.m;
@@ -354,9 +363,6 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
     // is in flight.  The accumulator goes back to the MMA thread as soon as its last chunk
     // has been loaded, before that chunk's arithmetic.
     int va[16], vb[16];
-#ifdef AQ_TRACE
-    long long aq_sums[4] = {0, 0, 0, 0};
-#endif
     tc_fence_before();
     __syncwarp();
     if (lane == 0) {  // every accumulator starts out free
@@ -371,15 +377,16 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       const int b = kt % kAccs;
       const int b_next = (kt + 1) % kAccs;
       const uint32_t col = taddr + static_cast<uint32_t>(b * S::kCols);
-      AQ_SUM_BEGIN();
       const float a_scale = tile_scales != nullptr ? tile_scales[k_begin + kt] : token_scale;
       TileRecord rec[kTH];
       float scale[kTH];
+      uint64_t scale2[kTH];
       int32_t* dump[kTH];
 #pragma unroll
       for (int t = 0; t < kTH; ++t) {
         rec[t] = recs[t * kMaxNk + kt];
         scale[t] = __fmul_rn(a_scale, rec[t].scale);
+        scale2[t] = pack2(__float_as_uint(scale[t]), __float_as_uint(scale[t]));
         dump[t] = nullptr;
         if (kDump && row_valid && kTH * half + t < tiles_here) {
           dump[t] = p.acc_dump + ((grow * p.n_j + (j0 + kTH * half + t)) * n_k + k_begin + kt) * kTile;
@@ -397,9 +404,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
           // next one is waited for before this one is handed back: a poll made after the
           // hand-over would queue behind the MMA thread, which starts issuing at that moment.
           // There is no dead-lock: the MMA of step kt+1 never needs the accumulator of step kt.
-          AQ_SUM_MARK(0);
           if (kt + 1 < steps) ok = warp_wait(acc_full(b_next), ((kt + 1) / kAccs) & 1, lane, abort_flag, &g_gemm_status, 7);
-          AQ_SUM_MARK(3);
           if (kt + 1 < steps && ok) {
             tc_fence_after();
             tc_ld16(taddr + static_cast<uint32_t>(b_next * S::kCols), next);
@@ -407,14 +412,15 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(acc_empty(b));
-          AQ_SUM_MARK(1);
         }
-        drain_chunk(acc, c, cur, scale[c >> 2]);
+        if (kFused) {
+          drain_chunk_fused(acc, c, cur, scale2[c >> 2]);
+        } else {
+          drain_chunk(acc, c, cur, scale[c >> 2]);
+        }
         if (kDump) dump_chunk(dump[c >> 2], (c & 3) * 16, cur, rec[c >> 2]);
       }
-      AQ_SUM_MARK(2);
     }
-    AQ_SUM_WRITE(3500 + (warp - kFirstDrainWarp) * 4);
 
     // ---------------- epilogue: rows through shared memory, coalesced stores --------
     if (split_k > 1) {
@@ -519,24 +525,30 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
 
   tc_fence_before();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == S::kMmaWarp) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(static_cast<uint32_t>(kTmemColumns))
+                 "r"(static_cast<uint32_t>(S::kTmemColumns))
                  : "memory");
   }
 }
 
-template <int TN>
-int launch_shape(const CUtensorMap& x_map, const GemmParams& p, bool dump, int split, int device, cudaStream_t stream) {
+template <int TN, bool kPaired>
+int launch_shape(const CUtensorMap& x_map, const GemmParams& p, bool dump, bool fused, int split, int device,
+                 cudaStream_t stream) {
+  using S = Layout<TN, kPaired>;
   static std::once_flag once[64];
   cudaError_t attr_status = cudaSuccess;
   std::call_once(once[device & 63], [&] {
-    attr_status = cudaFuncSetAttribute(tmem_gemm_kernel<TN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Shape<TN>::kSmemBytes);
-    if (attr_status == cudaSuccess) {
-      attr_status = cudaFuncSetAttribute(tmem_gemm_kernel<TN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Shape<TN>::kSmemBytes);
+    const void* kernels[4] = {
+        reinterpret_cast<const void*>(tmem_gemm_kernel<TN, kPaired, false, false>),
+        reinterpret_cast<const void*>(tmem_gemm_kernel<TN, kPaired, false, true>),
+        reinterpret_cast<const void*>(tmem_gemm_kernel<TN, kPaired, true, false>),
+        reinterpret_cast<const void*>(tmem_gemm_kernel<TN, kPaired, true, true>)};
+    for (const void* kernel : kernels) {
+      if (attr_status == cudaSuccess) {
+        attr_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kSmemBytes);
+      }
     }
   });
   int rc = check_cuda(attr_status, "cudaFuncSetAttribute(tmem_gemm_kernel)");
@@ -544,8 +556,8 @@ int launch_shape(const CUtensorMap& x_map, const GemmParams& p, bool dump, int s
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3(static_cast<unsigned>((p.n_j + TN - 1) / TN), static_cast<unsigned>((p.m + kBM - 1) / kBM),
                         static_cast<unsigned>(split));
-  config.blockDim = dim3(kThreads, 1, 1);
-  config.dynamicSmemBytes = static_cast<size_t>(Shape<TN>::kSmemBytes);
+  config.blockDim = dim3(S::kThreads, 1, 1);
+  config.dynamicSmemBytes = static_cast<size_t>(S::kSmemBytes);
   config.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -554,8 +566,14 @@ int launch_shape(const CUtensorMap& x_map, const GemmParams& p, bool dump, int s
   attr[0].val.clusterDim.z = static_cast<unsigned>(split);
   config.attrs = attr;
   config.numAttrs = 1;
-  const cudaError_t status = dump ? cudaLaunchKernelEx(&config, tmem_gemm_kernel<TN, true>, x_map, p)
-                                  : cudaLaunchKernelEx(&config, tmem_gemm_kernel<TN, false>, x_map, p);
+  cudaError_t status;
+  if (dump) {
+    status = fused ? cudaLaunchKernelEx(&config, tmem_gemm_kernel<TN, kPaired, true, true>, x_map, p)
+                   : cudaLaunchKernelEx(&config, tmem_gemm_kernel<TN, kPaired, true, false>, x_map, p);
+  } else {
+    status = fused ? cudaLaunchKernelEx(&config, tmem_gemm_kernel<TN, kPaired, false, true>, x_map, p)
+                   : cudaLaunchKernelEx(&config, tmem_gemm_kernel<TN, kPaired, false, false>, x_map, p);
+  }
   return check_cuda(status, "tensor-memory GEMM launch");
 }
 
@@ -574,16 +592,19 @@ int device_sm_count(int* count) {
   return AQ_OK;
 }
 
-// Width of the CTA tile in weight tile rows: 256 columns, or 128 columns where the wider
-// grid would occupy at most half of the SMs (measured cross-over on the decoder shapes).
-// ALIGNQUANT_B200_GEMM_TILE=2|4 forces one of them (for tests and measurements).
-int tile_rows(int64_t m, int n_j, int sm_count) {
-  if (const char* forced = std::getenv("ALIGNQUANT_B200_GEMM_TILE")) {
-    if (forced[0] == '2') return 2;
-    if (forced[0] == '4') return 4;
+// Kernel variant of a problem: AQ_GEMM_TILE_WIDE (256 columns, one CTA per SM),
+// AQ_GEMM_TILE_NARROW (128 columns, one CTA per SM) or AQ_GEMM_TILE_PAIRED (128 columns, two CTAs
+// per SM), unless AQ_OPT_GEMM_TILE forces one.  K ranges over a cluster use the one-CTA-per-SM
+// layouts (their exchange tile lives in the larger stage ring).
+int tile_variant(int64_t m, int n_j, int split, int sm_count) {
+  const int forced = gemm_tile_option();
+  if (forced == AQ_GEMM_TILE_WIDE || forced == AQ_GEMM_TILE_NARROW) return forced;
+  if (forced == AQ_GEMM_TILE_PAIRED) return split > 1 ? AQ_GEMM_TILE_NARROW : AQ_GEMM_TILE_PAIRED;
+  if (split > 1) {
+    const int64_t wide_ctas = ((m + kBM - 1) / kBM) * ((n_j + 3) / 4);
+    return 2 * wide_ctas <= sm_count ? AQ_GEMM_TILE_NARROW : AQ_GEMM_TILE_WIDE;
   }
-  const int64_t wide_ctas = ((m + kBM - 1) / kBM) * ((n_j + 3) / 4);
-  return 2 * wide_ctas <= sm_count ? 2 : 4;
+  return AQ_GEMM_TILE_PAIRED;
 }
 
 }  // namespace
@@ -592,16 +613,15 @@ int64_t tmem_gemm_workspace_bytes(int64_t, int, int) { return 0; }
 
 // Number of K ranges (cluster size along z): more than one only where the output tiles alone
 // would leave at least half of the SMs idle (few rows), at least four K steps per range.
-// ALIGNQUANT_B200_GEMM_SPLIT=1..8 forces a value (for tests and measurements).
+// AQ_OPT_GEMM_SPLIT forces a value (for tests and measurements).
 int tmem_gemm_split(int64_t m, int n_j, int n_k) {
   int sm_count = 148;
   if (device_sm_count(&sm_count) != AQ_OK) sm_count = 148;
-  int split = 1;
-  if (const char* forced = std::getenv("ALIGNQUANT_B200_GEMM_SPLIT")) {
-    split = forced[0] - '0';
-    if (split < 1 || split > 8) split = 1;
-  } else {
-    const int tn = tile_rows(m, n_j, sm_count);
+  int split = gemm_split_option();
+  if (split < 1 || split > 8) {
+    split = 1;
+    const int64_t wide_ctas = ((m + kBM - 1) / kBM) * ((n_j + 3) / 4);
+    const int tn = 2 * wide_ctas <= sm_count ? 2 : 4;
     const int64_t ctas = ((m + kBM - 1) / kBM) * ((n_j + tn - 1) / tn);
     if (2 * ctas <= sm_count) split = static_cast<int>(sm_count / ctas < 8 ? sm_count / ctas : 8);
   }
@@ -637,16 +657,17 @@ int launch_tmem_gemm(const LinearArgs& a, cudaStream_t stream) {
   p.scale_mode = a.scale_mode;
   p.out_dtype = a.out_dtype;
   const bool dump = a.acc_dump != nullptr;
+  const bool fused = !gemm_separate_rounding();
   const int split = tmem_gemm_split(a.m, a.n_j, a.n_k);
-  return tile_rows(a.m, a.n_j, sm_count) == 4 ? launch_shape<4>(x_map, p, dump, split, device, stream)
-                                             : launch_shape<2>(x_map, p, dump, split, device, stream);
+  switch (tile_variant(a.m, a.n_j, split, sm_count)) {
+    case AQ_GEMM_TILE_WIDE:
+      return launch_shape<4, false>(x_map, p, dump, fused, split, device, stream);
+    case AQ_GEMM_TILE_NARROW:
+      return launch_shape<2, false>(x_map, p, dump, fused, split, device, stream);
+    default:
+      return launch_shape<2, true>(x_map, p, dump, fused, split, device, stream);
+  }
 }
-
-#ifdef AQ_TRACE
-extern "C" __attribute__((visibility("default"))) int aq_debug_read_gemm_trace(long long* dst) {
-  return static_cast<int>(cudaMemcpyFromSymbol(dst, g_gemm_trace, sizeof(long long) * 4096));
-}
-#endif
 
 int take_gemm_status() {
   int status = 0;

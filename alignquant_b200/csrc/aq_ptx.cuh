@@ -58,6 +58,23 @@ __device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_
       "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
+// Asks the L2 cache to fetch `bytes` (a multiple of 16, 16-byte aligned address) of this GPU's
+// own global memory; nothing waits for it and nothing is written.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+// This CTA's share of a look-ahead prefetch: the `total_bytes` at `base` are cut into one
+// contiguous slice per CTA (128-byte granules) and requested in pieces of at most 16 KiB.
+// Called by one thread per CTA.
+__device__ __forceinline__ void prefetch_slice_l2(const uint8_t* base, int64_t total_bytes, int64_t cta, int64_t ctas) {
+  const int64_t slice = (((total_bytes + ctas - 1) / ctas) + 127) & ~static_cast<int64_t>(127);
+  const int64_t begin = cta * slice;
+  const int64_t end = begin + slice < total_bytes ? begin + slice : total_bytes;
+  for (int64_t at = begin; at < end; at += 16384) {
+    const int64_t left = end - at;
+    bulk_prefetch_l2(base + at, static_cast<uint32_t>(left < 16384 ? left : 16384) & ~15u);
+  }
+}
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

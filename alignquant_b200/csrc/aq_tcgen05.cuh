@@ -108,6 +108,11 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
   return r;
 }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
 // There is no packed multiply here on purpose: the assembler contracts a packed multiply
 // (however it is written) that feeds a packed add into one fused multiply-add, which
 // rounds a * b + c once instead of twice.  The products are therefore formed with the

@@ -226,8 +226,14 @@ def alignquant_linear_prepared(
     scale_mode: str = "tile",
     acc_dump: torch.Tensor | None = None,
     out: torch.Tensor | None = None,
+    prefetch: PreparedWeights | None = None,
 ) -> torch.Tensor:
-    """Run one packed projection on a prepared weight image; returns ``[M, N]``."""
+    """Run one packed projection on a prepared weight image; returns ``[M, N]``.
+
+    ``prefetch``: the weights of the projection that runs next.  The decode kernels ask the L2
+    cache to fetch that image while this projection runs (``aq_linear_ahead``); other kernels
+    ignore it.
+    """
     try:
         schedule_code = _lib.SCHEDULE_CODES[str(schedule)]
     except KeyError as error:
@@ -289,11 +295,14 @@ def alignquant_linear_prepared(
         if ws_bytes < 0:
             _lib.check(ws_bytes)
         workspace = _workspace(device, ws_bytes) if ws_bytes else None
+        if prefetch is not None and prefetch.device != device:
+            raise RuntimeError("prefetch must name weights on the device of this call")
         _lib.check(
-            lib.aq_linear(
+            lib.aq_linear_ahead(
                 _ptr(x), _ptr(scales), mode, m, _ptr(weights.image), n_j, n_k, _ptr(meta), schedule_code,
                 int(decode_splits), _DTYPE_CODES[output_dtype], _ptr(out), _ptr(workspace), ws_bytes,
-                _ptr(acc_dump), _stream(device),
+                _ptr(acc_dump), None if prefetch is None else _ptr(prefetch.image),
+                0 if prefetch is None else int(prefetch.image.numel()), _stream(device),
             )
         )
     return out
@@ -309,6 +318,7 @@ def alignquant_linear_allreduce(
     output_dtype: torch.dtype = torch.float32,
     scale_mode: str = "tile",
     out: torch.Tensor | None = None,
+    prefetch: PreparedWeights | None = None,
 ) -> torch.Tensor | None:
     """Row-parallel projection and the sum over the tensor-parallel ranks in ONE kernel.
 
@@ -336,7 +346,9 @@ def alignquant_linear_allreduce(
         _lib.check(
             lib.aq_linear_allreduce(
                 _ptr(x), _ptr(scales), mode, m, _ptr(weights.image), n_j, n_k, _ptr(meta), _DTYPE_CODES[output_dtype],
-                _ptr(out), reducer.rank, reducer.world, reducer.peer_array_pointer(), reducer.max_count, _stream(device),
+                _ptr(out), reducer.rank, reducer.world, reducer.peer_array_pointer(), reducer.max_count,
+                None if prefetch is None else _ptr(prefetch.image),
+                0 if prefetch is None else int(prefetch.image.numel()), _stream(device),
             )
         )
     return out
@@ -469,6 +481,43 @@ def alignquant_linear_decode_static(
     return out
 
 
+def set_peer_poll_limit(polls: int | None) -> None:
+    """How often a tensor-parallel sum polls for a peer before giving up (None: the default)."""
+    _lib.check(_lib.load().aq_set_option(_lib.AQ_OPT_PEER_POLL_LIMIT, (1 << 22) if polls is None else int(polls)))
+
+
+def set_gemm_rounding(separate: bool) -> None:
+    """GEMM FP32 accumulation: one fused multiply-add per tile (default) or the reference
+    kernels' separately rounded multiply and add (``AQ_OPT_GEMM_ROUNDING``)."""
+    _lib.check(_lib.load().aq_set_option(
+        _lib.AQ_OPT_GEMM_ROUNDING, _lib.AQ_GEMM_ROUNDING_SEPARATE if separate else _lib.AQ_GEMM_ROUNDING_FUSED))
+
+
+def gemm_rounding_is_separate() -> bool:
+    return int(_lib.load().aq_get_option(_lib.AQ_OPT_GEMM_ROUNDING)) == _lib.AQ_GEMM_ROUNDING_SEPARATE
+
+
+def set_gemm_tile(name: str = "auto") -> None:
+    """Force a CTA tile of the GEMM: "auto", "paired", "narrow" or "wide" (``AQ_OPT_GEMM_TILE``)."""
+    _lib.check(_lib.load().aq_set_option(_lib.AQ_OPT_GEMM_TILE, _lib.GEMM_TILES[str(name)]))
+
+
+def set_gemm_split(split: int = 0) -> None:
+    """Force the number of K ranges of the GEMM, 0 = automatic (``AQ_OPT_GEMM_SPLIT``)."""
+    _lib.check(_lib.load().aq_set_option(_lib.AQ_OPT_GEMM_SPLIT, int(split)))
+
+
+def measure_int8_peak(pairs: int = 4096, device: torch.device | str | None = None) -> float:
+    """Integer TOPS of back-to-back ``tcgen05.mma kind::i8`` on all SMs (``aq_measure_int8_peak``)."""
+    import ctypes
+
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    tops = ctypes.c_double()
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().aq_measure_int8_peak(int(pairs), ctypes.addressof(tops), _stream(dev)))
+    return float(tops.value)
+
+
 def linear_plan(m: int, n_j: int, n_k: int, *, schedule: str = "auto", decode_splits: int = 0) -> dict[str, int]:
     """Kernel family, split count and accumulator count ``aq_linear`` will use.
 
@@ -499,4 +548,10 @@ __all__ = [
     "PreparedWeights",
     "device_status",
     "linear_plan",
+    "set_peer_poll_limit",
+    "set_gemm_rounding",
+    "gemm_rounding_is_separate",
+    "set_gemm_tile",
+    "measure_int8_peak",
+    "set_gemm_split",
 ]

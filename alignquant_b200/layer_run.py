@@ -37,12 +37,19 @@ def main() -> None:
     ap.add_argument("--out-dtype", choices=("float32", "bfloat16", "float16"), default="bfloat16")
     ap.add_argument("--schedule", default="auto")
     ap.add_argument("--flush-l2", action="store_true", help="overwrite a 512 MB buffer before every launch")
+    ap.add_argument("--gemm-tile", choices=("auto", "paired", "narrow", "wide"), default="auto", help="CTA tile of the GEMM")
+    ap.add_argument("--gemm-separate-rounding", action="store_true",
+                    help="GEMM adds a tile with a separately rounded multiply and add (the reference kernels' order)")
+    ap.add_argument("--lookahead", action="store_true",
+                    help="with --layers: every projection names the next layer's weights as its L2 look-ahead")
     args = ap.parse_args()
 
     from alignquant_b200.kernels.cuda import extension as ext
     from alignquant_b200.synthetic import algorithmic_weight_bytes, synthetic_activation, synthetic_module_tensors
 
     ext.load_extension()
+    ext.set_gemm_tile(args.gemm_tile)
+    ext.set_gemm_rounding(args.gemm_separate_rounding)
     device = torch.device("cuda", 0)
     row_counts = [int(v) for v in str(args.rows).split(",")]
     if args.layers > 1:
@@ -81,6 +88,7 @@ def main() -> None:
         "n": args.n, "k": args.k, "rows": args.rows, "plan": plan,
         "us": seconds * 1e6, "tops": 2.0 * args.rows * args.n * args.k / seconds / 1e12,
         "weight_gbs": weight_bytes / seconds / 1e9, "scale_mode": args.scale_mode, "out_dtype": args.out_dtype,
+        "gemm_tile": args.gemm_tile, "gemm_rounding": "separate" if args.gemm_separate_rounding else "fused",
     }))
 
 
@@ -102,11 +110,12 @@ def chain(args, ext, device, row_counts, synthetic_module_tensors, synthetic_act
         out = torch.empty((rows, args.n), dtype=out_dtype, device=device)
 
         def sweep() -> None:
-            for weights in layers:
+            for index, weights in enumerate(layers):
                 if args.with_quantizer:
                     ext.alignquant_activation_quantize_cuda(x, None, scale_mode=args.scale_mode, out=(xq, scales))
+                ahead = layers[(index + 1) % len(layers)] if args.lookahead else None
                 ext.alignquant_linear_prepared(xq, scales, weights, None, schedule=args.schedule, scale_mode=args.scale_mode,
-                                               output_dtype=out_dtype, out=out)
+                                               output_dtype=out_dtype, out=out, prefetch=ahead)
 
         sweep()
         torch.cuda.synchronize()
@@ -128,7 +137,7 @@ def chain(args, ext, device, row_counts, synthetic_module_tensors, synthetic_act
             "n": args.n, "k": args.k, "rows": rows, "layers": args.layers, "with_quantizer": bool(args.with_quantizer),
             "plan": ext.linear_plan(rows, args.n // 64, args.k // 64, schedule=args.schedule),
             "us_per_layer": seconds * 1e6, "weight_gbs": weight_bytes / args.layers / seconds / 1e9,
-            "scale_mode": args.scale_mode, "out_dtype": args.out_dtype,
+            "scale_mode": args.scale_mode, "out_dtype": args.out_dtype, "lookahead": bool(args.lookahead),
         }), flush=True)
 
 

@@ -14,7 +14,10 @@ Differences, all behind keyword arguments with reference-compatible defaults:
   * ``scale_mode="token"`` selects per-row activation scales (only for identity V);
   * ``tp_rank`` / ``tp_size`` / ``process_group`` install a tile-aligned tensor-parallel
     shard: q/k/v/gate/up keep a range of tile rows per member (column parallel), o/down a
-    range of tile columns (row parallel) followed by an all-reduce of the partial output.
+    range of tile columns (row parallel) followed by an all-reduce of the partial output;
+  * every group knows the group that runs after it in a decoder layer (qkv -> o -> gate_up ->
+    down -> next layer's qkv) and hands that group's weight image to the decode kernels as a
+    look-ahead, so that the L2 cache fetches it while the current projection runs.
 """
 
 from __future__ import annotations
@@ -219,6 +222,8 @@ class _ProjectionGroupRuntime:
         self.v_metadata = None if identity_v else metadata_stack(v_seeds, self.device)
         self.u_metadata = None if all(seed == -1 for seed in u_seeds) else metadata_stack(u_seeds, self.device)
         self._prepared: _PreparedGroupOutput | None = None
+        self.has_bias = False  # set at install: a biased member keeps the kernel output in FP32
+        self.next_weights = None  # weights of the group that runs next (look-ahead), set at install
 
     @staticmethod
     def _activation_key(activation: torch.Tensor) -> tuple[Any, ...]:
@@ -262,19 +267,25 @@ class _ProjectionGroupRuntime:
                 raise ValueError("Activation must contain at least one row.")
             flat = activation.reshape(rows, width)
             qx, scales = _ext.alignquant_activation_quantize_cuda(flat, self.v_metadata, scale_mode=self.scale_mode)
-            out_dtype = activation.dtype if activation.dtype in (torch.bfloat16, torch.float16) and not self.row_parallel else torch.float32
+            # Low-precision kernel output only for bias-free groups, as in the reference
+            # (model.py:343-349): with a bias the FP32 result is kept through the bias add and
+            # rounded once at the end.  Row-parallel partials stay FP32 for the sum over ranks.
+            low_precision = activation.dtype in (torch.bfloat16, torch.float16) and not self.row_parallel and not self.has_bias
+            out_dtype = activation.dtype if low_precision else torch.float32
             combined = None
             self.sum_fused = False
             reducer = getattr(self, "peer_allreduce", None)
             if self.row_parallel and reducer is not None:
                 # decode sizes: projection and the sum over the ranks in one kernel
                 combined = _ext.alignquant_linear_allreduce(
-                    qx, scales, self.weights, self.u_metadata, reducer, scale_mode=self.scale_mode, output_dtype=out_dtype
+                    qx, scales, self.weights, self.u_metadata, reducer, scale_mode=self.scale_mode, output_dtype=out_dtype,
+                    prefetch=self.next_weights,
                 )
                 self.sum_fused = combined is not None
             if combined is None:
                 combined = _ext.alignquant_linear_prepared(
-                    qx, scales, self.weights, self.u_metadata, scale_mode=self.scale_mode, output_dtype=out_dtype
+                    qx, scales, self.weights, self.u_metadata, scale_mode=self.scale_mode, output_dtype=out_dtype,
+                    prefetch=self.next_weights,
                 )
             if tuple(combined.shape) != (rows, self.out_features):
                 raise RuntimeError(
@@ -326,7 +337,7 @@ class AlignQuantLinear(nn.Module):
             else:
                 dist.all_reduce(result, group=self.process_group)  # sum of the K-shard partials
         if self.bias is not None:
-            result = result + self.bias.to(dtype=result.dtype)
+            result = result.float() + self.bias.float()  # FP32 through the bias add, one rounding below
         result = result.reshape(*original_shape[:-1], self.out_features)
         return result.to(dtype=activation.dtype)
 
@@ -413,11 +424,17 @@ def install_alignquant(
         for name in members:
             parent, attr, _ = records.pop(name)
             runtime.peer_allreduce = peer_allreduce
+            runtime.has_bias = runtime.has_bias or getattr(parent, attr).bias is not None
             module = AlignQuantLinear(getattr(parent, attr), layer_name=name, runtime=runtime, process_group=process_group,
                                       peer_allreduce=peer_allreduce)
             setattr(parent, attr, module)
             installed.append(module)
     model._alignquant_projection_groups = tuple(runtimes.values())
+    chain = execution_order(runtimes)
+    for position, group_id in enumerate(chain):
+        successor = runtimes[chain[(position + 1) % len(chain)]]
+        if successor.device == runtimes[group_id].device and len(chain) > 1:
+            runtimes[group_id].next_weights = successor.weights
     metadata = {
         "module_count": len(installed),
         "projection_group_count": len(runtimes),
@@ -427,6 +444,18 @@ def install_alignquant(
         "tensor_parallel": {"rank": int(tp_rank), "size": int(tp_size)},
     }
     return installed, metadata
+
+
+def execution_order(group_ids: Sequence[str]) -> list[str]:
+    """Group ids in the order a decoder runs them: by layer index, then qkv, o, gate_up, down."""
+    rank = {"qkv": 0, "q_proj": 0, "k_proj": 0, "v_proj": 0, "o_proj": 1, "gate_up": 2, "gate_proj": 2, "up_proj": 2, "down_proj": 3}
+
+    def key(group_id: str):
+        parts = group_id.split(".")
+        layer = next((int(parts[i + 1]) for i, part in enumerate(parts[:-1]) if part == "layers" and parts[i + 1].isdigit()), -1)
+        return (layer, rank.get(parts[-1], 4), group_id)
+
+    return sorted((str(g) for g in group_ids), key=key)
 
 
 def reset_alignquant_state(model: nn.Module) -> None:

@@ -121,7 +121,7 @@ def run(args) -> dict:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         dist.init_process_group("nccl", device_id=device)
     ext.load_extension()
     model = build_model(args.model, world, device, layers=args.layers)
@@ -209,6 +209,18 @@ def run(args) -> dict:
         "decode_launch": decode_mode, "decode_ms_per_step": decode_s * 1e3 / max(decode_steps, 1),
         "prefill_s": prefill_s, "decode_s": decode_s, "rank": rank, "world": world,
     }
+
+
+def generation_record(model: str, batch: int, prompt_len: int, new_tokens: int, *, layers: int | None = None,
+                      scale_mode: str = "token", warmup: int = 1) -> dict:
+    """One generation run as a dict (what ``main`` prints); callable from another script.
+
+    Reads RANK / LOCAL_RANK / WORLD_SIZE from the environment and uses the default process
+    group if one is initialised already.
+    """
+    args = argparse.Namespace(model=model, batch=batch, prompt_len=prompt_len, new_tokens=new_tokens, layers=layers,
+                              scale_mode=scale_mode, warmup=warmup, decode_graph=True)
+    return run(args)
 
 
 def main() -> None:

@@ -18,6 +18,19 @@ is the same sweep through the public Python API from pinned host buffers, host<-
 copies included; `roofline` times the packed-GEMV kernel alone; `cpu_baseline` times
 the CPU oracle (the reference's dequantize-and-matmul recipe) on a bounded sample.
 `--impl reference` runs only that CPU arm.
+
+Every projection hands the weights of the projection that runs after it to the decode
+kernel as a look-ahead (`aq_linear_ahead`), exactly as the quantized modules of an installed
+model do: the L2 cache fetches the next image while the current kernel runs.
+
+The line also carries the other two legs of the metric (`--legs` selects them):
+`prefill` -- the same four Llama-3.2-3B shapes at M = 2048 with bf16 activations through the
+tensor-memory GEMM, in integer TOPS against the nominal 4.5 POPS and against this GPU's own
+back-to-back `tcgen05.mma kind::i8` rate (`aq_measure_int8_peak`); `generation` -- prompt and
+generated tokens per second of a random-init Qwen3-4B-shaped model on one GPU, or of the
+tensor-parallel Qwen3-14B-shaped model on N > 1 GPUs, with a shortened, stated token count.
+With N > 1 the fused projection + rank sum is first checked against the two-step path
+(`tp_check`); a mismatch ends the run with a non-zero exit code.
 """
 
 from __future__ import annotations
@@ -46,9 +59,12 @@ GROUPS = {
 }
 WORKLOAD = "llama-3.2-3b decode sweep: 28 layers x (qkv, o, gate_up, down), M in {1,4,8,16}, 60% W4, per-token A8"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the packed-GEMV kernel, from the
-# ncu capture summarised in profiles/ (average over the four projection groups at M = 1).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 17.72e6  # (11.077 + 6.65 + 35.367 + 17.77) MB / 4; o and down scaled from their byte counts
+NOMINAL_INT8_TOPS = 4500.0
+PREFILL_ROWS = 2048
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the packed-GEMV kernel per projection
+# group at M = 1, one GPU, from an ncu capture of this sweep's four shapes run as a chain with the
+# look-ahead on (L2 not flushed between launches).  None until captured; N > 1 is not captured.
+NCU_DRAM_BYTES_PER_LAUNCH = {"qkv": None, "o": None, "gate_up": None, "down": None}
 
 
 def parse_args():
@@ -57,6 +73,10 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=("native", "reference"), default="native")
+    ap.add_argument("--legs", default="decode,prefill,generation",
+                    help="comma-separated legs besides the decode sweep: prefill, generation")
+    ap.add_argument("--gen-tokens", type=int, default=32, help="generated tokens of the generation leg")
+    ap.add_argument("--no-lookahead", action="store_true", help="run the sweep without the L2 look-ahead")
     return ap.parse_args()
 
 
@@ -204,6 +224,75 @@ def run_reference(args) -> None:
 # ---------------------------------------------------------------------------
 
 
+def prefill_leg(ext, device, steps: int) -> dict:
+    """The four Llama-3.2-3B shapes at M = 2048, bf16 activations, through the tensor-memory GEMM."""
+    import torch
+
+    from alignquant_b200.synthetic import synthetic_activation, synthetic_module_tensors
+
+    shapes = {}
+    total_ops, total_seconds = 0.0, 0.0
+    for index, (name, (n, k, _)) in enumerate(GROUPS.items()):
+        tensors = synthetic_module_tensors(n, k, seed=900 + index, device=device)
+        weights = ext.prepare_weights(
+            tensors["state_bits"], tensors["w4_payload"], tensors["w4_scales"], tensors["w8_payload"], tensors["w8_scales"],
+            tensors["w4_row_offsets"], tensors["w8_row_offsets"], n_k=k // 64,
+        )
+        del tensors
+        x = synthetic_activation(PREFILL_ROWS, k, seed=950 + index, dtype=torch.bfloat16, device=device)
+        xq, a_s = ext.alignquant_activation_quantize_cuda(x, None, scale_mode="token")
+        out = torch.empty((PREFILL_ROWS, n), dtype=torch.bfloat16, device=device)
+
+        def call():
+            ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token", output_dtype=torch.bfloat16, out=out)
+
+        for _ in range(3):
+            call()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        begin.record()
+        for _ in range(steps):
+            call()
+        end.record()
+        torch.cuda.synchronize()
+        seconds = begin.elapsed_time(end) / 1e3 / steps
+        ops = 2.0 * PREFILL_ROWS * n * k
+        plan = ext.linear_plan(PREFILL_ROWS, n // 64, k // 64)
+        shapes[name] = {"n": n, "k": k, "us": seconds * 1e6, "tops": ops / seconds / 1e12, "kernel": plan["kernel"]}
+        total_ops += ops
+        total_seconds += seconds
+        del weights, out, xq, a_s, x
+    ext.device_status(device)
+    measured_peak = ext.measure_int8_peak(4096, device)
+    tops = total_ops / total_seconds / 1e12
+    return {
+        "workload": f"llama-3.2-3b prefill: (qkv, o, gate_up, down) at M = {PREFILL_ROWS}, bf16 activations, bf16 results, 60% W4",
+        "metric": "prefill_gemm_int8_tops", "value": tops, "unit": "TOPS", "shapes": shapes,
+        "frac_of_nominal_peak": tops / NOMINAL_INT8_TOPS, "nominal_peak_tops": NOMINAL_INT8_TOPS,
+        "frac_of_measured_peak": tops / measured_peak, "measured_peak_tops": measured_peak,
+        "measured_peak_how": "aq_measure_int8_peak: back-to-back tcgen05.mma kind::i8 M128 N256 K32 on every SM, no operand traffic, no drain",
+        "drain": "fused multiply-add per K64 tile (AQ_GEMM_ROUNDING_FUSED)",
+        "inputs": "weights (35 MB at most) stay in the 126 MB L2 between repeats; the kernel is bound by the tensor pipe and the CUDA-core drain, not by HBM",
+    }
+
+
+def generation_leg(world: int, tokens: int) -> dict:
+    """Prompt and generated tokens per second of a random-init model with synthetic artifacts."""
+    from alignquant_b200.runner import generation_record
+
+    if world == 1:
+        model, batch, prompt_len, full_tokens = "qwen3-4b", 8, 2048, 128
+    else:
+        model, batch, prompt_len, full_tokens = "qwen3-14b", 32, 1024, 256
+    record = generation_record(model, batch, prompt_len, tokens, warmup=1)
+    keep = ("model", "layers", "tp", "batch", "prompt_len", "new_tokens", "prefill_tokens_per_s", "decode_tokens_per_s",
+            "decode_ms_per_step", "decode_launch", "decode_steps_timed", "quantized_modules")
+    result = {key: record[key] for key in keep}
+    result["note"] = (f"{tokens} generated tokens instead of the configuration's {full_tokens} (the decode step does not "
+                      "depend on the count beyond the KV-cache length); random-init weights, random token ids")
+    return result
+
+
 def run_native(args) -> None:
     import torch
     import torch.distributed as dist
@@ -216,6 +305,7 @@ def run_native(args) -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
+    legs = {leg.strip() for leg in args.legs.split(",") if leg.strip()}
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
@@ -266,34 +356,45 @@ def run_native(args) -> None:
     outs = {(m, name): torch.empty((m, local_shape[name][0]), dtype=out_dtype[name], device=device)
             for m in ROW_COUNTS for name in GROUPS}
 
+    # The step as a flat list of calls; every call names the weights of the call after it (the
+    # first call of the next step after the last one) as its look-ahead.
+    calls = [(m, li, name) for m in ROW_COUNTS for li in range(LAYERS) for name in GROUPS]
+    lookahead = not args.no_lookahead
+
+    def next_weights(position: int):
+        if not lookahead:
+            return None
+        _, li, name = calls[(position + 1) % len(calls)]
+        return layers[li][name]
+
     step_bytes = 0
     linear_bytes = 0
-    for m in ROW_COUNTS:
-        for layer in range(LAYERS):
-            for name in GROUPS:
-                n, k = local_shape[name]
-                step_bytes += call_bytes(m, n, k, weight_bytes[(layer, name)], out_bytes[name])
-                linear_bytes += weight_bytes[(layer, name)] + m * k + 4 * m + m * n * out_bytes[name]
-    pairs_per_step = len(ROW_COUNTS) * LAYERS * len(GROUPS)
-    allreduces_per_step = len(ROW_COUNTS) * LAYERS * sum(1 for _, _, axis in GROUPS.values() if axis == "k")
+    for m, li, name in calls:
+        n, k = local_shape[name]
+        step_bytes += call_bytes(m, n, k, weight_bytes[(li, name)], out_bytes[name])
+        linear_bytes += weight_bytes[(li, name)] + m * k + 4 * m + m * n * out_bytes[name]
+    pairs_per_step = len(calls)
+    allreduces_per_step = sum(1 for _, _, name in calls if GROUPS[name][2] == "k")
 
     separate_sums = [0]  # all-reduce kernels of our own launched by the last sweep (not fused ones, not NCCL's)
 
     def sweep(with_quantizer: bool, with_allreduce: bool) -> None:
         separate_sums[0] = 0
-        for m in ROW_COUNTS:
-            for entry in layers:
-                for name, (_, _, axis) in GROUPS.items():
-                    if with_quantizer:
-                        ext.alignquant_activation_quantize_cuda(acts[(m, name)], None, scale_mode="token", out=qbuf[(m, name)])
-                    xq, a_s = qbuf[(m, name)]
-                    if with_allreduce and reducer is not None and axis == "k" and ext.alignquant_linear_allreduce(
-                            xq, a_s, entry[name], None, reducer, scale_mode="token", output_dtype=out_dtype[name], out=outs[(m, name)]) is not None:
-                        continue  # projection and the sum over the ranks ran as one kernel
-                    ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", output_dtype=out_dtype[name], out=outs[(m, name)])
-                    if with_allreduce and world > 1 and axis == "k":
-                        all_reduce(outs[(m, name)])
-                        separate_sums[0] += 1 if reducer is not None else 0
+        for position, (m, li, name) in enumerate(calls):
+            axis = GROUPS[name][2]
+            weights, ahead = layers[li][name], next_weights(position)
+            if with_quantizer:
+                ext.alignquant_activation_quantize_cuda(acts[(m, name)], None, scale_mode="token", out=qbuf[(m, name)])
+            xq, a_s = qbuf[(m, name)]
+            if with_allreduce and reducer is not None and axis == "k" and ext.alignquant_linear_allreduce(
+                    xq, a_s, weights, None, reducer, scale_mode="token", output_dtype=out_dtype[name], out=outs[(m, name)],
+                    prefetch=ahead) is not None:
+                continue  # projection and the sum over the ranks ran as one kernel
+            ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token", output_dtype=out_dtype[name],
+                                           out=outs[(m, name)], prefetch=ahead)
+            if with_allreduce and world > 1 and axis == "k":
+                all_reduce(outs[(m, name)])
+                separate_sums[0] += 1 if reducer is not None else 0
 
     def barrier():
         if world > 1:
@@ -317,6 +418,44 @@ def run_native(args) -> None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             seconds = float(t.item())
         return seconds
+
+    # ---- N > 1: the fused projection + rank sum against projection, then NCCL all-reduce
+    tp_check = None
+    if world > 1:
+        worst = 0.0
+        ok = True
+        for m in ROW_COUNTS:
+            for name, (_, _, axis) in GROUPS.items():
+                if axis != "k":
+                    continue
+                ext.alignquant_activation_quantize_cuda(acts[(m, name)], None, scale_mode="token", out=qbuf[(m, name)])
+                xq, a_s = qbuf[(m, name)]
+                weights = layers[0][name]
+                want = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token", output_dtype=torch.float32)
+                dist.all_reduce(want)
+                got = None
+                if reducer is not None:
+                    got = ext.alignquant_linear_allreduce(xq, a_s, weights, None, reducer, scale_mode="token",
+                                                          output_dtype=torch.float32)
+                if got is None:  # shape without the fused epilogue: projection, then the peer-memory (or NCCL) sum
+                    got = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token", output_dtype=torch.float32)
+                    all_reduce(got)
+                torch.cuda.synchronize()
+                # NCCL's summation order differs from the rank order of the fused sum
+                close = torch.isclose(got, want, rtol=1e-5, atol=1e-5)
+                ok = ok and bool(close.all())
+                worst = max(worst, float((got - want).abs().max()))
+        ext.device_status(device)
+        verdict = torch.tensor([0 if ok else 1], device=device, dtype=torch.int32)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MAX)
+        tp_check = "ok" if int(verdict.item()) == 0 else "mismatch"
+        if tp_check != "ok":
+            if rank == 0:
+                print(json.dumps({"metric": "decode_gemv_hbm_gbs", "n_gpus": world, "tp_check": tp_check,
+                                  "max_abs_difference": worst}), flush=True)
+            barrier()
+            sys.stdout.flush()
+            os._exit(3)
 
     # ---- device-resident step: one CUDA graph per rank (kernels and, for N > 1, the all-reduces)
     sweep(True, True)
@@ -358,16 +497,27 @@ def run_native(args) -> None:
     h2d = sum(host_x[(m, name)].numel() * 2 for m in ROW_COUNTS for name in GROUPS) * LAYERS
     d2h = sum(host_out[(m, name)].numel() * out_bytes[name] for m in ROW_COUNTS for name in GROUPS) * LAYERS
 
+    def project(position: int, x):
+        """quantize -> linear (-> sum over ranks) of call `position` through the public API."""
+        m, li, name = calls[position]
+        axis = GROUPS[name][2]
+        weights, ahead = layers[li][name], next_weights(position)
+        xq, a_s = ext.alignquant_activation_quantize_cuda(x, None, scale_mode="token")
+        y = None
+        if reducer is not None and axis == "k":
+            y = ext.alignquant_linear_allreduce(xq, a_s, weights, None, reducer, scale_mode="token",
+                                                output_dtype=out_dtype[name], prefetch=ahead)
+        if y is None:
+            y = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token", output_dtype=out_dtype[name],
+                                               prefetch=ahead)
+            if world > 1 and axis == "k":
+                all_reduce(y)
+        return y
+
     def e2e_step() -> None:
-        for m in ROW_COUNTS:
-            for entry in layers:
-                for name, (_, _, axis) in GROUPS.items():
-                    x = host_x[(m, name)].to(device, non_blocking=True)
-                    xq, a_s = ext.alignquant_activation_quantize_cuda(x, None, scale_mode="token")
-                    y = ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", output_dtype=out_dtype[name])
-                    if world > 1 and axis == "k":
-                        all_reduce(y)
-                    host_out[(m, name)].copy_(y, non_blocking=True)
+        for position, (m, li, name) in enumerate(calls):
+            y = project(position, host_x[(m, name)].to(device, non_blocking=True))
+            host_out[(m, name)].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
     # The same calls captured once into a CUDA graph (the library's entry points are plain
@@ -396,20 +546,15 @@ def run_native(args) -> None:
                             x_dev[(li, m, name)].copy_(host_x[(m, name)], non_blocking=True)
                     staged[m] = torch.cuda.Event()
                     staged[m].record(copy_in)
+            position = 0
             for m in ROW_COUNTS:
                 main.wait_event(staged[m])
-                for li, entry in enumerate(layers):
+                for li in range(LAYERS):
                     results = []
-                    for name, (_, _, axis) in GROUPS.items():
-                        xq, a_s = ext.alignquant_activation_quantize_cuda(x_dev[(li, m, name)], None, scale_mode="token")
-                        y = None
-                        if reducer is not None and axis == "k":
-                            y = ext.alignquant_linear_allreduce(xq, a_s, entry[name], None, reducer, scale_mode="token", output_dtype=out_dtype[name])
-                        if y is None:
-                            y = ext.alignquant_linear_prepared(xq, a_s, entry[name], None, scale_mode="token", output_dtype=out_dtype[name])
-                            if world > 1 and axis == "k":
-                                all_reduce(y)
-                        results.append((name, y))
+                    for name in GROUPS:
+                        assert calls[position] == (m, li, name)
+                        results.append((name, project(position, x_dev[(li, m, name)])))
+                        position += 1
                     computed = torch.cuda.Event()
                     computed.record(main)
                     with torch.cuda.stream(copy_out):
@@ -432,6 +577,9 @@ def run_native(args) -> None:
 
     e2e_seconds = timed(e2e_run, max(1, min(args.steps, 5)), 1)
 
+    traffic = None
+    if world == 1 and lookahead and all(v is not None for v in NCU_DRAM_BYTES_PER_LAUNCH.values()):
+        traffic = sum(NCU_DRAM_BYTES_PER_LAUNCH.values()) / len(NCU_DRAM_BYTES_PER_LAUNCH)
     total_bytes = step_bytes * world  # every rank streams its own shard
     line = {
         "metric": "decode_gemv_hbm_gbs",
@@ -449,6 +597,8 @@ def run_native(args) -> None:
         "config": {
             "workload": WORKLOAD,
             "l2": "2 GB of distinct weights per step exceed the 126 MB L2; no flush between steps",
+            "lookahead": ("every projection asks the L2 to fetch the next projection's image while it runs (aq_linear_ahead)"
+                          if lookahead else "off"),
             "parallelism": f"tp{world}",
             "launch": launch_mode + ("" if world == 1 else
                                      f" + sum over ranks fused into the GEMV epilogue (peer memory; {own_sum_launches} of "
@@ -462,10 +612,12 @@ def run_native(args) -> None:
         "roofline": {
             "kernel": "cluster_decode_kernel (packed W4/W8 GEMV, M<=16)", "bound": "hbm",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-            "peak_source": f"{peak_source} HBM copy bandwidth", "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+            "peak_source": f"{peak_source} HBM copy bandwidth", "traffic": traffic,
             "bytes_per_launch": linear_bytes / pairs_per_step, "us_per_launch": kernel_seconds * 1e6,
         },
     }
+    if tp_check is not None:
+        line["tp_check"] = tp_check
     if rank == 0 and world == 1:
         sample = CpuSample()
         sample.run()
@@ -474,6 +626,25 @@ def run_native(args) -> None:
             "value": sample.bytes / cpu_seconds / 1e9, "unit": "GB/s", "cores": os.cpu_count() or 1,
             "kind": "port", "sample": CpuSample.description,
         }
+
+    # ---- the other legs of the metric; the sweep's buffers are released first
+    del layers, graph, kernel_graph, step
+    try:
+        del e2e_graph, x_dev
+    except NameError:
+        pass
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    if "prefill" in legs and world == 1:
+        try:
+            line["prefill"] = prefill_leg(ext, device, max(3, min(args.steps, 10)))
+        except Exception as error:  # the headline line is still reported
+            line["prefill"] = {"error": f"{type(error).__name__}: {error}"}
+    if "generation" in legs:
+        try:
+            line["generation"] = generation_leg(world, args.gen_tokens)
+        except Exception as error:
+            line["generation"] = {"error": f"{type(error).__name__}: {error}"}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -54,6 +54,41 @@ extern "C" {
 /* Library version: major * 10000 + minor * 100 + patch. */
 AQ_API int aq_version(void);
 
+/*
+ * Process-wide options.  The reference has no counterpart (its kernels have no device-side
+ * waits and one fixed FP32 operation order).
+ *   AQ_OPT_PEER_POLL_LIMIT  how often a tensor-parallel sum (aq_allreduce_f32, aq_linear_allreduce)
+ *                           polls for a peer's data before it gives up and reports AQ_ERR_DEVICE
+ *                           through aq_device_status; 64 .. 2^31-1, default 2^22 (seconds).  Takes
+ *                           effect for launches issued after the call.
+ *   AQ_OPT_GEMM_ROUNDING    how the tensor-memory GEMM (aq_linear_plan kernel 1) adds a K64 tile:
+ *                           AQ_GEMM_ROUNDING_FUSED (default): acc = fma(float(int32), a*w, acc),
+ *                           one rounding per tile; AQ_GEMM_ROUNDING_SEPARATE: multiply and add
+ *                           rounded separately, the operation order of the reference kernels
+ *                           (alignquant/kernels/cuda/linear.cu:956-963), about 20 % slower.  The
+ *                           per-tile int32 sums are exact either way.
+ *   AQ_OPT_GEMM_TILE        CTA tile of the GEMM, for tests and measurements: AQ_GEMM_TILE_AUTO
+ *                           (default), AQ_GEMM_TILE_PAIRED (128 columns, two 256-thread CTAs per
+ *                           SM), AQ_GEMM_TILE_NARROW (128 columns, one 512-thread CTA per SM),
+ *                           AQ_GEMM_TILE_WIDE (256 columns, one CTA per SM).  Results are
+ *                           bit-identical across the three.
+ *   AQ_OPT_GEMM_SPLIT       number of K ranges of the GEMM (1..8), 0 = automatic (default); changes
+ *                           the FP32 summation order as aq_linear_plan reports.
+ * aq_set_option returns AQ_OK or AQ_ERR_INVALID; aq_get_option the value or AQ_ERR_INVALID.
+ */
+#define AQ_OPT_PEER_POLL_LIMIT 1
+#define AQ_OPT_GEMM_ROUNDING 2
+#define AQ_OPT_GEMM_TILE 3
+#define AQ_OPT_GEMM_SPLIT 4
+#define AQ_GEMM_ROUNDING_FUSED 0
+#define AQ_GEMM_ROUNDING_SEPARATE 1
+#define AQ_GEMM_TILE_AUTO 0
+#define AQ_GEMM_TILE_PAIRED 1
+#define AQ_GEMM_TILE_NARROW 2
+#define AQ_GEMM_TILE_WIDE 4
+AQ_API int aq_set_option(int option, int64_t value);
+AQ_API int64_t aq_get_option(int option);
+
 /* Text of the last error raised on the calling thread ("" if none). */
 AQ_API const char* aq_last_error(void);
 
@@ -143,6 +178,24 @@ AQ_API int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, 
               void* workspace, int64_t workspace_bytes, int32_t* acc_dump, void* stream);
 
 /*
+ * aq_linear with a look-ahead: while this projection runs, the decode kernels (aq_linear_plan
+ * kernels 2 and 3; other kernels ignore the hint) ask the L2 cache to fetch next_bytes bytes at
+ * next_prepared -- normally the prepared image of the projection that the caller runs next
+ * (aq_prepared_bytes long).  A decode-size projection is a few microseconds of HBM traffic, less
+ * than a kernel's start-up and split-K hand-over; with the look-ahead HBM keeps streaming
+ * through those phases and the next kernel finds its weights on chip.  The range must lie in
+ * this GPU's own memory, be 16-byte aligned and a multiple of 16 bytes long; it is only read.
+ * next_prepared == NULL or next_bytes == 0: exactly aq_linear.  The reference has no
+ * counterpart (its decode kernels read weights straight from HBM,
+ * alignquant/kernels/cuda/linear.cu:1216-1313).
+ */
+AQ_API int aq_linear_ahead(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
+                    const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
+                    int schedule, int decode_splits, int out_dtype, void* out,
+                    void* workspace, int64_t workspace_bytes, int32_t* acc_dump,
+                    const void* next_prepared, int64_t next_bytes, void* stream);
+
+/*
  * aq_linear for callers that have no way to supply a workspace.  (No counterpart in the
  * reference, whose host function allocates its temporaries itself.)
  *
@@ -194,9 +247,9 @@ AQ_API int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int
 
 /*
  * Sum of the partial outputs of a row-parallel (K-sharded) projection over the ranks of
- * one node, through peer memory.  Replaces the dist.all_reduce that follows o_proj and
- * down_proj under tensor parallelism (alignquant/quantization/model.py:352-356) for the
- * small messages of decode; one process per GPU.
+ * one node, through peer memory.  The reference has no counterpart: it runs on one GPU and
+ * contains no collective.  This stands in for the dist.all_reduce that tensor parallelism
+ * needs after o_proj and down_proj, for the small messages of decode; one process per GPU.
  *   Every rank allocates an exchange buffer of aq_allreduce_buffer_bytes(world, max_count)
  *   bytes that all ranks of the node can address (peer-mapped: a CUDA IPC / VMM mapping,
  *   torch symmetric memory ...), zeroes it once, and all ranks synchronise on the host
@@ -208,8 +261,9 @@ AQ_API int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int
  *   are added in rank order, so every rank receives the same bits; `out` may alias `partial`.
  *   The call is one asynchronous kernel launch on `stream` (it can be captured and replayed:
  *   the call counter lives in the exchange buffer).  The kernel waits for the peers' data
- *   with a bounded poll; when a peer never arrives the wait gives up, the output is invalid
- *   and aq_device_status reports AQ_ERR_DEVICE.
+ *   with a bounded poll (AQ_OPT_PEER_POLL_LIMIT); when a peer never arrives the wait gives up,
+ *   the kernel still ends normally, the output is invalid and aq_device_status reports
+ *   AQ_ERR_DEVICE naming the rank.  Zero the exchange buffers of all ranks before using them again.
  */
 AQ_API int64_t aq_allreduce_buffer_bytes(int32_t world, int64_t max_count);
 /*
@@ -219,14 +273,26 @@ AQ_API int64_t aq_allreduce_buffer_bytes(int32_t world, int64_t max_count);
  * mixed as long as every rank issues the same sequence).  Automatic schedule only, and only
  * where aq_linear_plan reports kernel 3 (decode sizes, at most 32 rows); otherwise
  * AQ_ERR_INVALID, and the caller uses aq_linear + aq_allreduce_f32.  m * N <= max_count.
- * `out` receives the summed result in out_dtype.
+ * `out` receives the summed result in out_dtype.  next_prepared / next_bytes: look-ahead as in
+ * aq_linear_ahead (NULL / 0: none).
  */
 AQ_API int aq_linear_allreduce(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
                                const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
                                int out_dtype, void* out, int32_t rank, int32_t world, void* const* peer_buffers,
-                               int64_t max_count, void* stream);
+                               int64_t max_count, const void* next_prepared, int64_t next_bytes, void* stream);
 AQ_API int aq_allreduce_f32(const float* partial, float* out, int64_t count, int32_t rank, int32_t world,
                             void* const* peer_buffers, int64_t max_count, void* stream);
+
+/*
+ * Measurement aid: how fast this GPU's tensor cores execute tcgen05.mma kind::i8 when nothing
+ * else happens (operands resident in shared memory, no accumulator drain): one CTA per SM issues
+ * `pairs` x 2 MMAs of shape M128 N256 K32 back to back.  Runs the kernel twice on `stream`
+ * (warm-up, timed with CUDA events), SYNCHRONISES, and stores integer tera-operations per second
+ * in *tops (host pointer).  It is the denominator of the GEMM's tensor-pipe fraction, taken on
+ * the same device and clocks.  pairs in [16, 2^20]; 4096 takes about half a millisecond.  The
+ * reference has no counterpart.
+ */
+AQ_API int aq_measure_int8_peak(int32_t pairs, double* tops, void* stream);
 
 /*
  * Synchronises `stream`, then returns AQ_ERR_DEVICE if a kernel of this library gave

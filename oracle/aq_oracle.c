@@ -16,10 +16,14 @@
  *     (alignquant/quantization/exact.py:277-285 and
  *     alignquant/quantization/calibration.py:566-567), identity output transform.
  *
- * Build: gcc -O3 -march=x86-64-v3 -ffp-contract=off -fopenmp -shared -fPIC aq_oracle.c -o libaq_oracle.so
+ *   - fused FP32 variant (fused != 0): acc = fma(float(int), a * ws, acc), one rounding
+ *     per tile instead of two -- the order of the tensor-memory GEMM's default drain.
+ *
+ * Build: gcc -O3 -march=x86-64-v3 -ffp-contract=off -fopenmp -shared -fPIC aq_oracle.c -o libaq_oracle.so -lm
  * (-ffp-contract=off keeps every multiply and add separately rounded, as the
- * FP32 contract requires.)
+ * FP32 contract requires; the fused variant calls fmaf explicitly.)
  */
+#include <math.h>
 #include <stdint.h>
 #include <stddef.h>
 
@@ -54,8 +58,9 @@ void aqo_tile_accumulators(const int8_t* xq, const int8_t* w, int32_t* out,
  * sums are added in worker order and the range sums in range order.  workers = 1 is the
  * reference kernels' own order.
  */
-void aqo_linear_fp32(const int8_t* xq, const float* a, const int8_t* w, const float* ws,
-                     float* out, int64_t M, int64_t n_j, int64_t n_k, int64_t split_k, int64_t workers) {
+static void linear_fp32_impl(const int8_t* xq, const float* a, const int8_t* w, const float* ws,
+                             float* out, int64_t M, int64_t n_j, int64_t n_k, int64_t split_k, int64_t workers,
+                             int fused) {
   if (split_k < 1) split_k = 1;
   if (workers < 1) workers = 1;
   if (workers > 64) workers = 64;
@@ -73,9 +78,13 @@ void aqo_linear_fp32(const int8_t* xq, const float* a, const int8_t* w, const fl
           const float scale = a[m * n_k + k] * ws[j * n_k + k];
           const int8_t* x = xq + (m * n_k + k) * TILE;
           const int8_t* t = w + ((j * n_k + k) * TILE) * TILE;
-          for (int c = 0; c < TILE; ++c) {
-            const float scaled = (float)dot64(x, t + c * TILE) * scale;
-            part[v][c] = part[v][c] + scaled;
+          if (fused) {
+            for (int c = 0; c < TILE; ++c) part[v][c] = fmaf((float)dot64(x, t + c * TILE), scale, part[v][c]);
+          } else {
+            for (int c = 0; c < TILE; ++c) {
+              const float scaled = (float)dot64(x, t + c * TILE) * scale;
+              part[v][c] = part[v][c] + scaled;
+            }
           }
         }
         for (int c = 0; c < TILE; ++c) {
@@ -87,6 +96,17 @@ void aqo_linear_fp32(const int8_t* xq, const float* a, const int8_t* w, const fl
       for (int c = 0; c < TILE; ++c) out[m * n_j * TILE + j * TILE + c] = total[c];
     }
   }
+}
+
+void aqo_linear_fp32(const int8_t* xq, const float* a, const int8_t* w, const float* ws,
+                     float* out, int64_t M, int64_t n_j, int64_t n_k, int64_t split_k, int64_t workers) {
+  linear_fp32_impl(xq, a, w, ws, out, M, n_j, n_k, split_k, workers, 0);
+}
+
+/* acc = fma(float(int), a * ws, acc): the product a * ws is still rounded to FP32 first. */
+void aqo_linear_fp32_fused(const int8_t* xq, const float* a, const int8_t* w, const float* ws,
+                           float* out, int64_t M, int64_t n_j, int64_t n_k, int64_t split_k, int64_t workers) {
+  linear_fp32_impl(xq, a, w, ws, out, M, n_j, n_k, split_k, workers, 1);
 }
 
 /*

@@ -10,13 +10,20 @@ Every array below is produced by functions of the reference package
 nothing from this repository is imported, so the fixtures are independent of
 the code they check.  The linear cases follow the recipe of the reference's CPU
 dequantize-and-matmul (alignquant/quantization/calibration.py:552-572) with the
-per-tile selected W4/W8 payload.
+per-tile selected W4/W8 payload.  ``artifact_tiny/`` is a whole artifact directory
+written by the reference's ``build_artifact`` (alignquant/quantization/artifact.py:271-389)
+for a two-layer toy decoder, the way ``alignquant/build.py:62-100`` feeds it, with
+precision bitmaps and V/U seeds cut from the reference's Llama-3.2-3B preset;
+``artifact_tiny_io.npz`` holds inputs and the reference's FP64 outputs per module.
 """
 
 from __future__ import annotations
 
+import json
+import shutil
 import sys
 from pathlib import Path
+from types import SimpleNamespace
 
 import numpy as np
 import torch
@@ -141,7 +148,70 @@ def main(reference_root: str) -> None:
             y=y.numpy(),
             **{f"packed_{key}": value.numpy() for key, value in packed.items()},
         )
-    print("wrote", sorted(p.name for p in out_dir.glob("*.npz")))
+    # ---- a whole artifact directory through build_artifact (artifact.py:271-389) ----------
+    preset = json.loads((Path(reference_root) / "alignquant" / "data" / "llama-3.2-3b-instruct.json").read_text())
+    preset_rows = {row["name"]: row for row in preset["modules"]}
+    toy_shapes = {
+        "self_attn.q_proj": (256, 128), "self_attn.k_proj": (128, 128), "self_attn.v_proj": (128, 128),
+        "self_attn.o_proj": (128, 256), "mlp.gate_proj": (256, 128), "mlp.up_proj": (256, 128),
+        "mlp.down_proj": (128, 256),
+    }
+    shares_v_with = {"self_attn.k_proj": "self_attn.q_proj", "self_attn.v_proj": "self_attn.q_proj",
+                     "mlp.up_proj": "mlp.gate_proj"}  # members of a fused group share the V seeds
+    m = 5
+    inputs = {128: None, 256: None}
+    for k in inputs:
+        x = torch.randn((m, k), generator=gen, dtype=torch.float32)
+        x[:, 3] *= 20.0
+        inputs[k] = x.to(torch.float16)
+    modules, io = [], {f"x{k}": v.numpy() for k, v in inputs.items()}
+    for layer in (0, 1):
+        for short, (n, k) in toy_shapes.items():
+            name = f"model.layers.{layer}.{short}"
+            n_j, n_k = n // 64, k // 64
+            row = preset_rows[name]
+            # the first n_j * n_k bits of the preset's bitmap and the first seeds of its lists
+            bitmap = bytes.fromhex(row["w4_state_bits_lsb_hex"])[: (n_j * n_k + 7) // 8]
+            states = ra.unpack_w4w8_state_bits(torch.tensor(list(bitmap), dtype=torch.uint8), n_j=n_j, n_k=n_k)
+            if name == "model.layers.1.mlp.down_proj":
+                states = torch.full_like(states, ra.P4)  # an all-W4 module
+            if name == "model.layers.1.self_attn.o_proj":
+                states = torch.full_like(states, ra.P8)  # an all-W8 module
+            v_row = preset_rows[f"model.layers.{layer}.{shares_v_with.get(short, short)}"]
+            v_seeds = [int(v) for v in v_row["r5"]["v_seeds"][:n_k]]
+            u_seeds = [int(v) for v in row["r5"]["u_seeds"][:n_j]]
+            weight = (torch.randn((n, k), generator=gen, dtype=torch.float32) * 0.02).to(torch.float16)
+            wt = rx.transform_weight_tiles(rx.split_weight_tiles(weight.to(torch.float64)), v_seeds=v_seeds, u_seeds=u_seeds)
+            q4, s4 = rx.mse_quantize_tiles(wt, bits=4)
+            q8, s8 = rx.mse_quantize_tiles(wt, bits=8)
+            plan = SimpleNamespace(variant="R5", t_seed=-1, v_seeds=v_seeds, u_seeds=u_seeds)
+            modules.append(SimpleNamespace(
+                layer_name=name, weight_state_map=states, qweight4=q4.to(torch.int8), weight_scale4=s4.to(torch.float32),
+                qweight8=q8.to(torch.int8), weight_scale8=s8.to(torch.float32), n_j=n_j, n_k=n_k, in_features=k,
+                out_features=n, p4_codebook=None, plan=SimpleNamespace(normalized=lambda *, n_k, n_j, _p=plan: _p),
+            ))
+            # the module's output for the toy input (calibration.py:552-572 recipe, selected payload)
+            sel_q = torch.where((states == ra.P4)[:, :, None, None], q4, q8)
+            sel_s = torch.where(states == ra.P4, s4.to(torch.float32), s8.to(torch.float32))
+            xp = torch.zeros((16, k), dtype=torch.float16)
+            xp[:m] = inputs[k]
+            transformed = rx.transform_activation_tiles(xp.reshape(16, n_k, 64).permute(1, 0, 2), v_seeds=v_seeds)
+            aq, a_s = rx.a8_endpoint_quantize_tiles(transformed.reshape(n_k, 1, 16, 64))
+            a8 = rx.reconstruct_tiles(aq, a_s.to(torch.float32), dtype=torch.float64).reshape(n_k, 16, 64).permute(1, 0, 2)[:m]
+            wd = rx.reconstruct_tiles(sel_q, sel_s, dtype=torch.float64)
+            y_t = torch.einsum("mki,jkoi->mjo", a8, wd)
+            y = rx.inverse_output_tiles(y_t.permute(1, 0, 2), u_seeds=u_seeds).permute(1, 0, 2).reshape(m, n)
+            io[f"{name}/y"] = y.numpy()
+            io[f"{name}/v_seeds"] = np.asarray(v_seeds)
+            io[f"{name}/u_seeds"] = np.asarray(u_seeds)
+            io[f"{name}/states"] = states.numpy()
+    artifact_dir = out_dir / "artifact_tiny"
+    if artifact_dir.exists():
+        shutil.rmtree(artifact_dir)
+    ra.build_artifact(artifact_dir, modules=modules, model_identity={"id": "toy-decoder", "revision": "none", "loader": "none"})
+    ra.load_artifact(artifact_dir)  # the reference's own loader accepts what it wrote
+    np.savez_compressed(out_dir / "artifact_tiny_io.npz", **io)
+    print("wrote", sorted(p.name for p in out_dir.glob("*.npz")), "and", artifact_dir.name)
 
 
 if __name__ == "__main__":

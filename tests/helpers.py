@@ -69,4 +69,6 @@ def planned_fp32(ext, xq_np, a_mk, tiles, scales, m, n_j, n_k, **plan_args):
     plan = ext.linear_plan(m, n_j, n_k, **plan_args)
     if plan["kernel"] == 2:
         return oc.linear_fp32_ranges_c(xq_np, a_mk, tiles, scales, plan["splits"], plan["workers"])
-    return oc.linear_fp32_c(xq_np, a_mk, tiles, scales, plan["splits"], plan["workers"])
+    # the GEMM adds a tile with one fused multiply-add unless the library is told otherwise
+    fused = plan["kernel"] == 1 and not ext.gemm_rounding_is_separate()
+    return oc.linear_fp32_c(xq_np, a_mk, tiles, scales, plan["splits"], plan["workers"], fused=fused)

@@ -59,3 +59,33 @@ def test_installed_model_matches_oracle(scale_mode, rows):
         assert got.dtype == torch.bfloat16 and got.shape[:-1] == src.shape[:-1]
         # bf16 output: 8 bits of mantissa on top of the rel 1e-3 / abs 1e-2 contract
         assert np.allclose(got.float().cpu().numpy().reshape(want.shape), want, rtol=1e-2, atol=2e-2), short
+
+
+def test_reference_built_artifact_installs_and_matches_reference_outputs(golden_dir):
+    """tests/golden/artifact_tiny (written by the reference's build_artifact, non-identity V/U seeds and
+    bitmaps cut from its Llama-3.2-3B preset, one all-W4 and one all-W8 module) through load_artifact,
+    install_alignquant and the kernels, against the reference's FP64 outputs for the same inputs."""
+    from alignquant_b200.kernels.cuda import extension as ext
+    from alignquant_b200.quantization.artifact import load_artifact
+    from alignquant_b200.quantization.model import install_alignquant, reset_alignquant_state
+
+    ext.load_extension()
+    io = dict(np.load(golden_dir / "artifact_tiny_io.npz"))
+    artifact = load_artifact(golden_dir / "artifact_tiny")
+    model = _Tiny(layers=2).cuda().to(torch.float16)
+    installed, meta = install_alignquant(model, artifact, "cuda")  # reference scale mode: 16 x 64 tiles
+    assert len(installed) == 14 and meta["projection_group_count"] == 8
+    inputs = {k: torch.from_numpy(io[f"x{k}"]).cuda() for k in (128, 256)}
+    for index, layer in enumerate(model.model.layers):
+        reset_alignquant_state(model)
+        for short in ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+                      "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj"):
+            module = layer.get_submodule(short)
+            got = module(inputs[module.in_features])
+            ext.device_status()
+            want = io[f"model.layers.{index}.{short}/y"]
+            if module.bias is not None:
+                want = want + module.bias.float().cpu().numpy()
+            assert got.dtype == torch.float16
+            # fp16 result (2^-11 relative) on top of the rel 1e-3 / abs 1e-2 contract
+            assert np.allclose(got.float().cpu().numpy(), want, rtol=2e-3, atol=1e-2), (index, short)

@@ -22,6 +22,15 @@ def ext():
     return extension
 
 
+@pytest.fixture()
+def options(ext):
+    """Library options are process-wide: put the defaults back after the test."""
+    yield ext
+    ext.set_gemm_tile("auto")
+    ext.set_gemm_split(0)
+    ext.set_gemm_rounding(False)
+
+
 def _case(ext, m, n, k, scale_mode, seed, fraction=0.6, act_dtype=torch.bfloat16):
     n_j, n_k = n // 64, k // 64
     packed, states, tiles, scales = oc.synthetic_layer(n, k, seed=seed, w4_fraction=fraction)
@@ -50,8 +59,24 @@ def test_gemm_matches_oracle(ext, n, k, m, scale_mode):
     assert np.array_equal(dump.cpu().numpy(), oc.tile_accumulators_c(xq_np, tiles)), "int32 tile accumulators differ"
     got = out.cpu().numpy()
     want = helpers.planned_fp32(ext, xq_np, a_mk, tiles, scales, m, n_j, n_k, schedule="forced_prefill_m64")
-    assert np.array_equal(got, want), "fp32 not in reference operation order"
+    assert np.array_equal(got, want), "fp32 not in the planned operation order"
     assert np.allclose(got, oc.dequant_matmul_fp64(xq_np, a_mk, tiles, scales), rtol=REL, atol=ABS)
+
+
+@pytest.mark.parametrize("tile", ["paired", "narrow", "wide"])
+@pytest.mark.parametrize("m,n,k", [(130, 192, 192), (300, 320, 1024)])
+def test_gemm_separate_rounding_is_the_reference_order(options, tile, m, n, k):
+    """AQ_GEMM_ROUNDING_SEPARATE: multiply and add rounded separately, K tiles in increasing order."""
+    ext = options
+    ext.set_gemm_rounding(True)
+    ext.set_gemm_tile(tile)
+    n_j, n_k = n // 64, k // 64
+    weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "tile", seed=n + k + m)
+    out = ext.alignquant_linear_prepared(xq, a_s, weights, None, schedule="forced_prefill_m64")
+    ext.device_status()
+    splits = ext.linear_plan(m, n_j, n_k, schedule="forced_prefill_m64")["splits"]
+    want = oc.linear_fp32_c(xq.cpu().numpy(), a_mk, tiles, scales, splits)
+    assert np.array_equal(out.cpu().numpy(), want)
 
 
 @pytest.mark.parametrize("fraction", [0.0, 1.0])
@@ -92,7 +117,9 @@ def test_gemm_reference_fixture_with_output_transform(ext, golden_dir):
     assert np.allclose(out.cpu().numpy(), g["y"], rtol=REL, atol=ABS)
 
 
-def test_gemm_agrees_with_streaming_kernel_bit_for_bit(ext):
+def test_gemm_agrees_with_streaming_kernel_bit_for_bit(options):
+    ext = options
+    ext.set_gemm_rounding(True)  # the streaming kernel rounds multiply and add separately
     m, n, k = 96, 256, 384
     weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "tile", seed=8)
     splits = ext.linear_plan(m, n // 64, k // 64, schedule="forced_prefill_m64")["splits"]
@@ -105,10 +132,11 @@ def test_gemm_agrees_with_streaming_kernel_bit_for_bit(ext):
     assert torch.equal(a, b)
 
 
-@pytest.mark.parametrize("tile_rows", ["2", "4"])
-def test_gemm_both_cta_tile_widths(ext, monkeypatch, tile_rows):
-    """The 128- and the 256-column CTA tile give the same bits (K long enough to wrap the stage ring)."""
-    monkeypatch.setenv("ALIGNQUANT_B200_GEMM_TILE", tile_rows)
+@pytest.mark.parametrize("tile", ["paired", "narrow", "wide"])
+def test_gemm_all_cta_tiles(options, tile):
+    """The three CTA tiles give the same bits (K long enough to wrap the stage ring)."""
+    ext = options
+    ext.set_gemm_tile(tile)
     m, n, k = 260, 448, 1280
     weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "tile", seed=31)
     dump = torch.zeros((m, n // 64, k // 64, 64), dtype=torch.int32, device="cuda")
@@ -124,9 +152,10 @@ def test_gemm_both_cta_tile_widths(ext, monkeypatch, tile_rows):
 
 @pytest.mark.parametrize("split", ["2", "3", "8"])
 @pytest.mark.parametrize("m", [40, 128, 200])
-def test_gemm_split_k_clusters(ext, monkeypatch, m, split):
+def test_gemm_split_k_clusters(options, m, split):
     """K ranges over a thread-block cluster: integer sums exact, FP32 in split order, output transform applied."""
-    monkeypatch.setenv("ALIGNQUANT_B200_GEMM_SPLIT", split)
+    ext = options
+    ext.set_gemm_split(int(split))
     n, k = 320, 2048
     weights, tiles, scales, xq, a_s, a_mk = _case(ext, m, n, k, "tile", seed=77 + m)
     n_j, n_k = n // 64, k // 64
@@ -137,4 +166,4 @@ def test_gemm_split_k_clusters(ext, monkeypatch, m, split):
     ext.device_status()
     xq_np = xq.cpu().numpy()
     assert np.array_equal(dump.cpu().numpy(), oc.tile_accumulators_c(xq_np, tiles))
-    assert np.array_equal(out.cpu().numpy(), oc.linear_fp32_c(xq_np, a_mk, tiles, scales, int(split)))
+    assert np.array_equal(out.cpu().numpy(), oc.linear_fp32_c(xq_np, a_mk, tiles, scales, int(split), fused=True))

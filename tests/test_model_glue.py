@@ -83,11 +83,11 @@ class _Layer(nn.Module):
 
 
 class _Tiny(nn.Module):
-    def __init__(self, tp=1, hidden=128, q=256, kv=128, inter=256):
+    def __init__(self, tp=1, hidden=128, q=256, kv=128, inter=256, layers=1):
         super().__init__()
         self.config = type("C", (), {"model_type": "llama"})()
         self.model = nn.Module()
-        self.model.layers = nn.ModuleList([_Layer(hidden, q, kv, inter, tp)])
+        self.model.layers = nn.ModuleList([_Layer(hidden, q, kv, inter, tp) for _ in range(layers)])
 
 
 FULL_SHAPES = {

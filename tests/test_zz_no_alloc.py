@@ -4,8 +4,6 @@
 but cannot give it a workspace (fixed-signature operator plug-ins, runtimes that stop
 allocating device memory after start-up).  It must return what ``aq_linear`` returns for
 the same layer, call after call, although all its calls share one built-in scratch array.
-The file name sorts last so that a run that stops at the first failure has already run
-every other test.
 """
 
 from __future__ import annotations
@@ -24,11 +22,12 @@ pytestmark = pytest.mark.gpu
 REL, ABS = 1e-3, 1e-2  # the tolerance every fp32-output comparison in this suite uses
 
 
-def _static_call(lib, xq, a_s, weights, mode, out):
+def _static_call(lib, xq, a_s, weights, mode, out, u_meta=None):
     stream = torch.cuda.current_stream().cuda_stream
     return lib.aq_linear_decode_static(
         ctypes.c_void_p(xq.data_ptr()), ctypes.c_void_p(a_s.data_ptr()), mode, xq.size(0),
-        ctypes.c_void_p(weights.image.data_ptr()), weights.n_j, weights.n_k, None, 2,
+        ctypes.c_void_p(weights.image.data_ptr()), weights.n_j, weights.n_k,
+        None if u_meta is None else ctypes.c_void_p(u_meta.data_ptr()), 2,
         ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(stream),
     )
 
@@ -76,3 +75,41 @@ def test_static_scratch_entry_point_rejects_what_it_cannot_hold():
     out = torch.empty((17, 64), dtype=torch.float32, device="cuda")
     assert _static_call(lib, xq, a_s, weights, _lib.AQ_SCALE_TOKEN, out) == -1
     assert "1 to 16 rows" in _lib.last_error()
+    # A layer whose stream-K scratch need exceeds the built-in array: refused before anything is
+    # queued or read, so small stand-in buffers are enough (more than 1024 x 148 tiles = more than
+    # 256 CTA ranges of 16 rows).
+    weights.n_j, weights.n_k = 4096, 64
+    assert _static_call(lib, xq[:16], a_s[:16], weights, _lib.AQ_SCALE_TOKEN, out) == -3
+    assert "built-in scratch holds" in _lib.last_error()
+    weights.n_j, weights.n_k = 16385, 1  # more tile rows than the counter region has counters
+    assert _static_call(lib, xq[:1], a_s[:1], weights, _lib.AQ_SCALE_TOKEN, out) == -1
+    torch.cuda.synchronize()
+
+
+def test_static_scratch_entry_point_with_output_transform_and_tile_scales():
+    """Non-identity inverse output transform and 16 x 64 activation-tile scales: the same bits as
+    ``aq_linear`` where that runs the same kernel."""
+    from alignquant_b200 import _lib
+    from alignquant_b200.kernels.cuda import extension as ext
+
+    ext.load_extension()
+    lib = _lib.load()
+    n, k, m = 640, 1024, 11
+    n_j, n_k = n // 64, k // 64
+    packed, _, tiles, scales = oc.synthetic_layer(n, k, seed=23)
+    weights, _ = helpers.prepare_layer(packed, n_k)
+    from alignquant_b200.quantization.exact import metadata_stack
+
+    u_meta = metadata_stack([3, -1, 0, 7, 2, -1, 5, 1, 4, 6], torch.device("cuda"))
+    xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=2), torch.float16)
+    xq, a_s = ext.alignquant_activation_quantize_cuda(xt, None)
+    want = ext.alignquant_linear_prepared(xq, a_s, weights, u_meta)
+    assert ext.linear_plan(m, n_j, n_k)["kernel"] == 2
+    for call in range(2):
+        out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+        assert _static_call(lib, xq, a_s, weights, _lib.AQ_SCALE_TILE, out, u_meta) == 0, _lib.last_error()
+        ext.device_status()
+        assert torch.equal(out, want), f"call {call}"
+    a_mk = np.repeat(a_s.cpu().numpy().reshape(-1, n_k), 16, axis=0)[:m]
+    y64 = oc.dequant_matmul_fp64(xq.cpu().numpy(), a_mk, tiles, scales, u_meta.cpu().numpy())
+    assert np.allclose(want.cpu().numpy(), y64, rtol=REL, atol=ABS)
