@@ -10,7 +10,8 @@ from pathlib import Path
 AQ_OK = 0
 AQ_F16, AQ_BF16, AQ_F32 = 0, 1, 2
 AQ_SCALE_TILE, AQ_SCALE_TOKEN = 0, 1
-AQ_OPT_PEER_POLL_LIMIT, AQ_OPT_GEMM_ROUNDING, AQ_OPT_GEMM_TILE, AQ_OPT_GEMM_SPLIT = 1, 2, 3, 4
+AQ_OPT_PEER_POLL_LIMIT, AQ_OPT_GEMM_ROUNDING, AQ_OPT_GEMM_TILE, AQ_OPT_GEMM_SPLIT, AQ_OPT_DECODE_KERNEL = 1, 2, 3, 4, 5
+AQ_DECODE_KERNEL_AUTO, AQ_DECODE_KERNEL_CLUSTER = 0, 1
 AQ_GEMM_ROUNDING_FUSED, AQ_GEMM_ROUNDING_SEPARATE = 0, 1
 GEMM_TILES = {"auto": 0, "paired": 1, "narrow": 2, "wide": 4}
 SCHEDULE_CODES = {"auto": 0, "forced_decode": 1, "forced_prefill": 2, "forced_prefill_m64": 3}
@@ -25,6 +26,7 @@ SIGNATURES = {
     "aq_version": (_INT, []),
     "aq_last_error": (ctypes.c_char_p, []),
     "aq_quantize_act": (_INT, [_P, _INT, _I64, _I64, _P, _INT, _P, _P, _P]),
+    "aq_rmsnorm_quantize": (_INT, [_P, _INT, _I64, _I64, _P, ctypes.c_float, _P, _P, _P, _P]),
     "aq_prepared_bytes": (_I64, [_I32, _I32, _I64, _I64]),
     "aq_repack": (_INT, [_P, _P, _P, _P, _P, _P, _P, _I32, _I32, _I64, _I64, _P, _I64, _P]),
     "aq_linear_workspace_bytes": (_I64, [_I64, _I32, _I32, _INT, _INT]),

@@ -10,7 +10,7 @@ from pathlib import Path
 PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIB_PATH = PACKAGE_DIR / "libalignquant_b200.so"
-SOURCES = ("aq_abi.cu", "aq_quantize.cu", "aq_repack.cu", "aq_stream.cu", "aq_cluster_decode.cu", "aq_decode.cu", "aq_gemm_tmem.cu", "aq_allreduce.cu", "aq_peak.cu")
+SOURCES = ("aq_abi.cu", "aq_quantize.cu", "aq_repack.cu", "aq_stream.cu", "aq_cluster_decode.cu", "aq_direct_decode.cu", "aq_decode.cu", "aq_gemm_tmem.cu", "aq_allreduce.cu", "aq_peak.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",

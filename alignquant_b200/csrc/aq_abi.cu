@@ -62,12 +62,14 @@ std::atomic<int64_t> g_peer_poll_limit{kDefaultPeerPollLimit};
 std::atomic<int64_t> g_gemm_rounding{0};
 std::atomic<int64_t> g_gemm_tile{0};
 std::atomic<int64_t> g_gemm_split{0};
+std::atomic<int64_t> g_decode_kernel{0};
 }  // namespace
 
 uint32_t peer_poll_limit() { return static_cast<uint32_t>(g_peer_poll_limit.load(std::memory_order_relaxed)); }
 bool gemm_separate_rounding() { return g_gemm_rounding.load(std::memory_order_relaxed) != 0; }
 int gemm_tile_option() { return static_cast<int>(g_gemm_tile.load(std::memory_order_relaxed)); }
 int gemm_split_option() { return static_cast<int>(g_gemm_split.load(std::memory_order_relaxed)); }
+int decode_kernel_option() { return static_cast<int>(g_decode_kernel.load(std::memory_order_relaxed)); }
 
 namespace {
 
@@ -83,11 +85,16 @@ bool valid_split(int s) { return s == 0 || s == 1 || s == 2 || s == 4 || s == 8 
 //     (explicit split counts, forced non-GEMM schedules up to 128 rows)
 //   1 tensor-memory GEMM (K ranges over a cluster where few rows leave SMs idle)
 //   2 persistent stream-K kernel (at most 16 rows, layers with very few tile rows)
-//   3 cluster kernel, one warp (two for 17..32 rows) per tile; the default decode kernel
+//   3 cluster kernel, one warp (two for 17..32 rows) per tile: decode sizes, layers too narrow
+//     for family 4
+//   4 decode kernel of many small CTAs without a K split (reported to callers as kernel 3 with
+//     one range): the default decode kernel of layers with enough tile rows and K up to 64 tiles
+//     (128 for at most eight rows)
 int choose_kernel(int64_t m, int n_j, int n_k, int schedule, int decode_splits) {
   if (schedule == AQ_SCHEDULE_PREFILL_M64) return 1;
   if (schedule == AQ_SCHEDULE_AUTO && (m > kStreamMaxRows || (decode_splits == 0 && m > kAutoGemmRows))) return 1;
   if (decode_splits != 0 || m > kClusterMaxRows) return 0;
+  if (decode_kernel_option() != AQ_DECODE_KERNEL_CLUSTER && direct_decode_supported(m, n_j, n_k)) return 4;
   const bool cluster_ok = cluster_decode_supported(n_j, n_k);
   if (m <= kDecodeMaxRows && (8 * n_j < num_sms() || !cluster_ok)) return 2;
   return cluster_ok ? 3 : 0;
@@ -121,6 +128,12 @@ int aq_set_option(int option, int64_t value) {
                  "AQ_OPT_GEMM_TILE must be one of the AQ_GEMM_TILE_* values, got %lld", static_cast<long long>(value));
       g_gemm_tile.store(value, std::memory_order_relaxed);
       return AQ_OK;
+    case AQ_OPT_DECODE_KERNEL:
+      AQ_REQUIRE(value == AQ_DECODE_KERNEL_AUTO || value == AQ_DECODE_KERNEL_CLUSTER,
+                 "AQ_OPT_DECODE_KERNEL must be AQ_DECODE_KERNEL_AUTO or AQ_DECODE_KERNEL_CLUSTER, got %lld",
+                 static_cast<long long>(value));
+      g_decode_kernel.store(value, std::memory_order_relaxed);
+      return AQ_OK;
     case AQ_OPT_GEMM_SPLIT:
       AQ_REQUIRE(value >= 0 && value <= 8, "AQ_OPT_GEMM_SPLIT must be 0 (automatic) or 1..8, got %lld",
                  static_cast<long long>(value));
@@ -141,6 +154,8 @@ int64_t aq_get_option(int option) {
       return g_gemm_tile.load(std::memory_order_relaxed);
     case AQ_OPT_GEMM_SPLIT:
       return g_gemm_split.load(std::memory_order_relaxed);
+    case AQ_OPT_DECODE_KERNEL:
+      return g_decode_kernel.load(std::memory_order_relaxed);
     default:
       fail(AQ_ERR_INVALID, "unknown option %d", option);
       return AQ_ERR_INVALID;
@@ -164,6 +179,20 @@ int aq_quantize_act(const void* x, int x_dtype, int64_t m, int64_t k, const int3
   AQ_REQUIRE(aligned(scales, 4) && aligned(v_metadata, 4), "scales and v_metadata must be 4-byte aligned");
   return launch_quantize(x, x_dtype, m, k, v_metadata, scale_mode, q, scales,
                          static_cast<cudaStream_t>(stream));
+}
+
+int aq_rmsnorm_quantize(const void* x, int x_dtype, int64_t m, int64_t k, const void* weight, float eps, int8_t* q,
+                        float* scales, void* normed, void* stream) {
+  AQ_REQUIRE(x != nullptr && weight != nullptr && q != nullptr && scales != nullptr,
+             "x, weight, q and scales must not be NULL");
+  AQ_REQUIRE(m >= 1, "x must have at least one row, got m=%lld", static_cast<long long>(m));
+  AQ_REQUIRE(k >= kTile && k % kTile == 0, "K must be a positive multiple of 64, got %lld", static_cast<long long>(k));
+  AQ_REQUIRE(k <= (1 << 24), "K too large");
+  AQ_REQUIRE(eps >= 0.0f, "eps must not be negative");
+  AQ_REQUIRE(aligned(x, 16) && aligned(weight, 16) && aligned(q, 16) && aligned(normed, 16),
+             "x, weight, q and normed must be 16-byte aligned for 128-bit access");
+  AQ_REQUIRE(aligned(scales, 4), "scales must be 4-byte aligned");
+  return launch_rmsnorm_quantize(x, x_dtype, m, k, weight, eps, q, scales, normed, static_cast<cudaStream_t>(stream));
 }
 
 int64_t aq_prepared_bytes(int32_t n_j, int32_t n_k, int64_t t4, int64_t t8) {
@@ -286,12 +315,13 @@ static int linear_impl(const int8_t* xq, const float* act_scales, int scale_mode
 
   const int kernel = choose_kernel(m, n_j, n_k, schedule, decode_splits);
   if (tp != nullptr) {
-    AQ_REQUIRE(kernel == 3, "the fused tensor-parallel sum is only available where aq_linear_plan reports kernel 3");
+    AQ_REQUIRE(kernel == 3 || kernel == 4, "the fused tensor-parallel sum is only available where aq_linear_plan reports kernel 3");
     a.peer_buffers = tp->peer_buffers;
     a.tp_rank = tp->rank;
     a.tp_world = tp->world;
     a.ar_max_count = tp->max_count;
   }
+  if (kernel == 4) return launch_direct_decode(a, s);
   if (kernel == 3) return launch_cluster_decode(a, s);
   if (kernel == 0) {
     AQ_REQUIRE(decode_splits == 0 || m <= kStreamMaxRows,
@@ -404,6 +434,10 @@ int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int decode
   } else if (k == 3) {
     *splits = cluster_decode_split(m, n_j, n_k);
     *workers = 8;
+  } else if (k == 4) {  // same order as kernel 3 with a single K range
+    *kernel = 3;
+    *splits = 1;
+    *workers = direct_decode_workers(m, n_k);
   }
   return AQ_OK;
 }
@@ -443,7 +477,9 @@ int aq_device_status(void* stream) {
   const int stream_status = take_stream_status();
   const int gemm_status = take_gemm_status();
   const int decode_status = take_decode_status();
-  const int cluster_decode_status = take_cluster_decode_status();
+  const int direct_status = take_direct_decode_status();
+  int cluster_decode_status = take_cluster_decode_status();
+  if (cluster_decode_status == 0) cluster_decode_status = direct_status;  // both report the fused rank sum's waits
   const int allreduce_status = take_allreduce_status();
   if (allreduce_status > 0) {
     return fail(AQ_ERR_DEVICE, "the peer all-reduce gave up waiting for rank %d; its output is invalid", allreduce_status - 1);

@@ -50,6 +50,9 @@ int num_sms();
 int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, const int32_t* v_metadata,
                     int scale_mode, int8_t* q, float* scales, cudaStream_t stream);
 
+int launch_rmsnorm_quantize(const void* x, int x_dtype, int64_t m, int64_t k, const void* weight, float eps, int8_t* q,
+                            float* scales, void* normed, cudaStream_t stream);
+
 int launch_repack(const uint8_t* state_bits, const uint8_t* w4_payload, const float* w4_scales,
                   const int8_t* w8_payload, const float* w8_scales, const int32_t* w4_row_offsets,
                   const int32_t* w8_row_offsets, int n_j, int n_k, void* prepared,
@@ -101,6 +104,13 @@ int cluster_decode_split(int64_t m, int n_j, int n_k);
 bool cluster_decode_supported(int n_j, int n_k);
 int take_cluster_decode_status();
 
+// Decode kernel of many small CTAs without a K split for m <= 32: layers with enough column
+// groups to fill the machine and K short enough for a CTA's block to fit shared memory.
+int launch_direct_decode(const LinearArgs& a, cudaStream_t stream);
+bool direct_decode_supported(int64_t m, int n_j, int n_k);
+int direct_decode_workers(int64_t m, int n_k);
+int take_direct_decode_status();
+
 // Persistent stream-K kernel for m <= 16 (needs a zeroed, self-cleaning workspace).
 int launch_decode_linear(const LinearArgs& a, cudaStream_t stream);
 int64_t decode_workspace_bytes(int64_t m, int n_j, int n_k);
@@ -134,6 +144,7 @@ uint32_t peer_poll_limit();
 bool gemm_separate_rounding();
 int gemm_tile_option();   // AQ_GEMM_TILE_*
 int gemm_split_option();  // 0 = automatic, 1..8 forced
+int decode_kernel_option();  // AQ_DECODE_KERNEL_*
 // Whether kernels are launched with programmatic stream serialization (dependent
 // launch); on by default, ALIGNQUANT_B200_PDL=0 turns it off.
 bool use_dependent_launch();

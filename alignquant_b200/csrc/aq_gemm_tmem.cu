@@ -57,8 +57,8 @@ constexpr int kEpiRowFloats = 65;
 // CTA tile; kPaired = two small CTAs per SM instead of one large one.
 //   large CTA (512 threads, one per SM): warps 0..TN-1 widen, 4 issues the MMAs, 5 streams the
 //     activations, 6-7 the weights, 8-15 drain (lane quarter x column half); 512 tensor-memory
-//     columns = 512 / (64 TN) accumulators.  TN = 4 is the default tile, TN = 2 is used where
-//     the wider grid would leave SMs idle.
+//     columns = 512 / (64 TN) accumulators.  With TN = 2 (four accumulators) warps 2-5 issue the
+//     MMAs in turn and warp 6 also streams the activations.
 //   paired CTA (256 threads, TN = 2, two per SM): warp 0 issues the MMAs, warp 1 streams
 //     activations and weights, warps 2-3 widen, warps 4-7 drain (one per lane quarter, all 128
 //     columns); 256 tensor-memory columns = two accumulators; six stages of 16 KiB.  The step
@@ -71,8 +71,14 @@ struct Layout {
   static constexpr int kCtasPerSm = kPaired ? 2 : 1;
   static constexpr int kStages = kPaired ? 6 : 8;
   static constexpr int kTmemColumns = kPaired ? 256 : 512;
-  static constexpr int kMmaWarp = kPaired ? 0 : 4;
-  static constexpr int kActWarp = kPaired ? 1 : 5;
+  static constexpr bool kNarrow = !kPaired && TN == 2;
+  // MMA-issuing warps: warp kMmaWarp + i issues the K steps kt with kt % kMmaWarps == i.  Waiting
+  // for operands and an accumulator, two MMAs and two commits cost the issuing warp several
+  // hundred cycles per step; with four 128-column accumulators that, not the tensor pipe or the
+  // drain, bounds a step, so the one-CTA 128-column layout spreads the steps over four warps.
+  static constexpr int kMmaWarp = kPaired ? 0 : kNarrow ? 2 : 4;
+  static constexpr int kMmaWarps = kNarrow ? 4 : 1;
+  static constexpr int kActWarp = kPaired ? 1 : kNarrow ? 6 : 5;
   static constexpr int kFirstCopyWarp = kPaired ? 1 : 6;
   static constexpr int kCopyWarps = kPaired ? 1 : 2;
   static constexpr int kFirstWidenWarp = kPaired ? 2 : 0;
@@ -85,8 +91,8 @@ struct Layout {
   static constexpr int kStageBytes = kABytes + kBBytes;  // a multiple of the 1024-byte operand alignment
   static constexpr int kRecBytes = TN * kMaxNk * static_cast<int>(sizeof(TileRecord));
   static constexpr int kAccs = kTmemColumns / kCols;
-  // ready[S], empty[S], packed[S][TN], acc_full[kAccs], acc_empty[kAccs], final
-  static constexpr int kNumBars = (2 + TN) * kStages + 2 * kAccs + 1;
+  // ready[S], empty[S], packed[S][TN], acc_full[kAccs], acc_empty[kAccs], final[kMmaWarps]
+  static constexpr int kNumBars = (2 + TN) * kStages + 2 * kAccs + kMmaWarps;
   static constexpr int kSmemBytes = kStages * kStageBytes + kRecBytes + kNumBars * 8 + 16;
   static constexpr int kHalves = kDrainWarps / 4;        // column groups of the drain warps
   static constexpr int kTilesPerHalf = TN / kHalves;     // weight tile rows drained by one warp
@@ -130,6 +136,39 @@ __device__ __forceinline__ void drain_chunk_fused(uint64_t (&acc)[NACC], int c, 
   for (int i = 0; i < 8; ++i) {
     const uint64_t f = pack2(__float_as_uint(__int2float_rn(v[2 * i])), __float_as_uint(__int2float_rn(v[2 * i + 1])));
     acc[c * 8 + i] = fma2(f, scale2, acc[c * 8 + i]);
+  }
+}
+
+// 64 consecutive FP32 sums (32 packed pairs) of one row -> out[first .. first + 63] with 16-byte stores.
+__device__ __forceinline__ void store_row64(void* out, int dtype, int64_t first, const uint64_t* acc) {
+  if (dtype == AQ_F32) {
+    float4* dst = reinterpret_cast<float4*>(static_cast<float*>(out) + first);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float a, b, c, d;
+      unpack2(acc[2 * i], a, b);
+      unpack2(acc[2 * i + 1], c, d);
+      dst[i] = make_float4(a, b, c, d);
+    }
+  } else {
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<uint16_t*>(out) + first);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint32_t w[4];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        float a, b;
+        unpack2(acc[4 * i + h], a, b);
+        if (dtype == AQ_BF16) {
+          const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+          w[h] = *reinterpret_cast<const uint32_t*>(&v);
+        } else {
+          const __half2 v = __floats2half2_rn(a, b);
+          w[h] = *reinterpret_cast<const uint32_t*>(&v);
+        }
+      }
+      dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
   }
 }
 
@@ -181,7 +220,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
   auto packed = [&](int s, int t) { return bar0 + 8u * (2 * kStages + TN * s + t); };
   auto acc_full = [&](int b) { return bar0 + 8u * ((2 + TN) * kStages + b); };
   auto acc_empty = [&](int b) { return bar0 + 8u * ((2 + TN) * kStages + kAccs + b); };
-  const uint32_t final_bar = bar0 + 8u * ((2 + TN) * kStages + 2 * kAccs);
+  auto final_bar = [&](int i) { return bar0 + 8u * ((2 + TN) * kStages + 2 * kAccs + i); };
 
   // one thread per barrier: the initialisations would otherwise run one after the other
   if (threadIdx.x < S::kNumBars) {
@@ -297,14 +336,16 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         }
       }
       __syncwarp();
-    } else if (warp == S::kMmaWarp) {
-      // ---------------- MMA issuer ---------------------------------------------------
+    } else if (warp >= S::kMmaWarp && warp < S::kMmaWarp + S::kMmaWarps) {
+      // ---------------- MMA issuer(s) ------------------------------------------------
       // The whole warp walks the loop so that addresses and descriptors stay warp-uniform
-      // values (the MMA takes them from uniform registers); one elected lane issues.
+      // values (the MMA takes them from uniform registers); one elected lane issues.  Steps
+      // issued by different warps use different stages and different accumulators.
       const uint32_t idesc = instr_desc_i8(64 * tiles_here);
       const uint32_t stage0 = smem_u32(stages);
+      const int issuer = warp - S::kMmaWarp;
       bool ok = true;
-      for (int kt = 0; kt < steps; ++kt) {
+      for (int kt = issuer; kt < steps; kt += S::kMmaWarps) {
         const int s = kt % kStages;
         const int b = kt % kAccs;
         ok = warp_wait(ready(s), (kt / kStages) & 1, lane, abort_flag, &g_gemm_status, 2);
@@ -326,8 +367,8 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
       }
       if (!ok && lane == 0) {
         // make sure nothing issued is still running before tensor memory is freed
-        tc_commit(final_bar);
-        for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(final_bar, 0); ++i) {
+        tc_commit(final_bar(issuer));
+        for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(final_bar(issuer), 0); ++i) {
         }
       }
       __syncwarp();
@@ -358,17 +399,66 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         (p.scale_mode == AQ_SCALE_TILE && row_valid) ? p.act_scales + (grow >> 4) * n_k : nullptr;
     const TileRecord* recs = rec_smem + (kTH * half) * kMaxNk;
 
-    // Software pipeline over 16-column chunks (four per weight tile) with two register
-    // buffers: while the arithmetic of one chunk runs, the tensor-memory load of the next one
-    // is in flight.  The accumulator goes back to the MMA thread as soon as its last chunk
-    // has been loaded, before that chunk's arithmetic.
-    int va[16], vb[16];
     tc_fence_before();
     __syncwarp();
     if (lane == 0) {  // every accumulator starts out free
       for (int b = 0; b < kAccs; ++b) mbar_arrive(acc_empty(b));
     }
-    bool ok = warp_wait(acc_full(0), 0, lane, abort_flag, &g_gemm_status, 7);
+    bool ok = true;
+    if constexpr (kTH == 1) {
+      // One weight tile (64 columns) per warp and K step: the whole slice of the accumulator is
+      // loaded at once and the accumulator handed back BEFORE the arithmetic, so that it is held
+      // only for the time of the loads.  What bounds a K step otherwise is not arithmetic but the
+      // round trip of an accumulator (hand back, wake the MMA warp, MMA, commit, wake the drain
+      // warps) divided by the number of accumulators the 512 tensor-memory columns hold.
+      int v0[16], v1[16], v2[16], v3[16];
+      for (int kt = 0; kt < steps; ++kt) {
+        const int b = kt % kAccs;
+        ok = warp_wait(acc_full(b), (kt / kAccs) & 1, lane, abort_flag, &g_gemm_status, 7);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t col = taddr + static_cast<uint32_t>(b * S::kCols);
+        tc_ld16(col, v0);
+        tc_ld16(col + 16, v1);
+        tc_ld16(col + 32, v2);
+        tc_ld16(col + 48, v3);
+        tc_wait_ld(v0);
+        tc_wait_ld(v1);
+        tc_wait_ld(v2);
+        tc_wait_ld(v3);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty(b));
+        const float a_scale = tile_scales != nullptr ? tile_scales[k_begin + kt] : token_scale;
+        const TileRecord rec = recs[kt];
+        const float scale = __fmul_rn(a_scale, rec.scale);
+        const uint64_t scale2 = pack2(__float_as_uint(scale), __float_as_uint(scale));
+        if (kFused) {
+          drain_chunk_fused(acc, 0, v0, scale2);
+          drain_chunk_fused(acc, 1, v1, scale2);
+          drain_chunk_fused(acc, 2, v2, scale2);
+          drain_chunk_fused(acc, 3, v3, scale2);
+        } else {
+          drain_chunk(acc, 0, v0, scale);
+          drain_chunk(acc, 1, v1, scale);
+          drain_chunk(acc, 2, v2, scale);
+          drain_chunk(acc, 3, v3, scale);
+        }
+        if (kDump && row_valid && half < tiles_here) {
+          int32_t* dump = p.acc_dump + ((grow * p.n_j + (j0 + half)) * n_k + k_begin + kt) * kTile;
+          dump_chunk(dump, 0, v0, rec);
+          dump_chunk(dump, 16, v1, rec);
+          dump_chunk(dump, 32, v2, rec);
+          dump_chunk(dump, 48, v3, rec);
+        }
+      }
+    } else {
+    // Software pipeline over 16-column chunks (four per weight tile) with two register
+    // buffers: while the arithmetic of one chunk runs, the tensor-memory load of the next one
+    // is in flight.  The accumulator goes back to the MMA thread as soon as its last chunk
+    // has been loaded, before that chunk's arithmetic.
+    int va[16], vb[16];
+    ok = warp_wait(acc_full(0), 0, lane, abort_flag, &g_gemm_status, 7);
     if (ok) {
       tc_fence_after();
       tc_ld16(taddr, va);
@@ -421,6 +511,7 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         if (kDump) dump_chunk(dump[c >> 2], (c & 3) * 16, cur, rec[c >> 2]);
       }
     }
+    }
 
     // ---------------- epilogue: rows through shared memory, coalesced stores --------
     if (split_k > 1) {
@@ -446,6 +537,13 @@ tmem_gemm_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) 
         const int tl = kTH * half + t;
         if (tl < tiles_here) {
           const int j = j0 + tl;
+          const int32_t* row_meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
+          if (row_meta == nullptr || row_meta[0] == 0) {
+            // No output transform: a thread owns 64 consecutive columns of its row, i.e. whole
+            // 128-byte lines of the result, and stores them straight from its registers.
+            if (row_valid) store_row64(p.out, p.out_dtype, grow * n_cols + static_cast<int64_t>(j) * kTile, &acc[t * 32]);
+            continue;
+          }
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             float lo, hi;

@@ -5,8 +5,9 @@
 //                  rounding of the reference kernel
 //                  (alignquant/kernels/cuda/linear.cu:453-603), optional structured
 //                  64-point transform of every 64-column block first;
-//   AQ_SCALE_TOKEN one scale per row, IEEE float32 arithmetic.
-// Both are bandwidth-bound: 128-bit loads and stores, warp-shuffle reductions.
+//   AQ_SCALE_TOKEN one scale per row, IEEE float32 arithmetic; also fused with the RMSNorm
+//                  that precedes a decoder's qkv and gate/up projections.
+// All are bandwidth-bound: 128-bit loads and stores, warp-shuffle reductions.
 #include "aq_common.cuh"
 #include "aq_ptx.cuh"
 
@@ -143,6 +144,165 @@ __global__ void __launch_bounds__(256) quantize_token_kernel(const T* __restrict
         float v[16];
         load16(xr + c * 16, v);
         *reinterpret_cast<uint4*>(qr + c * 16) = quantize_chunk(v, scale, inv_scale);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm + AQ_SCALE_TOKEN quantizer in one pass over the row.
+//   r    = float(1 / sqrt(sum(x^2) / K + eps))      sum, division and root in FP64
+//   n    = round_T(x * r)                            the normalised value in the activation type
+//   y    = round_T(float(weight) * n)                what a decoder's RMSNorm module returns
+//   s    = max(absmax(y) / 127, 1e-12),  q = rint(y / s) clamped to [-127, 127]
+// (the arithmetic of the Llama / Qwen3 RMSNorm module followed by the per-token quantizer).
+// One CTA per row; rows of up to 8192 values stay in registers between the three phases,
+// longer rows are read again.
+// ---------------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ float round_to(float v);
+template <>
+__device__ __forceinline__ float round_to<__half>(float v) { return __half2float(__float2half_rn(v)); }
+template <>
+__device__ __forceinline__ float round_to<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+template <>
+__device__ __forceinline__ float round_to<float>(float v) { return v; }
+
+template <typename T>
+__device__ __forceinline__ void store16(T* p, const float (&v)[16]);
+template <>
+__device__ __forceinline__ void store16<__half>(__half* p, const float (&v)[16]) {
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  reinterpret_cast<uint4*>(p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+template <>
+__device__ __forceinline__ void store16<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[16]) {
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  reinterpret_cast<uint4*>(p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+template <>
+__device__ __forceinline__ void store16<float>(float* p, const float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(p)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+
+template <typename T>
+__device__ __forceinline__ void normalise16(float (&v)[16], const T* weight, float r) {
+  float w[16];
+  load16(weight, w);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = round_to<T>(__fmul_rn(w[i], round_to<T>(__fmul_rn(v[i], r))));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const T* __restrict__ x, const T* __restrict__ weight,
+                                                               float eps, int8_t* __restrict__ q,
+                                                               float* __restrict__ scales, T* __restrict__ normed,
+                                                               int64_t m, int k) {
+  __shared__ double warp_sum[8];
+  __shared__ float warp_max[8];
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int chunks = k / 16;
+  const bool in_registers = chunks <= 512;
+  for (int64_t row = blockIdx.x; row < m; row += gridDim.x) {
+    const T* xr = x + row * k;
+    float v0[16], v1[16];
+    const int c0 = threadIdx.x, c1 = threadIdx.x + 256;
+    double ss = 0.0;
+    if (in_registers) {
+      if (c0 < chunks) {
+        load16(xr + c0 * 16, v0);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ss += static_cast<double>(v0[i]) * static_cast<double>(v0[i]);
+      }
+      if (c1 < chunks) {
+        load16(xr + c1 * 16, v1);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ss += static_cast<double>(v1[i]) * static_cast<double>(v1[i]);
+      }
+    } else {
+      for (int c = threadIdx.x; c < chunks; c += 256) {
+        float v[16];
+        load16(xr + c * 16, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ss += static_cast<double>(v[i]) * static_cast<double>(v[i]);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) warp_sum[warp] = ss;
+    __syncthreads();
+    double total = warp_sum[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) total += warp_sum[w];
+    const float r = static_cast<float>(1.0 / sqrt(total / static_cast<double>(k) + static_cast<double>(eps)));
+
+    float amax = 0.0f;
+    if (in_registers) {
+      if (c0 < chunks) {
+        normalise16(v0, weight + c0 * 16, r);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v0[i]));
+      }
+      if (c1 < chunks) {
+        normalise16(v1, weight + c1 * 16, r);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v1[i]));
+      }
+    } else {
+      for (int c = threadIdx.x; c < chunks; c += 256) {
+        float v[16];
+        load16(xr + c * 16, v);
+        normalise16(v, weight + c * 16, r);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) warp_max[warp] = amax;
+    __syncthreads();
+    float block_max = warp_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) block_max = fmaxf(block_max, warp_max[w]);
+    const float scale = fmaxf(__fdiv_rn(block_max, 127.0f), 1.0e-12f);
+    const float inv_scale = __fdiv_rn(1.0f, scale);
+    if (threadIdx.x == 0) scales[row] = scale;
+    int8_t* qr = q + row * k;
+    T* nr = normed != nullptr ? normed + row * k : nullptr;
+    if (in_registers) {
+      if (c0 < chunks) {
+        *reinterpret_cast<uint4*>(qr + c0 * 16) = quantize_chunk(v0, scale, inv_scale);
+        if (nr != nullptr) store16(nr + c0 * 16, v0);
+      }
+      if (c1 < chunks) {
+        *reinterpret_cast<uint4*>(qr + c1 * 16) = quantize_chunk(v1, scale, inv_scale);
+        if (nr != nullptr) store16(nr + c1 * 16, v1);
+      }
+    } else {
+      for (int c = threadIdx.x; c < chunks; c += 256) {
+        float v[16];
+        load16(xr + c * 16, v);
+        normalise16(v, weight + c * 16, r);
+        *reinterpret_cast<uint4*>(qr + c * 16) = quantize_chunk(v, scale, inv_scale);
+        if (nr != nullptr) store16(nr + c * 16, v);
       }
     }
     __syncthreads();
@@ -307,7 +467,40 @@ int launch_typed(const void* x, int64_t m, int64_t k, const int32_t* v_metadata,
   return check_cuda(status, "activation quantizer launch");
 }
 
+template <typename T>
+int launch_rmsnorm_typed(const void* x, const void* weight, float eps, int64_t m, int64_t k, int8_t* q, float* scales,
+                         void* normed, cudaStream_t stream) {
+  cudaLaunchConfig_t config = {};
+  config.blockDim = dim3(256, 1, 1);
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = use_dependent_launch() ? 1 : 0;
+  const int64_t grid = m < 148 * 16 ? m : 148 * 16;
+  config.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  return check_cuda(cudaLaunchKernelEx(&config, rmsnorm_quantize_kernel<T>, static_cast<const T*>(x),
+                                       static_cast<const T*>(weight), eps, q, scales, static_cast<T*>(normed), m,
+                                       static_cast<int>(k)),
+                    "rmsnorm + quantizer launch");
+}
+
 }  // namespace
+
+int launch_rmsnorm_quantize(const void* x, int x_dtype, int64_t m, int64_t k, const void* weight, float eps, int8_t* q,
+                            float* scales, void* normed, cudaStream_t stream) {
+  switch (x_dtype) {
+    case AQ_F16:
+      return launch_rmsnorm_typed<__half>(x, weight, eps, m, k, q, scales, normed, stream);
+    case AQ_BF16:
+      return launch_rmsnorm_typed<__nv_bfloat16>(x, weight, eps, m, k, q, scales, normed, stream);
+    case AQ_F32:
+      return launch_rmsnorm_typed<float>(x, weight, eps, m, k, q, scales, normed, stream);
+    default:
+      return fail(AQ_ERR_INVALID, "x_dtype must be AQ_F16, AQ_BF16 or AQ_F32, got %d", x_dtype);
+  }
+}
 
 int launch_quantize(const void* x, int x_dtype, int64_t m, int64_t k, const int32_t* v_metadata,
                     int scale_mode, int8_t* q, float* scales, cudaStream_t stream) {

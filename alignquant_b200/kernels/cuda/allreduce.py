@@ -1,8 +1,8 @@
 """Peer-memory all-reduce for the partial outputs of row-parallel projections.
 
-Replaces ``dist.all_reduce`` after o_proj / down_proj (reference:
-``alignquant/quantization/model.py:352-356``) for the small FP32 messages of decode.  One
-process per GPU; the exchange buffers are torch symmetric-memory allocations, so every rank
+Stands in for the ``dist.all_reduce`` that tensor parallelism needs after o_proj / down_proj, for
+the small FP32 messages of decode.  The reference has no counterpart: it runs on one GPU and
+contains no collective.  One process per GPU; the exchange buffers are torch symmetric-memory allocations, so every rank
 can store into every other rank's buffer over NVLink.  The kernel itself is
 ``aq_allreduce_f32`` of the C library (plain peer stores of values tagged with the call
 number, bounded polls of the local receive area).

@@ -125,6 +125,49 @@ def alignquant_activation_quantize_cuda(
     return q, scales
 
 
+def alignquant_rmsnorm_quantize_cuda(
+    activation: torch.Tensor,
+    weight: torch.Tensor,
+    eps: float,
+    *,
+    out: tuple[torch.Tensor, torch.Tensor] | None = None,
+    normed: torch.Tensor | None = None,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """RMSNorm (Llama / Qwen3 module arithmetic) + per-token int8 quantizer in one kernel.
+
+    ``activation`` [M, K] and ``weight`` [K] share one dtype (fp16 / bf16 / fp32).  Returns
+    ``(int8 [M, K], float32 scales [M])``, what ``alignquant_activation_quantize_cuda(norm(x),
+    None, scale_mode="token")`` returns; ``normed`` (same dtype, [M, K]) optionally receives the
+    normalised activations as well.
+    """
+    _require_cuda(activation, "x")
+    if activation.dtype not in _DTYPE_CODES or weight.dtype != activation.dtype:
+        raise RuntimeError("x and weight must share one dtype: bf16, fp16, or fp32")
+    if activation.dim() != 2 or activation.size(0) < 1:
+        raise RuntimeError("x must be [M,K] with positive M")
+    x, w = activation.contiguous(), weight.contiguous()
+    m, k = int(x.size(0)), int(x.size(1))
+    if k % 64 or tuple(w.shape) != (k,) or w.device != x.device:
+        raise RuntimeError("K must be a multiple of 64 and weight must be [K] on x's device")
+    with torch.cuda.device(x.device):
+        if out is not None:
+            q, scales = out
+            if (q.dtype != torch.int8 or tuple(q.shape) != (m, k) or not q.is_contiguous() or scales.dtype != torch.float32
+                    or tuple(scales.shape) != (m,) or not scales.is_contiguous()):
+                raise RuntimeError("out must be (contiguous int8 [M,K], contiguous float32 [M])")
+        else:
+            q = torch.empty((m, k), dtype=torch.int8, device=x.device)
+            scales = torch.empty((m,), dtype=torch.float32, device=x.device)
+        if normed is not None and (normed.dtype != x.dtype or tuple(normed.shape) != (m, k) or not normed.is_contiguous()):
+            raise RuntimeError("normed must be a contiguous [M,K] tensor of x's dtype")
+        _lib.check(
+            _lib.load().aq_rmsnorm_quantize(
+                _ptr(x), _DTYPE_CODES[x.dtype], m, k, _ptr(w), float(eps), _ptr(q), _ptr(scales), _ptr(normed), _stream(x.device)
+            )
+        )
+    return q, scales
+
+
 @dataclass
 class PreparedWeights:
     """A layer's weights re-laid-out once for the B200 kernels (see ``aq_repack``)."""
@@ -502,6 +545,12 @@ def set_gemm_tile(name: str = "auto") -> None:
     _lib.check(_lib.load().aq_set_option(_lib.AQ_OPT_GEMM_TILE, _lib.GEMM_TILES[str(name)]))
 
 
+def set_decode_kernel(cluster_only: bool = False) -> None:
+    """``True``: never use the register-staged decode kernel (``AQ_OPT_DECODE_KERNEL``)."""
+    _lib.check(_lib.load().aq_set_option(
+        _lib.AQ_OPT_DECODE_KERNEL, _lib.AQ_DECODE_KERNEL_CLUSTER if cluster_only else _lib.AQ_DECODE_KERNEL_AUTO))
+
+
 def set_gemm_split(split: int = 0) -> None:
     """Force the number of K ranges of the GEMM, 0 = automatic (``AQ_OPT_GEMM_SPLIT``)."""
     _lib.check(_lib.load().aq_set_option(_lib.AQ_OPT_GEMM_SPLIT, int(split)))
@@ -541,6 +590,7 @@ def linear_plan(m: int, n_j: int, n_k: int, *, schedule: str = "auto", decode_sp
 __all__ = [
     "load_extension",
     "alignquant_activation_quantize_cuda",
+    "alignquant_rmsnorm_quantize_cuda",
     "alignquant_linear_cuda",
     "alignquant_linear_prepared",
     "alignquant_linear_decode_static",
@@ -554,4 +604,5 @@ __all__ = [
     "set_gemm_tile",
     "measure_int8_peak",
     "set_gemm_split",
+    "set_decode_kernel",
 ]

@@ -40,6 +40,7 @@ def main() -> None:
     ap.add_argument("--gemm-tile", choices=("auto", "paired", "narrow", "wide"), default="auto", help="CTA tile of the GEMM")
     ap.add_argument("--gemm-separate-rounding", action="store_true",
                     help="GEMM adds a tile with a separately rounded multiply and add (the reference kernels' order)")
+    ap.add_argument("--cluster-decode", action="store_true", help="keep the register-staged decode kernel off")
     ap.add_argument("--lookahead", action="store_true",
                     help="with --layers: every projection names the next layer's weights as its L2 look-ahead")
     args = ap.parse_args()
@@ -50,6 +51,7 @@ def main() -> None:
     ext.load_extension()
     ext.set_gemm_tile(args.gemm_tile)
     ext.set_gemm_rounding(args.gemm_separate_rounding)
+    ext.set_decode_kernel(cluster_only=args.cluster_decode)
     device = torch.device("cuda", 0)
     row_counts = [int(v) for v in str(args.rows).split(",")]
     if args.layers > 1:

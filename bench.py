@@ -77,6 +77,8 @@ def parse_args():
                     help="comma-separated legs besides the decode sweep: prefill, generation")
     ap.add_argument("--gen-tokens", type=int, default=32, help="generated tokens of the generation leg")
     ap.add_argument("--no-lookahead", action="store_true", help="run the sweep without the L2 look-ahead")
+    ap.add_argument("--cluster-decode", action="store_true",
+                    help="keep the register-staged decode kernel off (AQ_DECODE_KERNEL_CLUSTER), for comparison")
     return ap.parse_args()
 
 
@@ -311,6 +313,7 @@ def run_native(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     ext.load_extension()
+    ext.set_decode_kernel(cluster_only=args.cluster_decode)
     reducer = None
     if world > 1 and os.environ.get("ALIGNQUANT_B200_ALLREDUCE", "peer") == "peer":
         from alignquant_b200.kernels.cuda.allreduce import PeerAllReduce
@@ -610,7 +613,8 @@ def run_native(args) -> None:
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "launch": e2e_mode},
         "gpu_launches": (2 * pairs_per_step + own_sum_launches) * args.steps,
         "roofline": {
-            "kernel": "cluster_decode_kernel (packed W4/W8 GEMV, M<=16)", "bound": "hbm",
+            "kernel": ("cluster_decode_kernel" if args.cluster_decode else "direct_decode_kernel") + " (packed W4/W8 GEMV, M<=16)",
+            "bound": "hbm",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "peak_source": f"{peak_source} HBM copy bandwidth", "traffic": traffic,
             "bytes_per_launch": linear_bytes / pairs_per_step, "us_per_launch": kernel_seconds * 1e6,

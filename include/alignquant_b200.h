@@ -74,12 +74,18 @@ AQ_API int aq_version(void);
  *                           bit-identical across the three.
  *   AQ_OPT_GEMM_SPLIT       number of K ranges of the GEMM (1..8), 0 = automatic (default); changes
  *                           the FP32 summation order as aq_linear_plan reports.
+ *   AQ_OPT_DECODE_KERNEL    AQ_DECODE_KERNEL_AUTO (default), or AQ_DECODE_KERNEL_CLUSTER: never use
+ *                           the register-staged decode kernel (for tests and measurements; changes
+ *                           the FP32 summation order as aq_linear_plan reports).
  * aq_set_option returns AQ_OK or AQ_ERR_INVALID; aq_get_option the value or AQ_ERR_INVALID.
  */
 #define AQ_OPT_PEER_POLL_LIMIT 1
 #define AQ_OPT_GEMM_ROUNDING 2
 #define AQ_OPT_GEMM_TILE 3
 #define AQ_OPT_GEMM_SPLIT 4
+#define AQ_OPT_DECODE_KERNEL 5
+#define AQ_DECODE_KERNEL_AUTO 0
+#define AQ_DECODE_KERNEL_CLUSTER 1
 #define AQ_GEMM_ROUNDING_FUSED 0
 #define AQ_GEMM_ROUNDING_SEPARATE 1
 #define AQ_GEMM_TILE_AUTO 0
@@ -111,6 +117,22 @@ AQ_API const char* aq_last_error(void);
 AQ_API int aq_quantize_act(const void* x, int x_dtype, int64_t m, int64_t k,
                     const int32_t* v_metadata, int scale_mode,
                     int8_t* q, float* scales, void* stream);
+
+/*
+ * RMSNorm followed by the per-token activation quantizer (AQ_SCALE_TOKEN) in one kernel, for the
+ * two places of a decoder layer where a norm feeds quantized projections (qkv, gate/up).  It
+ * replaces the normalisation module plus the quantizer call the reference makes per group
+ * (alignquant/quantization/model.py:329-331) and saves a launch and a pass over the activations.
+ *   x, weight   x_dtype (AQ_F16 / AQ_BF16 / AQ_F32): x[m][k] row-major, weight[k]
+ *   arithmetic  r = float(1 / sqrt(sum(x^2)/k + eps)) with sum, division and root in FP64;
+ *               n = round(x * r) to x_dtype; y = round(weight * n) to x_dtype (the Llama / Qwen3
+ *               RMSNorm module); scales[row] = max(absmax(y)/127, 1e-12); q = rint(y/scale) in
+ *               IEEE float32, clamp [-127, 127]
+ *   normed      NULL, or x_dtype [m][k]: also receives y (for consumers other than the projections)
+ *   Requirements: m >= 1, k % 64 == 0, pointers 16-byte aligned.
+ */
+AQ_API int aq_rmsnorm_quantize(const void* x, int x_dtype, int64_t m, int64_t k, const void* weight,
+                        float eps, int8_t* q, float* scales, void* normed, void* stream);
 
 /*
  * Size in bytes of the prepared weight image of a layer with n_j x n_k tiles of
@@ -178,12 +200,13 @@ AQ_API int aq_linear(const int8_t* xq, const float* act_scales, int scale_mode, 
               void* workspace, int64_t workspace_bytes, int32_t* acc_dump, void* stream);
 
 /*
- * aq_linear with a look-ahead: while this projection runs, the decode kernels (aq_linear_plan
- * kernels 2 and 3; other kernels ignore the hint) ask the L2 cache to fetch next_bytes bytes at
- * next_prepared -- normally the prepared image of the projection that the caller runs next
- * (aq_prepared_bytes long).  A decode-size projection is a few microseconds of HBM traffic, less
- * than a kernel's start-up and split-K hand-over; with the look-ahead HBM keeps streaming
- * through those phases and the next kernel finds its weights on chip.  The range must lie in
+ * aq_linear with a look-ahead: while this projection runs, the decode kernels whose own traffic
+ * leaves HBM idle (the many-small-CTA kernel of layers with few tile rows and the stream-K kernel;
+ * the others ignore the hint) ask the L2 cache to fetch next_bytes bytes at next_prepared --
+ * normally the prepared image of the projection that the caller runs next (aq_prepared_bytes
+ * long).  A decode-size projection is a few microseconds of HBM traffic, less than a kernel's
+ * chain of latencies; with the look-ahead HBM keeps streaming through them and the next kernel
+ * finds its weights on chip.  The range must lie in
  * this GPU's own memory, be 16-byte aligned and a multiple of 16 bytes long; it is only read.
  * next_prepared == NULL or next_bytes == 0: exactly aq_linear.  The reference has no
  * counterpart (its decode kernels read weights straight from HBM,
@@ -236,8 +259,10 @@ AQ_API int aq_linear_decode_static(const int8_t* xq, const float* act_scales, in
  *            2  persistent stream-K kernel: the (j, k)-ordered tile sequence cut into
  *               *splits contiguous ranges [i*T/splits, (i+1)*T/splits); inside a range
  *               tile t goes to accumulator (t - range begin) % *workers
- *            3  warp-per-tile cluster kernel: ranges as for 0; inside a range tile k
- *               goes to accumulator (k - range begin) % *workers
+ *            3  warp-per-tile decode kernels: ranges as for 0; inside a range tile k
+ *               goes to accumulator (k - range begin) % *workers.  Layers with at least as many
+ *               groups of 16 output columns as the GPU has SMs run without a K split
+ *               (*splits == 1, register-staged kernel), narrower ones split K over a cluster
  *   In 2 and 3 every accumulator adds its tiles in increasing k, the accumulators of a
  *   range (row segment) are added in index order, and the range sums in range order.
  * The reference's counterpart is its split-K heuristic (linear.cu:1679-1691).

@@ -117,7 +117,9 @@ def _check(ext, n: int, k: int, m: int, act_dtype: torch.dtype, out_dtype: torch
         low = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token", output_dtype=out_dtype)
         ext.device_status()
         assert torch.equal(low.cpu(), torch.from_numpy(want).to(out_dtype)), "low-precision result is not the rounded fp32 result"
-        assert np.allclose(low[torch.from_numpy(rows).cuda()].float().cpu().numpy(), y64, rtol=REL, atol=ABS)
+        # fp16 keeps the rel 1e-3 / abs 1e-2 contract; bf16 has 8 bits of mantissa (2^-9 per rounding)
+        rel = REL if out_dtype == torch.float16 else 1e-2
+        assert np.allclose(low[torch.from_numpy(rows).cuda()].float().cpu().numpy(), y64, rtol=rel, atol=ABS)
 
 
 def test_config0_single_linear_m16_k3072_n8192(ext):

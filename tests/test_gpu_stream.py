@@ -74,6 +74,34 @@ def test_token_quantizer_rounding_boundaries(ext, k):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,k", [(1, 64), (5, 2560), (8, 5120), (32, 3072), (3, 8192), (2, 16384)])
+def test_rmsnorm_quantizer_bit_exact(ext, m, k, dtype):
+    """Fused RMSNorm + per-token quantizer against the oracle's restatement of the decoder's norm
+    module followed by the token quantizer: int8 codes, scales and the normalised values."""
+    name = "bfloat16" if dtype == torch.bfloat16 else (np.float16 if dtype == torch.float16 else np.float32)
+    rng = np.random.default_rng(m * 13 + k)
+    x = oc.round_to_dtype(oc.synthetic_activation(m, k, seed=m + k, dtype=np.float32) * np.float32(0.37), name)
+    w = oc.round_to_dtype(1.0 + 0.1 * rng.standard_normal(k, dtype=np.float32), name)
+    if m > 2:
+        x[2] = 0.0  # all-zero row: the norm returns zeros and the scale takes its floor
+    eps = 1e-6
+    xt, wt = torch.from_numpy(x).cuda().to(dtype), torch.from_numpy(w).cuda().to(dtype)
+    normed = torch.empty_like(xt)
+    q, s = ext.alignquant_rmsnorm_quantize_cuda(xt, wt, eps, normed=normed)
+    q_ref, s_ref, y_ref = oc.rmsnorm_token_quantize(x, w, eps, name)
+    assert np.array_equal(normed.float().cpu().numpy(), y_ref)
+    assert np.array_equal(s.cpu().numpy(), s_ref)
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+    # the same codes as the two-step path on the module's output
+    q2, s2 = ext.alignquant_activation_quantize_cuda(normed, None, scale_mode="token")
+    assert torch.equal(q2, q) and torch.equal(s2, s)
+    if dtype != torch.float32:  # and the module arithmetic is torch's own
+        xf = xt.float()
+        n = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(dtype)
+        assert float((wt * n - normed).abs().max()) <= float(normed.abs().max()) * 2.0 ** -7
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("m,k", [(1, 64), (4, 192), (16, 3072), (17, 128), (130, 256)])
 def test_tile_quantizer_bit_exact_identity(ext, m, k, dtype):
     x = oc.synthetic_activation(m, k, seed=m * 11 + k, dtype="bfloat16" if dtype == torch.bfloat16 else np.float16)
