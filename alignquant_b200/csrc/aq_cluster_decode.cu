@@ -1,18 +1,25 @@
 // Decode kernel for at most 32 rows: one CTA per (tile row j, K split), split-K partial
 // sums exchanged through the distributed shared memory of a thread-block cluster.
 //
-// This is the default small-M kernel.  It combines the two things that matter at decode
-// sizes, where a whole layer is a few microseconds of HBM traffic:
+// This is the small-M kernel of the layers that do not fit a CTA's shared memory at once.  It
+// combines the two things that matter at decode sizes, where a whole layer is a few
+// microseconds of HBM traffic:
 //   * a byte stream that starts immediately and never stalls -- the tiles of one
-//     (row, K range) are contiguous in the prepared image, so the producer warp moves
-//     them with ONE bulk asynchronous copy per ring slot of eight tiles (up to 32 KiB,
-//     counted on the slot's mbarrier); the first two slots are requested before the grid
-//     dependency is resolved, so under programmatic dependent launch they overlap the
-//     preceding kernel;
-//   * tile-level parallelism -- eight consumer warps each take whole tiles (tile i of
-//     the range goes to warp i % 8; weights are the 16-row operand of
-//     mma.sync.m16n8k32.s8, up to eight activation rows the 8-column operand), so
-//     eight tiles are in progress per CTA and, with two CTAs per SM, sixteen per SM.
+//     (row, K range) are contiguous in the prepared image, so ONE bulk asynchronous copy
+//     moves the eight tiles of a ring slot (up to 32 KiB, counted on the slot's mbarrier);
+//     the first three slots are requested before the grid dependency is resolved, so under
+//     programmatic dependent launch they overlap the preceding kernel, and for the layers
+//     that are split over a cluster they are the CTA's whole K range.  There is no producer
+//     warp: the warp that is last to finish a slot's tiles (a counter in shared memory)
+//     requests the slot's next eight.  A CTA of eight warps, not nine, also lifts the
+//     compiler's register limit from 96 to 128, which the 16-row variant needs to stay
+//     free of spills;
+//   * tile-level parallelism -- the eight warps each take whole tiles (tile i of the range
+//     goes to warp i % 8; weights are the 16-row operand of mma.sync.m16n8k32.s8, up to
+//     eight activation rows the 8-column operand), so eight tiles are in progress per CTA
+//     and, with two CTAs per SM, sixteen per SM.  What a warp needs to know of its tiles
+//     (place in the slot, W4 flag, scale) sits in one register per lane and reaches the
+//     loop by shuffle; W4 and W8 tiles take separate, branch-free instruction sequences.
 // The split count is chosen so that rows x splits is at most two CTAs per SM; all CTAs
 // are then co-resident and stream concurrently.
 //
@@ -67,43 +74,85 @@ __device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
 }
 
 constexpr int kGroupTiles = 8;  // tiles per ring slot
-constexpr int kSlots = 2;
+constexpr int kSlots = 3;
 constexpr int kSlotBytes = kGroupTiles * kW8TileBytes;
 constexpr int kTileWorkers = 8;  // tiles in progress per CTA; WPT warps share one tile (16 rows each)
 constexpr int kMaxCount = 512;  // tiles of one CTA's K range
-constexpr int kNumBars = 2 * kSlots;
+constexpr int kNumBars = kSlots;  // one "slot filled" barrier per ring slot
 
-template <int kConsumerThreads>
-__device__ __forceinline__ void consumer_sync() {
-  asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+// Counts a warp's arrival on a ring slot; release for the warp's reads of the slot, acquire for the
+// one that sees the last arrival and refills it.
+__device__ __forceinline__ uint32_t slot_arrive(uint32_t counter) {
+  uint32_t before;
+  asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(before) : "r"(counter) : "memory");
+  return before;
 }
 
-// Shared memory: [ring kSlots x 32 KiB][slabs 8 x (8*NT) x 64 f32][tile (8*NT) x 64 f32]
-//                [records kMaxCount][barriers][abort flag]
-// With 16 rows (NT = 2) the slabs reuse the ring's memory once the last tile has been
-// consumed (measured 4-5 % faster at M = 16: more shared memory left for the L1); with up to
-// 8 rows the extra barrier that this needs costs more than it gives, so the slabs keep their
-// own 16 KiB.
+// d = a * b (a fresh integer sum: the accumulator input is the constant zero)
+__device__ __forceinline__ void mma_s8_fresh(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// The integer products of the column groups Q0 .. Q0 + QN - 1 of one staged tile with NT groups of
+// eight activation rows.  `lane_base`
+// is the tile's address plus this lane's offset inside a block of eight columns; the blocks of the
+// four column groups and their two halves follow at fixed strides, so every read is base +
+// constant.  One instantiation per tile kind: the W8 one has no selects and no shifts.
+template <bool kW4, int NT, int Q0, int QN>
+__device__ __forceinline__ void tile_products(const uint8_t* lane_base, int w4_shift, const uint4 (&x)[NT], int (&d)[NT][QN][4]) {
+  constexpr int kHalf = kW4 ? 8 * 32 : 8 * 64;  // columns g + 8
+#pragma unroll
+  for (int q = 0; q < QN; ++q) {
+    uint4 wa = *reinterpret_cast<const uint4*>(lane_base + (Q0 + q) * 2 * kHalf);
+    uint4 wb = *reinterpret_cast<const uint4*>(lane_base + (Q0 + q) * 2 * kHalf + kHalf);
+    if (kW4) {
+      wa.x = (wa.x << w4_shift) & 0xf0f0f0f0u;
+      wa.y = (wa.y << w4_shift) & 0xf0f0f0f0u;
+      wa.z = (wa.z << w4_shift) & 0xf0f0f0f0u;
+      wa.w = (wa.w << w4_shift) & 0xf0f0f0f0u;
+      wb.x = (wb.x << w4_shift) & 0xf0f0f0f0u;
+      wb.y = (wb.y << w4_shift) & 0xf0f0f0f0u;
+      wb.z = (wb.z << w4_shift) & 0xf0f0f0f0u;
+      wb.w = (wb.w << w4_shift) & 0xf0f0f0f0u;
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      mma_s8_fresh(d[nt][q], wa.x, wb.x, wa.y, wb.y, x[nt].x, x[nt].y);
+      mma_s8(d[nt][q], wa.z, wb.z, wa.w, wb.w, x[nt].z, x[nt].w);
+    }
+  }
+}
+
+// Shared memory: [ring kSlots x 32 KiB][received sums (8*NT*WPT + 7) x 64 f32][records kMaxCount][barriers]
+//                [slot counters][abort flag]
+// The eight warp sums ("slabs", 8 x rows x 64 f32) reuse the ring's memory once every warp has
+// consumed its last tile, so that the ring can be three slots deep with two CTAs per SM: a CTA's
+// first request is then up to 24 tiles, which covers the whole K range of the layers that are
+// split over a cluster.
 // For 17..32 rows two warps share every tile (WPT = 2): warp 2t takes rows 0..15 and warp
 // 2t+1 rows 16..31 of tile worker t, so the weights are still streamed once.
 // kTp: the epilogue also sums over the tensor-parallel ranks (a separate instantiation, so that
 // the single-GPU kernel keeps its register count).
 template <int NT, int WPT, bool kTp>
-__global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 1) cluster_decode_kernel(const Params p) {
+__global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) cluster_decode_kernel(const Params p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int kConsumerWarps = kTileWorkers * WPT;
-  constexpr int kConsumerThreads = kConsumerWarps * 32;
-  constexpr int kThreads = kConsumerThreads + 32;
+  constexpr int kWarps = kTileWorkers * WPT;
+  constexpr int kThreads = kWarps * 32;
   constexpr int kWarpRows = 8 * NT;      // rows one warp accumulates
   constexpr int kRows = kWarpRows * WPT;  // rows of the CTA
-  constexpr bool kSlabsInRing = NT == 2;
+  constexpr int kReceivedRows = kRows + 7;  // split x ceil(rows / split) <= rows + split - 1, split <= 8
   static_assert(kTileWorkers * kRows * kTile * 4 <= kSlots * kSlotBytes, "slabs must fit into the ring");
   uint8_t* ring = smem;
-  float* slabs = reinterpret_cast<float*>(smem + (kSlabsInRing ? 0 : kSlots * kSlotBytes));
-  float* tile = reinterpret_cast<float*>(smem + kSlots * kSlotBytes) + (kSlabsInRing ? 0 : kTileWorkers * kRows * kTile);
-  TileRecord* recs = reinterpret_cast<TileRecord*>(tile + kRows * kTile);
+  float* slabs = reinterpret_cast<float*>(smem);
+  float* received = reinterpret_cast<float*>(smem + kSlots * kSlotBytes);  // [source CTA][owned row][64]
+  TileRecord* recs = reinterpret_cast<TileRecord*>(received + kReceivedRows * kTile);
   uint64_t* bars = reinterpret_cast<uint64_t*>(recs + kMaxCount);
-  volatile uint32_t* abort_flag = reinterpret_cast<uint32_t*>(bars + kNumBars);
+  uint32_t* consumed = reinterpret_cast<uint32_t*>(bars + kNumBars);  // warps that are done with the slot's current tiles
+  volatile uint32_t* abort_flag = consumed + kSlots;
 
   cg::cluster_group cluster = cg::this_cluster();
   const int split_k = static_cast<int>(cluster.num_blocks());
@@ -119,16 +168,16 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
   const int count = k_end - k_begin;
   const int groups = (count + kGroupTiles - 1) / kGroupTiles;
   const int rows = p.m < kRows ? static_cast<int>(p.m) : kRows;
+  const int owned_rows = (rows + split_k - 1) / split_k;  // rows a CTA of the cluster finishes, at most
 
   const uint32_t bar0 = smem_u32(bars);
   auto full = [&](int s) { return bar0 + 8u * s; };
-  auto empty = [&](int s) { return bar0 + 8u * (kSlots + s); };
   const uint32_t ring_addr = smem_u32(ring);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(full(s), 1);
-      mbar_init(empty(s), kGroupTiles * WPT);  // every warp working on a tile arrives
+      consumed[s] = 0;
     }
     *abort_flag = 0;
     mbar_init_fence();
@@ -137,10 +186,9 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
   __syncthreads();
 
   const TileRecord* my_records = p.records + static_cast<int64_t>(j) * n_k + k_begin;
-  const bool producer = warp == kConsumerWarps;  // the last warp
 
   // First ring fill before the grid dependency is resolved: weights are static.
-  if (producer && lane < kSlots && lane < groups) {
+  if (warp == 0 && lane < kSlots && lane < groups) {
     const int first = lane * kGroupTiles;
     const int last = (first + kGroupTiles < count ? first + kGroupTiles : count) - 1;
     const TileRecord rf = my_records[first];
@@ -149,7 +197,41 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
     bulk_copy(ring_addr + lane * kSlotBytes,
               p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(lane));
   }
-  for (int i = threadIdx.x; i < count; i += kThreads) recs[i] = my_records[i];
+  if (groups > kSlots) {  // only the later fills read the records from shared memory
+    for (int i = threadIdx.x; i < count; i += kThreads) recs[i] = my_records[i];
+  }
+  // A tile worker takes tile t of the CTA's range from every group of eight: tile worker + 8 t,
+  // which lies in ring slot t % kSlots.  Lane l keeps what the loop needs of the warp's tile l
+  // (of tile 32 b + l in the b-th block of 32): its byte offset inside the slot, the W4 flag and
+  // the scale, so that the loop gets them with two shuffles instead of shared-memory reads and
+  // address arithmetic.  All of this, and every kernel parameter the loop uses, is read here,
+  // before the dependency: afterwards each first read would be a round trip of its own.
+  const int my_tiles = worker < count ? (count - worker + kTileWorkers - 1) / kTileWorkers : 0;
+  uint32_t lane_off = 0;
+  float lane_scale = 0.0f;
+  auto load_lane_records = [&](int t0) {
+    lane_off = 0;
+    lane_scale = 0.0f;
+    const int t = t0 + lane;
+    if (t < my_tiles) {
+      const TileRecord r = my_records[worker + kTileWorkers * t];
+      const TileRecord r0 = my_records[kGroupTiles * t];  // first tile of the group, which starts the slot
+      lane_off = (((r.offset_flag & ~kW4Flag) - (r0.offset_flag & ~kW4Flag)) * kW4TileBytes) | (r.offset_flag & kW4Flag);
+      lane_scale = r.scale;
+    }
+  };
+  load_lane_records(0);
+  const int g = lane >> 2;
+  const int c = lane & 3;
+  const bool token_mode = p.scale_mode == AQ_SCALE_TOKEN;
+  const float* const scale_global = p.act_scales;
+  int32_t* const dump_global = p.acc_dump;
+  const int64_t k_bytes = static_cast<int64_t>(n_k) * kTile;
+  const int8_t* x_lane[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    x_lane[nt] = p.xq + static_cast<int64_t>(row0 + nt * 8 + g) * k_bytes + static_cast<int64_t>(k_begin + worker) * kTile + c * 16;
+  }
   grid_launch_dependents();
   grid_dependency_wait();  // activations and their scales come from the preceding kernel
   __shared__ uint32_t ar_epoch_shared;
@@ -158,46 +240,29 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
   }
   __syncthreads();
 
-  if (producer) {
-    if (lane == 0) {
-      for (int gi = kSlots; gi < groups; ++gi) {
-        const int slot = gi % kSlots;
-        if (!mbar_wait(empty(slot), ((gi / kSlots) - 1) & 1, abort_flag, &g_cluster_decode_status, 31)) break;
-        const int first = gi * kGroupTiles;
-        const int last = (first + kGroupTiles < count ? first + kGroupTiles : count) - 1;
-        const TileRecord rf = recs[first];
-        const uint32_t bytes = span_bytes(rf, recs[last]);
-        mbar_expect_tx(full(slot), bytes);
-        bulk_copy(ring_addr + slot * kSlotBytes,
-                  p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(slot));
-      }
-    }
-    __syncwarp();
-  } else {
+  {
     // Lane (g, c) = (lane/4, lane%4) holds, for column group q = 0..3, the weight vectors
     // of columns 16q+g and 16q+g+8 and the activation vector of token 8*pass+g, all for
     // k in [16c, 16c+16).  MMA results: d[0], d[1] = column 16q+g, tokens 8*pass+2c, +1;
     // d[2], d[3] = column 16q+g+8, same tokens.
-    const int g = lane >> 2;
-    const int c = lane & 3;
-    const int64_t k_bytes = static_cast<int64_t>(n_k) * kTile;
     const uint32_t w8_off = static_cast<uint32_t>(g * 64 + ((c ^ ((g >> 1) & 3)) << 4));
     const uint32_t w4_off = static_cast<uint32_t>(g * 32 + (c >> 1) * 16);
     const int w4_shift = (c & 1) ? 0 : 4;
     float token_scale[NT][2];
-    const int8_t* x_lane[NT];
+    bool x_row[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int tok = row0 + nt * 8 + 2 * c;
-      token_scale[nt][0] = (p.scale_mode == AQ_SCALE_TOKEN && tok < rows) ? p.act_scales[tok] : 0.0f;
-      token_scale[nt][1] = (p.scale_mode == AQ_SCALE_TOKEN && tok + 1 < rows) ? p.act_scales[tok + 1] : 0.0f;
-      x_lane[nt] = p.xq + static_cast<int64_t>(row0 + nt * 8 + g) * k_bytes + static_cast<int64_t>(k_begin) * kTile + c * 16;
+      token_scale[nt][0] = (token_mode && tok < rows) ? scale_global[tok] : 0.0f;
+      token_scale[nt][1] = (token_mode && tok + 1 < rows) ? scale_global[tok + 1] : 0.0f;
+      x_row[nt] = row0 + nt * 8 + g < rows;
     }
-    auto load_x = [&](int i, uint4 (&x)[NT]) {
+    auto load_x = [&](uint4 (&x)[NT]) {  // the activation vectors of the warp's next tile
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         x[nt] = make_uint4(0, 0, 0, 0);
-        if (row0 + nt * 8 + g < rows) x[nt] = ldg_x(x_lane[nt] + static_cast<int64_t>(i) * kTile);
+        if (x_row[nt]) x[nt] = ldg_x(x_lane[nt]);
+        x_lane[nt] += kTileWorkers * kTile;
       }
     };
 
@@ -211,74 +276,94 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
       }
     }
     uint4 x_next[NT];
-    if (worker < count) load_x(worker, x_next);  // activation vectors are requested one tile ahead
-    for (int i = worker; i < count; i += kTileWorkers) {
-      const int gi = i / kGroupTiles;
-      const int slot = gi % kSlots;
-      const int kt = k_begin + i;
+    if (my_tiles > 0) load_x(x_next);  // activation vectors are requested one tile ahead
+    int slot = 0;
+    uint32_t parity = 0;
+    for (int t = 0; t < my_tiles; ++t) {
+      if (t != 0 && (t & 31) == 0) load_lane_records(t);  // very long K ranges: the next block of records
       uint4 x[NT];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) x[nt] = x_next[nt];
-      if (i + kTileWorkers < count) load_x(i + kTileWorkers, x_next);
-      if (!mbar_wait(full(slot), (gi / kSlots) & 1, abort_flag, &g_cluster_decode_status, 32)) break;
-      const TileRecord rec = recs[i];
-      const TileRecord rec0 = recs[gi * kGroupTiles];
-      const bool is_w4 = (rec.offset_flag & kW4Flag) != 0;
-      const uint8_t* staged = ring + slot * kSlotBytes +
-                              ((rec.offset_flag & ~kW4Flag) - (rec0.offset_flag & ~kW4Flag)) * kW4TileBytes;
-      int d[NT][4][4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const uint8_t* group = staged + q * (is_w4 ? 16 * 32 : 16 * 64);
-        const uint4 wa = weight_vector(group, is_w4, w8_off, w4_off, w4_shift);
-        const uint4 wb = weight_vector(group + (is_w4 ? 8 * 32 : 8 * 64), is_w4, w8_off, w4_off, w4_shift);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          d[nt][q][0] = d[nt][q][1] = d[nt][q][2] = d[nt][q][3] = 0;
-          mma_s8(d[nt][q], wa.x, wb.x, wa.y, wb.y, x[nt].x, x[nt].y);
-          mma_s8(d[nt][q], wa.z, wb.z, wa.w, wb.w, x[nt].z, x[nt].w);
-        }
-      }
-      // every lane's operands have been consumed by the warp-wide MMAs: this tile is done
-      __syncwarp();
-      if (lane == 0 && gi + kSlots < groups) mbar_arrive(empty(slot));
+      if (t + 1 < my_tiles) load_x(x_next);
+      // the same decision in all lanes: the shuffles below need the whole warp
+      if (!__all_sync(0xffffffffu, mbar_wait(full(slot), parity, abort_flag, &g_cluster_decode_status, 32))) break;
+      const uint32_t of = __shfl_sync(0xffffffffu, lane_off, t & 31);
+      const float w_s = __shfl_sync(0xffffffffu, lane_scale, t & 31);
+      const bool is_w4 = (of & kW4Flag) != 0;
+      const uint8_t* staged = ring + slot * kSlotBytes + (of & ~kW4Flag);
+      const int kt = k_begin + worker + kTileWorkers * t;
+      float s0[NT], s1[NT];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        float s0, s1;
-        if (p.scale_mode == AQ_SCALE_TOKEN) {
-          s0 = __fmul_rn(token_scale[nt][0], rec.scale);
-          s1 = __fmul_rn(token_scale[nt][1], rec.scale);
+        if (token_mode) {
+          s0[nt] = __fmul_rn(token_scale[nt][0], w_s);
+          s1[nt] = __fmul_rn(token_scale[nt][1], w_s);
         } else {
           // tokens 8*nt .. 8*nt+7 share the scale of their 16-row group
-          const float a_s = (row0 + nt * 8 < rows) ? p.act_scales[static_cast<int64_t>((row0 + nt * 8) >> 4) * n_k + kt] : 0.0f;
-          s0 = s1 = __fmul_rn(a_s, rec.scale);
+          const float a_s = (row0 + nt * 8 < rows) ? scale_global[static_cast<int64_t>((row0 + nt * 8) >> 4) * n_k + kt] : 0.0f;
+          s0[nt] = s1[nt] = __fmul_rn(a_s, w_s);
+        }
+      }
+      // Sixteen rows: two column groups at a time, so that only half of the integer sums are live.
+      constexpr int QN = NT == 1 ? 4 : 2;
+#pragma unroll
+      for (int q0 = 0; q0 < 4; q0 += QN) {
+        int d[NT][QN][4];
+        if (is_w4) {
+          if (q0 == 0) tile_products<true, NT, 0, QN>(staged + w4_off, w4_shift, x, d);
+          else tile_products<true, NT, 4 - QN, QN>(staged + w4_off, w4_shift, x, d);
+        } else {
+          if (q0 == 0) tile_products<false, NT, 0, QN>(staged + w8_off, 0, x, d);
+          else tile_products<false, NT, 4 - QN, QN>(staged + w8_off, 0, x, d);
+        }
+        if (q0 + QN == 4) {
+          // Every lane's operands have been consumed by the warp-wide MMAs: this tile is done.  The
+          // warp that sees all others done with the group refills the slot with the group kSlots later.
+          __syncwarp();
+          if (lane == 0 && t + kSlots < groups && slot_arrive(smem_u32(consumed + slot)) == kGroupTiles * WPT - 1) {
+            consumed[slot] = 0;  // the next arrivals come after the new tiles have landed
+            const int first = (t + kSlots) * kGroupTiles;
+            const int last = (first + kGroupTiles < count ? first + kGroupTiles : count) - 1;
+            const TileRecord rf = recs[first];
+            const uint32_t bytes = span_bytes(rf, recs[last]);
+            mbar_expect_tx(full(slot), bytes);
+            bulk_copy(ring_addr + slot * kSlotBytes,
+                      p.payload + static_cast<int64_t>(rf.offset_flag & ~kW4Flag) * kW4TileBytes, bytes, full(slot));
+          }
         }
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          acc[nt][q][0] = __fadd_rn(acc[nt][q][0], __fmul_rn(static_cast<float>(d[nt][q][0]), s0));
-          acc[nt][q][1] = __fadd_rn(acc[nt][q][1], __fmul_rn(static_cast<float>(d[nt][q][1]), s1));
-          acc[nt][q][2] = __fadd_rn(acc[nt][q][2], __fmul_rn(static_cast<float>(d[nt][q][2]), s0));
-          acc[nt][q][3] = __fadd_rn(acc[nt][q][3], __fmul_rn(static_cast<float>(d[nt][q][3]), s1));
-        }
-        if (p.acc_dump != nullptr) {
-          const int shift = is_w4 ? 4 : 0;
-          const int tok = row0 + nt * 8 + 2 * c;
+        for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < QN; ++q) {
+            acc[nt][q0 + q][0] = __fadd_rn(acc[nt][q0 + q][0], __fmul_rn(static_cast<float>(d[nt][q][0]), s0[nt]));
+            acc[nt][q0 + q][1] = __fadd_rn(acc[nt][q0 + q][1], __fmul_rn(static_cast<float>(d[nt][q][1]), s1[nt]));
+            acc[nt][q0 + q][2] = __fadd_rn(acc[nt][q0 + q][2], __fmul_rn(static_cast<float>(d[nt][q][2]), s0[nt]));
+            acc[nt][q0 + q][3] = __fadd_rn(acc[nt][q0 + q][3], __fmul_rn(static_cast<float>(d[nt][q][3]), s1[nt]));
+          }
+          if (dump_global != nullptr) {
+            const int shift = is_w4 ? 4 : 0;
+            const int tok = row0 + nt * 8 + 2 * c;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int t = tok + (e & 1);
-              const int col = q * 16 + g + ((e & 2) ? 8 : 0);
-              if (t < rows) {
-                p.acc_dump[((static_cast<int64_t>(t) * p.n_j + j) * n_k + kt) * kTile + col] = d[nt][q][e] >> shift;
+            for (int q = 0; q < QN; ++q) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int tk = tok + (e & 1);
+                const int col = (q0 + q) * 16 + g + ((e & 2) ? 8 : 0);
+                if (tk < rows) {
+                  dump_global[((static_cast<int64_t>(tk) * p.n_j + j) * n_k + kt) * kTile + col] = d[nt][q][e] >> shift;
+                }
               }
             }
           }
         }
       }
+      if (++slot == kSlots) {
+        slot = 0;
+        parity ^= 1u;
+      }
     }
     // ---- combine the eight warp sums in warp order -----------------------------------------
-    if (kSlabsInRing) consumer_sync<kConsumerThreads>();  // every warp has consumed its last tile: the ring becomes the slabs
+    __syncthreads();  // every warp has consumed its last tile: the ring becomes the slabs
     float* slab = slabs + worker * kRows * kTile;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -295,35 +380,41 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
         }
       }
     }
-    consumer_sync<kConsumerThreads>();
-    for (int e = threadIdx.x; e < rows * kTile; e += kConsumerThreads) {
+    __syncthreads();
+    // The CTA's sum of row r goes straight to the CTA that finishes the row (r % split_k), into
+    // the place of this CTA's K range there: after ONE cluster barrier every CTA adds what it
+    // received, in its own shared memory, and nobody has to stay for a peer that still reads.
+    for (int e = threadIdx.x; e < rows * kTile; e += kThreads) {
       float v = slabs[e];
 #pragma unroll
       for (int w = 1; w < kTileWorkers; ++w) v = __fadd_rn(v, slabs[w * kRows * kTile + e]);
-      tile[e] = v;
+      const int row = e / kTile, col = e % kTile;
+      const int owner = row % split_k, place = row / split_k;
+      float* target = split_k > 1 ? cluster.map_shared_rank(received, owner) : received;
+      target[(split * owned_rows + place) * kTile + col] = v;
     }
   }
 
-  // ---- split-K exchange through cluster shared memory ------------------------------------
+  // ---- split-K sums: every CTA adds what the cluster sent it -------------------------------
   // A cluster barrier costs about half a microsecond even for a single CTA: without a K split
-  // (one CTA per tile row) a CTA barrier is enough, and nobody reads this CTA's tile remotely.
+  // (one CTA per tile row) a CTA barrier is enough.
   if (split_k > 1) {
     cluster.sync();
   } else {
     __syncthreads();
   }
-  if (!producer) {
+  {
     const int32_t* meta = p.u_metadata ? p.u_metadata + static_cast<int64_t>(j) * 4 * kTile : nullptr;
     const bool has_u = meta != nullptr && meta[0] != 0;
     const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
     // rank r finishes rows r, r + split_k, ...; its warps take them round robin
     if (!kTp) {
-      for (int row = split + split_k * warp; row < rows; row += split_k * kConsumerWarps) {  // all consumer warps
+      for (int row = split + split_k * warp; row < rows; row += split_k * kWarps) {  // all consumer warps
         float lo = 0.0f, hi = 0.0f;
         for (int s = 0; s < split_k; ++s) {
-          const float* remote = cluster.map_shared_rank(tile, s);
-          const float a = remote[row * kTile + lane];
-          const float b = remote[row * kTile + lane + 32];
+          const float* from = received + (s * owned_rows + row / split_k) * kTile;
+          const float a = from[lane];
+          const float b = from[lane + 32];
           lo = (s == 0) ? a : __fadd_rn(lo, a);
           hi = (s == 0) ? b : __fadd_rn(hi, b);
         }
@@ -340,18 +431,18 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
       // second launch.
       const uint32_t epoch = ar_epoch_shared;
       const int64_t area = (static_cast<int64_t>(epoch & 1u) * p.tp_world) * p.ar_max_count;  // values
-      constexpr int kMaxOwned = (kRows + kConsumerWarps - 1) / kConsumerWarps;
+      constexpr int kMaxOwned = (kRows + kWarps - 1) / kWarps;
       float own_lo[kMaxOwned], own_hi[kMaxOwned];
 #pragma unroll
       for (int it = 0; it < kMaxOwned; ++it) {
-        const int row = split + split_k * (warp + it * kConsumerWarps);
+        const int row = split + split_k * (warp + it * kWarps);
         own_lo[it] = own_hi[it] = 0.0f;
         if (row < rows) {
           float lo = 0.0f, hi = 0.0f;
           for (int s = 0; s < split_k; ++s) {
-            const float* remote = cluster.map_shared_rank(tile, s);
-            const float a = remote[row * kTile + lane];
-            const float b = remote[row * kTile + lane + 32];
+            const float* from = received + (s * owned_rows + row / split_k) * kTile;
+            const float a = from[lane];
+            const float b = from[lane + 32];
             lo = (s == 0) ? a : __fadd_rn(lo, a);
             hi = (s == 0) ? b : __fadd_rn(hi, b);
           }
@@ -369,7 +460,7 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
       }
 #pragma unroll
       for (int it = 0; it < kMaxOwned; ++it) {
-        const int row = split + split_k * (warp + it * kConsumerWarps);
+        const int row = split + split_k * (warp + it * kWarps);
         if (row < rows) {
           const int64_t e = static_cast<int64_t>(row) * n_cols + static_cast<int64_t>(j) * kTile + lane;
           float lo = 0.0f, hi = 0.0f;
@@ -401,11 +492,7 @@ __global__ void __launch_bounds__(32 * (kTileWorkers * WPT + 1), WPT == 1 ? 2 : 
       }
     }
   }
-  if (split_k > 1) {
-    cluster.sync();  // peers may still be reading this CTA's tile
-  } else if (kTp) {
-    __syncthreads();  // every warp has finished its exchange before the call counter may advance
-  }
+  if (kTp) __syncthreads();  // every warp has finished its exchange before the call counter may advance
   if (kTp && threadIdx.x == 0) {
     // the last CTA of the grid advances the call counter (the next launch starts after this one ends)
     uint32_t* counters = reinterpret_cast<uint32_t*>(p.peers.buffer[p.tp_rank]);
@@ -424,7 +511,7 @@ struct Variant {
 };
 Variant variant_for(int64_t m) { return m <= 8 ? Variant{1, 1} : m <= 16 ? Variant{2, 1} : Variant{2, 2}; }
 int variant_index(const Variant& v) { return v.wpt == 2 ? 2 : v.nt - 1; }
-int variant_threads(const Variant& v) { return 32 * (kTileWorkers * v.wpt + 1); }
+int variant_threads(const Variant& v) { return 32 * kTileWorkers * v.wpt; }
 const void* variant_kernel(const Variant& v, bool tp = false) {
   if (tp) {
     if (v.wpt == 2) return reinterpret_cast<const void*>(cluster_decode_kernel<2, 2, true>);
@@ -437,9 +524,8 @@ const void* variant_kernel(const Variant& v, bool tp = false) {
 }
 
 int smem_bytes(const Variant& v) {
-  const int rows = 8 * v.nt * v.wpt;
-  const int slabs = v.nt == 2 ? 0 : kTileWorkers * rows * kTile * 4;  // NT = 2 keeps them in the ring
-  return kSlots * kSlotBytes + slabs + rows * kTile * 4 + kMaxCount * 8 + kNumBars * 8 + 16;
+  const int rows = 8 * v.nt * v.wpt;  // the slabs live in the ring
+  return kSlots * kSlotBytes + (rows + 7) * kTile * 4 + kMaxCount * 8 + kNumBars * 8 + kSlots * 4 + 16;
 }
 
 int launch_variant(const Variant& v, const Params& p, int split_k, cudaStream_t stream) {
@@ -555,8 +641,9 @@ int launch_cluster_decode(const LinearArgs& a, cudaStream_t stream) {
   p.ar_max_count = a.ar_max_count;
   p.ar_poll_limit = peer_poll_limit();
   // The look-ahead hint of aq_linear_ahead is not used here: this kernel keeps HBM busy with its
-  // own ring, and prefetching the next image on top of it was measured slower (gate_up 3072 ->
-  // 16384 at one row: 9.1 us against 8.1 us per launch).
+  // own ring.  Prefetching the next image was measured both at the start of the kernel (slower:
+  // 9.1 us against 8.1 us per launch of the 3072 -> 16384 layer at one row) and at the end of the
+  // tile loop (no gain for the kernel that follows).
   for (int r = 0; r < kArMaxRanks; ++r) {
     p.peers.buffer[r] = (a.peer_buffers != nullptr && r < a.tp_world) ? static_cast<uint8_t*>(a.peer_buffers[r]) : nullptr;
   }

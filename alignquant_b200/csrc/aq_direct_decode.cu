@@ -187,16 +187,20 @@ __global__ void __launch_bounds__(32 * WARPS, NG == 1 ? 3 : 2) direct_decode_ker
       if (COLS == 16) copy16_async(slot + w8_off + 8 * 64, block + 8 * 64);
     }
   }
-  if (threadIdx.x == 0 && p.prefetch_bytes > 0) {
-    prefetch_slice_l2(p.prefetch, p.prefetch_bytes, static_cast<int64_t>(blockIdx.x) * gridDim.y + blockIdx.y,
-                      static_cast<int64_t>(gridDim.x) * gridDim.y);
-  }
   // Still before the dependency: wait for the block and widen its W4 tiles in place (every slot
   // has the size of a W8 block), so that after the dependency all tiles are read alike: two
   // vectors at fixed offsets, no selects, no shifts.  Every lane of a pair reads the packed
   // vector before any lane writes.
   copy_async_wait_all();
   __syncwarp();
+  // The look-ahead for the next launch goes out behind this CTA's own weights, one piece per warp
+  // at a time.  It pays where other kernels run between two projections; in a chain of nothing but
+  // projections it was measured to cost more than it gives whenever it is issued (at the start,
+  // here, or after the activation rows have landed).
+  if (lane == 0 && p.prefetch_bytes > 0) {
+    prefetch_slice_l2(p.prefetch, p.prefetch_bytes, static_cast<int64_t>(blockIdx.x) * gridDim.y + blockIdx.y,
+                      static_cast<int64_t>(gridDim.x) * gridDim.y, warp, WARPS);
+  }
   uint32_t w4_tiles = 0;  // bit i % 32: the warp's tile i is W4 (for the debug dump)
   if (my_tiles > 32) {
     lane_rec = {0u, 0.0f};
@@ -266,7 +270,6 @@ __global__ void __launch_bounds__(32 * WARPS, NG == 1 ? 3 : 2) direct_decode_ker
   }
   copy_async_wait_all();
   __syncthreads();
-
   float acc[NG][4];
 #pragma unroll
   for (int ng = 0; ng < NG; ++ng) acc[ng][0] = acc[ng][1] = acc[ng][2] = acc[ng][3] = 0.0f;

@@ -65,12 +65,15 @@ __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes
 }
 // This CTA's share of a look-ahead prefetch: the `total_bytes` at `base` are cut into one
 // contiguous slice per CTA (128-byte granules) and requested in pieces of at most 16 KiB.
-// Called by one thread per CTA.
-__device__ __forceinline__ void prefetch_slice_l2(const uint8_t* base, int64_t total_bytes, int64_t cta, int64_t ctas) {
+// The pieces are dealt to `issuers` callers (`issuer` = 0 .. issuers - 1, one thread each): a
+// bulk instruction holds its issuing warp for about 150 cycles whatever its size, so a slice
+// of a dozen pieces asked for by one thread would hold that warp for a microsecond.
+__device__ __forceinline__ void prefetch_slice_l2(const uint8_t* base, int64_t total_bytes, int64_t cta, int64_t ctas,
+                                                  int issuer = 0, int issuers = 1) {
   const int64_t slice = (((total_bytes + ctas - 1) / ctas) + 127) & ~static_cast<int64_t>(127);
   const int64_t begin = cta * slice;
   const int64_t end = begin + slice < total_bytes ? begin + slice : total_bytes;
-  for (int64_t at = begin; at < end; at += 16384) {
+  for (int64_t at = begin + static_cast<int64_t>(issuer) * 16384; at < end; at += static_cast<int64_t>(issuers) * 16384) {
     const int64_t left = end - at;
     bulk_prefetch_l2(base + at, static_cast<uint32_t>(left < 16384 ? left : 16384) & ~15u);
   }
