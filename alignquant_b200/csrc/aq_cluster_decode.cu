@@ -88,15 +88,6 @@ __device__ __forceinline__ uint32_t slot_arrive(uint32_t counter) {
   return before;
 }
 
-// d = a * b (a fresh integer sum: the accumulator input is the constant zero)
-__device__ __forceinline__ void mma_s8_fresh(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                             uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
-
 // The integer products of the column groups Q0 .. Q0 + QN - 1 of one staged tile with NT groups of
 // eight activation rows.  `lane_base`
 // is the tile's address plus this lane's offset inside a block of eight columns; the blocks of the

@@ -116,18 +116,15 @@ __device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.w
 __device__ __forceinline__ void sts16(uint32_t addr, const uint4& v) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
-// d = a * b (a fresh integer sum: the accumulator input is the constant zero)
-__device__ __forceinline__ void mma_s8_zero(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                            uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
 __device__ __forceinline__ uint4 lds16(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
+}
+
+// Bytes of a warp's block of shared memory: its tiles' weights, and room for its sums afterwards.
+__host__ __device__ constexpr uint32_t warp_block_bytes(int tiles_per_warp, int block_bytes, int sums_bytes) {
+  return static_cast<uint32_t>(tiles_per_warp * block_bytes > sums_bytes ? tiles_per_warp * block_bytes : sums_bytes);
 }
 
 // NG: groups of eight activation rows (1, 2 or 4).  COLS: output columns of a CTA (16 or 8).
@@ -140,8 +137,9 @@ __global__ void __launch_bounds__(32 * WARPS, NG == 1 ? 3 : 2) direct_decode_ker
   constexpr int kThreads = 32 * WARPS;
   constexpr int kGroups = kTile / COLS;
   constexpr int kBlockBytes = COLS * kTile;  // a W8 column group of one tile; W4 takes the first half
-  extern __shared__ __align__(128) uint8_t staged[];  // [WARPS][tiles per warp][kBlockBytes], then the activation rows
-  __shared__ float partial[WARPS][kRows][COLS];
+  // [WARPS][tiles per warp][kBlockBytes], then the activation rows.  A warp's block of weights
+  // becomes its [kRows][COLS] sums once its loop is over (nobody else reads the block).
+  extern __shared__ __align__(128) uint8_t staged[];
   __shared__ float finished[kRows][COLS];  // the CTA's columns, read by its cluster peers
   __shared__ uint32_t epoch_shared;
 
@@ -154,6 +152,7 @@ __global__ void __launch_bounds__(32 * WARPS, NG == 1 ? 3 : 2) direct_decode_ker
   const int n_k = p.n_k;
   const int rows = p.m < kRows ? static_cast<int>(p.m) : kRows;
   const int tiles_per_warp = (n_k + WARPS - 1) / WARPS;
+  const uint32_t warp_stage_bytes = warp_block_bytes(tiles_per_warp, kBlockBytes, kRows * COLS * 4);
   const int my_tiles = warp < n_k ? (n_k - warp + WARPS - 1) / WARPS : 0;  // tiles w, w + WARPS, ...
 
   grid_launch_dependents();
@@ -165,7 +164,7 @@ __global__ void __launch_bounds__(32 * WARPS, NG == 1 ? 3 : 2) direct_decode_ker
   const uint32_t w8_off = static_cast<uint32_t>(g * 64 + ((c ^ ((g >> 1) & 3)) << 4));
   const uint32_t w4_off = static_cast<uint32_t>(g * 32 + (c >> 1) * 16);
   const int w4_shift = (c & 1) ? 0 : 4;
-  const uint32_t my_stage = smem_u32(staged) + static_cast<uint32_t>(warp * tiles_per_warp) * kBlockBytes;
+  const uint32_t my_stage = smem_u32(staged) + static_cast<uint32_t>(warp) * warp_stage_bytes;
   TileRecord lane_rec = {0u, 0.0f};
   for (int i = 0; i < my_tiles; ++i) {
     if ((i & 31) == 0) {
@@ -243,7 +242,7 @@ __global__ void __launch_bounds__(32 * WARPS, NG == 1 ? 3 : 2) direct_decode_ker
   // constant memory, which the SM caches per line).
   const int64_t k_bytes = static_cast<int64_t>(n_k) * kTile;
   const uint32_t x_stride = static_cast<uint32_t>(k_bytes) + 64u;  // padded rows: no bank conflicts between rows
-  const uint32_t x_stage = smem_u32(staged) + static_cast<uint32_t>(WARPS * tiles_per_warp) * kBlockBytes;
+  const uint32_t x_stage = smem_u32(staged) + static_cast<uint32_t>(WARPS) * warp_stage_bytes;
   const int8_t* const x_global = p.xq;
   const float* const scale_global = p.act_scales;
   const bool token_mode = p.scale_mode == AQ_SCALE_TOKEN;
@@ -340,7 +339,7 @@ __global__ void __launch_bounds__(32 * WARPS, NG == 1 ? 3 : 2) direct_decode_ker
     int d[NG][4];
 #pragma unroll
     for (int ng = 0; ng < NG; ++ng) {
-      mma_s8_zero(d[ng], a.x, b.x, a.y, b.y, xv[ng].x, xv[ng].y);
+      mma_s8_fresh(d[ng], a.x, b.x, a.y, b.y, xv[ng].x, xv[ng].y);
       mma_s8(d[ng], a.z, b.z, a.w, b.w, xv[ng].z, xv[ng].w);
     }
     if (i > 0) accumulate(d_prev, ws_prev, i - 1);
@@ -356,14 +355,15 @@ __global__ void __launch_bounds__(32 * WARPS, NG == 1 ? 3 : 2) direct_decode_ker
   if (my_tiles > 0) accumulate(d_prev, ws_prev, my_tiles - 1);
 
   // ---- the warp sums, added in warp order ----------------------------------------------------------
+  float* partial = reinterpret_cast<float*>(staged + static_cast<size_t>(warp) * warp_stage_bytes);
 #pragma unroll
   for (int ng = 0; ng < NG; ++ng) {
     const int tok = ng * 8 + 2 * c;
-    partial[warp][tok][g] = acc[ng][0];
-    partial[warp][tok + 1][g] = acc[ng][1];
+    partial[tok * COLS + g] = acc[ng][0];
+    partial[(tok + 1) * COLS + g] = acc[ng][1];
     if (COLS == 16) {
-      partial[warp][tok][g + 8] = acc[ng][2];
-      partial[warp][tok + 1][g + 8] = acc[ng][3];
+      partial[tok * COLS + g + 8] = acc[ng][2];
+      partial[(tok + 1) * COLS + g + 8] = acc[ng][3];
     }
   }
   __syncthreads();
@@ -373,9 +373,10 @@ __global__ void __launch_bounds__(32 * WARPS, NG == 1 ? 3 : 2) direct_decode_ker
   const int64_t n_cols = static_cast<int64_t>(p.n_j) * kTile;
   for (int e = threadIdx.x; e < rows * COLS; e += kThreads) {
     const int row = e / COLS, col = e % COLS;
-    float v = partial[0][row][col];
+    const float* sums = reinterpret_cast<const float*>(staged) + e;  // warp 0's, the others one block further each
+    float v = sums[0];
 #pragma unroll
-    for (int w = 1; w < WARPS; ++w) v = __fadd_rn(v, partial[w][row][col]);
+    for (int w = 1; w < WARPS; ++w) v = __fadd_rn(v, sums[w * (warp_stage_bytes / 4)]);
     if (has_u) {
       finished[row][col] = v;
     } else {
@@ -436,7 +437,9 @@ constexpr int kMaxSmem = 112 * 1024;  // two CTAs per SM at least
 // weights of the CTA (every slot the size of a W8 block) + the activation rows, padded by 64 bytes each
 int staged_bytes(const Shape& shape, int n_k, int64_t m) {
   const int rows = static_cast<int>(m < 8 * shape.ng ? m : 8 * shape.ng);
-  return shape.warps * ((n_k + shape.warps - 1) / shape.warps) * shape.cols * kTile + rows * (n_k * kTile + 64);
+  const int tiles_per_warp = (n_k + shape.warps - 1) / shape.warps;
+  return shape.warps * static_cast<int>(warp_block_bytes(tiles_per_warp, shape.cols * kTile, 8 * shape.ng * shape.cols * 4)) +
+         rows * (n_k * kTile + 64);
 }
 
 bool shape_for(int64_t m, int n_k, Shape* shape) {
@@ -508,7 +511,8 @@ int launch_shape(const DirectParams& p, bool cluster, cudaStream_t stream) {
 
 // CTAs of a shape that fit one SM (shared memory, 64 Ki registers at the kernel's register count).
 int ctas_per_sm(const Shape& shape, int n_k, int64_t m) {
-  const int by_smem = (227 * 1024) / (staged_bytes(shape, n_k, m) + 4096);
+  // 228 KiB per SM; per CTA 1 KiB for the system and the kernel's static arrays (cluster exchange, epoch)
+  const int by_smem = (228 * 1024) / (staged_bytes(shape, n_k, m) + 1024 + 8 * shape.ng * shape.cols * 4 + 128);
   const int by_regs = shape.ng == 1 ? 3 : 2;  // the kernels' launch bounds
   return by_smem < by_regs ? by_smem : by_regs;
 }
@@ -521,7 +525,12 @@ bool direct_decode_supported(int64_t m, int n_j, int n_k) {
   Shape shape;
   if (!shape_for(m, n_k, &shape)) return false;
   const int64_t ctas = static_cast<int64_t>(n_j) * (kTile / shape.cols);
-  return ctas >= num_sms() && ctas <= static_cast<int64_t>(num_sms()) * ctas_per_sm(shape, n_k, m);
+  if (ctas < num_sms() || ctas > static_cast<int64_t>(num_sms()) * ctas_per_sm(shape, n_k, m)) return false;
+  // A grid that needs the SMs' shared memory to the brim to be resident is slower than the ring
+  // kernel (measured: 5120 x 3072 at 8 rows, three CTAs of 74 KiB per SM, 6.1 us against 5.6 us;
+  // 3072 x 8192 at one row, 8.9 us against 6.8 us): at most 200 KiB per SM.
+  const int64_t per_sm = (ctas + num_sms() - 1) / num_sms();
+  return per_sm * (staged_bytes(shape, n_k, m) + 2048) <= 200 * 1024;
 }
 
 int direct_decode_workers(int64_t m, int n_k) {

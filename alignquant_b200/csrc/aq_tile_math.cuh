@@ -23,6 +23,15 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// d = a * b (a fresh integer sum: the accumulator input is the constant zero)
+__device__ __forceinline__ void mma_s8_fresh(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 // Weight vector of lane (g, c) for output column n of a staged tile.
 //   W8 tile: row n is 64 bytes, 16-byte chunk c stored at slot c ^ ((n >> 1) & 3).
 //   W4 tile: row n is 32 bytes, chunk h = c / 2 holds k in [32h, 32h+32): low nibbles
