@@ -11,7 +11,7 @@ AQ_OK = 0
 AQ_F16, AQ_BF16, AQ_F32 = 0, 1, 2
 AQ_SCALE_TILE, AQ_SCALE_TOKEN = 0, 1
 AQ_OPT_PEER_POLL_LIMIT, AQ_OPT_GEMM_ROUNDING, AQ_OPT_GEMM_TILE, AQ_OPT_GEMM_SPLIT, AQ_OPT_DECODE_KERNEL = 1, 2, 3, 4, 5
-AQ_DECODE_KERNEL_AUTO, AQ_DECODE_KERNEL_CLUSTER = 0, 1
+AQ_DECODE_KERNEL_AUTO, AQ_DECODE_KERNEL_CLUSTER, AQ_DECODE_KERNEL_STREAMK = 0, 1, 2
 AQ_GEMM_ROUNDING_FUSED, AQ_GEMM_ROUNDING_SEPARATE = 0, 1
 GEMM_TILES = {"auto": 0, "paired": 1, "narrow": 2, "wide": 4}
 SCHEDULE_CODES = {"auto": 0, "forced_decode": 1, "forced_prefill": 2, "forced_prefill_m64": 3}

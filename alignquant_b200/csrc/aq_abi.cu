@@ -94,10 +94,11 @@ int choose_kernel(int64_t m, int n_j, int n_k, int schedule, int decode_splits) 
   if (schedule == AQ_SCHEDULE_PREFILL_M64) return 1;
   if (schedule == AQ_SCHEDULE_AUTO && (m > kStreamMaxRows || (decode_splits == 0 && m > kAutoGemmRows))) return 1;
   if (decode_splits != 0 || m > kClusterMaxRows) return 0;
-  if (decode_kernel_option() != AQ_DECODE_KERNEL_CLUSTER && direct_decode_supported(m, n_j, n_k)) return 4;
-  const bool cluster_ok = cluster_decode_supported(n_j, n_k);
-  if (m <= kDecodeMaxRows && (8 * n_j < num_sms() || !cluster_ok)) return 2;
-  return cluster_ok ? 3 : 0;
+  const int64_t wanted = decode_kernel_option();
+  if (wanted == AQ_DECODE_KERNEL_STREAMK && m <= kDecodeMaxRows) return 2;
+  if (wanted != AQ_DECODE_KERNEL_CLUSTER && direct_decode_supported(m, n_j, n_k)) return 4;
+  if (cluster_decode_supported(n_j, n_k)) return 3;
+  return m <= kDecodeMaxRows ? 2 : 0;
 }
 
 }  // namespace
@@ -129,8 +130,8 @@ int aq_set_option(int option, int64_t value) {
       g_gemm_tile.store(value, std::memory_order_relaxed);
       return AQ_OK;
     case AQ_OPT_DECODE_KERNEL:
-      AQ_REQUIRE(value == AQ_DECODE_KERNEL_AUTO || value == AQ_DECODE_KERNEL_CLUSTER,
-                 "AQ_OPT_DECODE_KERNEL must be AQ_DECODE_KERNEL_AUTO or AQ_DECODE_KERNEL_CLUSTER, got %lld",
+      AQ_REQUIRE(value == AQ_DECODE_KERNEL_AUTO || value == AQ_DECODE_KERNEL_CLUSTER || value == AQ_DECODE_KERNEL_STREAMK,
+                 "AQ_OPT_DECODE_KERNEL must be one of the AQ_DECODE_KERNEL_* values, got %lld",
                  static_cast<long long>(value));
       g_decode_kernel.store(value, std::memory_order_relaxed);
       return AQ_OK;
@@ -437,7 +438,7 @@ int aq_linear_plan(int64_t m, int32_t n_j, int32_t n_k, int schedule, int decode
   } else if (k == 4) {  // same order as kernel 3 with a single K range
     *kernel = 3;
     *splits = 1;
-    *workers = direct_decode_workers(m, n_k);
+    *workers = direct_decode_workers(m, n_j, n_k);
   }
   return AQ_OK;
 }

@@ -108,7 +108,7 @@ int take_cluster_decode_status();
 // groups to fill the machine and K short enough for a CTA's block to fit shared memory.
 int launch_direct_decode(const LinearArgs& a, cudaStream_t stream);
 bool direct_decode_supported(int64_t m, int n_j, int n_k);
-int direct_decode_workers(int64_t m, int n_k);
+int direct_decode_workers(int64_t m, int n_j, int n_k);
 int take_direct_decode_status();
 
 // Persistent stream-K kernel for m <= 16 (needs a zeroed, self-cleaning workspace).

@@ -442,16 +442,20 @@ int staged_bytes(const Shape& shape, int n_k, int64_t m) {
          rows * (n_k * kTile + 64);
 }
 
-bool shape_for(int64_t m, int n_k, Shape* shape) {
+// n_j: tile rows of the layer.  Sixteen-column CTAs unless they would leave SMs without a CTA
+// and eight-column CTAs (at most eight rows) are possible.
+bool shape_for(int64_t m, int n_j, int n_k, Shape* shape) {
   if (m < 1 || m > 32 || n_k < 1) return false;
   const int ng = m <= 8 ? 1 : m <= 16 ? 2 : 4;
   const Shape wide = {ng, 16, 8};
-  if (staged_bytes(wide, n_k, m) <= kMaxSmem) {
+  const Shape narrow = {1, 8, 8};
+  const bool wide_fits = staged_bytes(wide, n_k, m) <= kMaxSmem;
+  const bool narrow_fits = ng == 1 && staged_bytes(narrow, n_k, m) <= kMaxSmem;
+  if (wide_fits && !(narrow_fits && static_cast<int64_t>(n_j) * (kTile / 16) < num_sms())) {
     *shape = wide;
     return true;
   }
-  const Shape narrow = {1, 8, 8};
-  if (ng == 1 && staged_bytes(narrow, n_k, m) <= kMaxSmem) {
+  if (narrow_fits) {
     *shape = narrow;
     return true;
   }
@@ -523,9 +527,12 @@ int ctas_per_sm(const Shape& shape, int n_k, int64_t m) {
 // stream through a ring; narrower ones the kernels that split K.
 bool direct_decode_supported(int64_t m, int n_j, int n_k) {
   Shape shape;
-  if (!shape_for(m, n_k, &shape)) return false;
+  if (!shape_for(m, n_j, n_k, &shape)) return false;
   const int64_t ctas = static_cast<int64_t>(n_j) * (kTile / shape.cols);
-  if (ctas < num_sms() || ctas > static_cast<int64_t>(num_sms()) * ctas_per_sm(shape, n_k, m)) return false;
+  // At least a CTA for every fourth SM (narrow shards of a tensor-parallel layer: a megabyte or two,
+  // for which any kernel is a chain of latencies and this one has the shortest: 640 x 3072 at one row
+  // 2.2 us per launch against 12 us for the stream-K kernel), and all resident.
+  if (4 * ctas < num_sms() || ctas > static_cast<int64_t>(num_sms()) * ctas_per_sm(shape, n_k, m)) return false;
   // A grid that needs the SMs' shared memory to the brim to be resident is slower than the ring
   // kernel (measured: 5120 x 3072 at 8 rows, three CTAs of 74 KiB per SM, 6.1 us against 5.6 us;
   // 3072 x 8192 at one row, 8.9 us against 6.8 us): at most 200 KiB per SM.
@@ -533,14 +540,14 @@ bool direct_decode_supported(int64_t m, int n_j, int n_k) {
   return per_sm * (staged_bytes(shape, n_k, m) + 2048) <= 200 * 1024;
 }
 
-int direct_decode_workers(int64_t m, int n_k) {
+int direct_decode_workers(int64_t m, int n_j, int n_k) {
   Shape shape;
-  return shape_for(m, n_k, &shape) ? shape.warps : 0;
+  return shape_for(m, n_j, n_k, &shape) ? shape.warps : 0;
 }
 
 int launch_direct_decode(const LinearArgs& a, cudaStream_t stream) {
   Shape shape;
-  if (!shape_for(a.m, a.n_k, &shape)) return fail(AQ_ERR_INVALID, "the register-staged decode kernel does not take this shape");
+  if (!shape_for(a.m, a.n_j, a.n_k, &shape)) return fail(AQ_ERR_INVALID, "the register-staged decode kernel does not take this shape");
   DirectParams p;
   p.xq = a.xq;
   p.act_scales = a.act_scales;

@@ -545,10 +545,11 @@ def set_gemm_tile(name: str = "auto") -> None:
     _lib.check(_lib.load().aq_set_option(_lib.AQ_OPT_GEMM_TILE, _lib.GEMM_TILES[str(name)]))
 
 
-def set_decode_kernel(cluster_only: bool = False) -> None:
-    """``True``: never use the register-staged decode kernel (``AQ_OPT_DECODE_KERNEL``)."""
-    _lib.check(_lib.load().aq_set_option(
-        _lib.AQ_OPT_DECODE_KERNEL, _lib.AQ_DECODE_KERNEL_CLUSTER if cluster_only else _lib.AQ_DECODE_KERNEL_AUTO))
+def set_decode_kernel(cluster_only: bool = False, stream_k: bool = False) -> None:
+    """``cluster_only``: never use the decode kernel of many small CTAs; ``stream_k``: the persistent
+    stream-K kernel for everything of at most 16 rows (``AQ_OPT_DECODE_KERNEL``); neither: automatic."""
+    value = _lib.AQ_DECODE_KERNEL_STREAMK if stream_k else _lib.AQ_DECODE_KERNEL_CLUSTER if cluster_only else _lib.AQ_DECODE_KERNEL_AUTO
+    _lib.check(_lib.load().aq_set_option(_lib.AQ_OPT_DECODE_KERNEL, value))
 
 
 def set_gemm_split(split: int = 0) -> None:

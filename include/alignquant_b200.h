@@ -74,9 +74,12 @@ AQ_API int aq_version(void);
  *                           bit-identical across the three.
  *   AQ_OPT_GEMM_SPLIT       number of K ranges of the GEMM (1..8), 0 = automatic (default); changes
  *                           the FP32 summation order as aq_linear_plan reports.
- *   AQ_OPT_DECODE_KERNEL    AQ_DECODE_KERNEL_AUTO (default), or AQ_DECODE_KERNEL_CLUSTER: never use
- *                           the register-staged decode kernel (for tests and measurements; changes
- *                           the FP32 summation order as aq_linear_plan reports).
+ *   AQ_OPT_DECODE_KERNEL    AQ_DECODE_KERNEL_AUTO (default); AQ_DECODE_KERNEL_CLUSTER: never use
+ *                           the decode kernel of many small CTAs; AQ_DECODE_KERNEL_STREAMK: the
+ *                           persistent stream-K kernel for every problem of at most 16 rows (the
+ *                           kernel behind aq_linear_decode_static; the automatic choice no longer
+ *                           takes it where another kernel applies).  For tests and measurements;
+ *                           changes the FP32 summation order as aq_linear_plan reports.
  * aq_set_option returns AQ_OK or AQ_ERR_INVALID; aq_get_option the value or AQ_ERR_INVALID.
  */
 #define AQ_OPT_PEER_POLL_LIMIT 1
@@ -86,6 +89,7 @@ AQ_API int aq_version(void);
 #define AQ_OPT_DECODE_KERNEL 5
 #define AQ_DECODE_KERNEL_AUTO 0
 #define AQ_DECODE_KERNEL_CLUSTER 1
+#define AQ_DECODE_KERNEL_STREAMK 2
 #define AQ_GEMM_ROUNDING_FUSED 0
 #define AQ_GEMM_ROUNDING_SEPARATE 1
 #define AQ_GEMM_TILE_AUTO 0

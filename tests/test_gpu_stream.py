@@ -170,13 +170,24 @@ def test_stream_linear_matches_oracle(ext, n, k, m, scale_mode):
         assert np.allclose(got, y64, rtol=REL, atol=ABS)
 
 
+@pytest.fixture
+def decode_kernel(request, ext):
+    """Runs the test under a forced decode kernel and restores the automatic choice."""
+    ext.set_decode_kernel(cluster_only=request.param == "cluster", stream_k=request.param == "streamk")
+    yield request.param
+    ext.set_decode_kernel()
+
+
+@pytest.mark.parametrize("decode_kernel", ["auto", "cluster", "streamk"], indirect=True)
 @pytest.mark.parametrize("m", [1, 7, 8, 16, 24, 32])
 @pytest.mark.parametrize("n,k", [(3072, 3072), (1024, 8192), (5120, 256), (16384, 1024), (640, 4096)])
-def test_decode_kernel_many_ranges(ext, n, k, m):
-    """Layers with more tiles than SMs through both decode kernels (few tile rows: the
-    persistent stream-K kernel, whose ranges start and end inside tile rows and reuse the
-    workspace across calls; otherwise the warp-per-tile cluster kernel)."""
+def test_decode_kernel_many_ranges(ext, n, k, m, decode_kernel):
+    """Layers with more tiles than SMs through every decode kernel: the automatic choice, the ring
+    kernel alone, and the persistent stream-K kernel (up to 16 rows), whose ranges start and end
+    inside tile rows and reuse the workspace across calls."""
     n_j, n_k = n // 64, k // 64
+    wanted = {"cluster": (3,), "streamk": (2,) if m <= 16 else (3,), "auto": (2, 3)}[decode_kernel]
+    assert ext.linear_plan(m, n_j, n_k)["kernel"] in wanted
     packed, states, tiles, scales = oc.synthetic_layer(n, k, seed=n + k)
     weights, _ = helpers.prepare_layer(packed, n_k)
     xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=m), torch.float16)

@@ -44,8 +44,13 @@ def test_static_scratch_entry_point_matches_regular_entry_point(n, k, m):
     weights, _ = helpers.prepare_layer(packed, n_k)
     xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=m), torch.float16)
     xq, a_s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode="token")
-    want = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token")
-    same_kernel = ext.linear_plan(m, n_j, n_k)["kernel"] == 2
+    ext.set_decode_kernel(stream_k=True)  # the regular entry point with the kernel the static one runs
+    try:
+        want = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token")
+        same_kernel = ext.linear_plan(m, n_j, n_k)["kernel"] == 2
+    finally:
+        ext.set_decode_kernel()
+    assert same_kernel
     for call in range(2):  # two calls in a row share the built-in scratch
         out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
         status = _static_call(lib, xq, a_s, weights, _lib.AQ_SCALE_TOKEN, out)
@@ -103,8 +108,12 @@ def test_static_scratch_entry_point_with_output_transform_and_tile_scales():
     u_meta = metadata_stack([3, -1, 0, 7, 2, -1, 5, 1, 4, 6], torch.device("cuda"))
     xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=2), torch.float16)
     xq, a_s = ext.alignquant_activation_quantize_cuda(xt, None)
-    want = ext.alignquant_linear_prepared(xq, a_s, weights, u_meta)
-    assert ext.linear_plan(m, n_j, n_k)["kernel"] == 2
+    ext.set_decode_kernel(stream_k=True)  # the regular entry point with the kernel the static one runs
+    try:
+        want = ext.alignquant_linear_prepared(xq, a_s, weights, u_meta)
+        assert ext.linear_plan(m, n_j, n_k)["kernel"] == 2
+    finally:
+        ext.set_decode_kernel()
     for call in range(2):
         out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
         assert _static_call(lib, xq, a_s, weights, _lib.AQ_SCALE_TILE, out, u_meta) == 0, _lib.last_error()
