@@ -418,10 +418,21 @@ _PREPARED_CACHE: dict[tuple, PreparedWeights] = {}
 
 
 def _cached_prepared(tensors: tuple[torch.Tensor, ...], n_k: int) -> PreparedWeights:
-    key = tuple((int(t.data_ptr()), tuple(t.shape), int(t._version)) for t in tensors) + (n_k, str(tensors[0].device))
+    """Prepared image of the caller's seven arena tensors, cached while those tensors live.
+
+    Key and lifetime follow the caller's own tensor objects (storage address, offset, shape,
+    strides, version counter), not contiguous temporaries made from them, so a caller that passes
+    long-lived tensors pays the re-layout once whatever their memory format.  Tensors that are
+    themselves per-call temporaries (a fresh view or slice object on every call) cannot be
+    cached across calls: their image is rebuilt each time, which costs a pass over the weights.
+    """
+    key = tuple(
+        (int(t.untyped_storage().data_ptr()), int(t.storage_offset()), tuple(t.shape), tuple(t.stride()), int(t._version))
+        for t in tensors
+    ) + (n_k, str(tensors[0].device))
     hit = _PREPARED_CACHE.get(key)
     if hit is None:
-        hit = prepare_weights(*tensors, n_k=n_k)
+        hit = prepare_weights(*(t.contiguous() for t in tensors), n_k=n_k)
         _PREPARED_CACHE[key] = hit
         for tensor in tensors:  # the image is only valid while the source tensors are alive
             weakref.finalize(tensor, _PREPARED_CACHE.pop, key, None)
@@ -448,17 +459,15 @@ def alignquant_linear_cuda(
     """Run one packed projection from the raw artifact tensors (reference signature).
 
     The weight arenas are re-laid-out on first use and the image is cached for as long
-    as the seven tensors stay alive; callers that own the weights should call
-    ``prepare_weights`` once and ``alignquant_linear_prepared`` per step instead.
+    as the seven tensor objects passed here stay alive (per-call temporaries are re-laid-out
+    on every call); callers that own the weights should call ``prepare_weights`` once and
+    ``alignquant_linear_prepared`` per step instead.
     """
     if activation.dim() == 4:
         n_k = int(activation.size(1))
     else:
         n_k = int(activation.size(-1)) // 64
-    tensors = tuple(
-        t.contiguous()
-        for t in (state_bits, w4_payload, w4_scales, w8_payload, w8_scales, w4_row_offsets, w8_row_offsets)
-    )
+    tensors = (state_bits, w4_payload, w4_scales, w8_payload, w8_scales, w4_row_offsets, w8_row_offsets)
     weights = _cached_prepared(tensors, n_k)
     return alignquant_linear_prepared(
         activation, activation_scales, weights, u_metadata,

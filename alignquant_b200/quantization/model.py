@@ -266,7 +266,12 @@ class _ProjectionGroupRuntime:
             if rows <= 0:
                 raise ValueError("Activation must contain at least one row.")
             flat = activation.reshape(rows, width)
-            qx, scales = _ext.alignquant_activation_quantize_cuda(flat, self.v_metadata, scale_mode=self.scale_mode)
+            ready = getattr(activation, "_alignquant_quantized", None)  # left by AlignQuantRMSNorm
+            if (ready is not None and self.scale_mode == "token" and self.v_metadata is None
+                    and tuple(ready[0].shape) == (rows, width)):
+                qx, scales = ready
+            else:
+                qx, scales = _ext.alignquant_activation_quantize_cuda(flat, self.v_metadata, scale_mode=self.scale_mode)
             # Low-precision kernel output only for bias-free groups, as in the reference
             # (model.py:343-349): with a bias the FP32 result is kept through the bias add and
             # rounded once at the end.  Row-parallel partials stay FP32 for the sum over ranks.
@@ -342,6 +347,65 @@ class AlignQuantLinear(nn.Module):
         return result.to(dtype=activation.dtype)
 
 
+class AlignQuantRMSNorm(nn.Module):
+    """The RMSNorm in front of a projection group, with the group's activation quantizer in the
+    same kernel (``aq_rmsnorm_quantize``).
+
+    Returns the normalised tensor as the module it replaces does, and leaves the int8 rows and
+    their scales on it, where the projection group picks them up instead of launching its own
+    quantizer (the reference runs the model's norm module and then the quantizer:
+    alignquant/quantization/model.py:329-331).  The sum of squares is taken in FP64 where the stock
+    module uses FP32; every rounding step of the result is the module's.  Inputs the kernel does
+    not take (other dtypes, CPU tensors) go through the original module.
+    """
+
+    def __init__(self, norm: nn.Module) -> None:
+        super().__init__()
+        self.original = norm
+        self.eps = float(getattr(norm, "variance_epsilon", getattr(norm, "eps", 1e-6)))
+
+    @property
+    def weight(self) -> torch.Tensor:
+        return self.original.weight
+
+    def forward(self, hidden: torch.Tensor) -> torch.Tensor:
+        weight = self.original.weight
+        width = int(hidden.shape[-1]) if hidden.dim() else 0
+        if (not hidden.is_cuda or hidden.dtype not in (torch.float16, torch.bfloat16) or weight.dtype != hidden.dtype
+                or width % 64 or hidden.numel() == 0 or tuple(weight.shape) != (width,)):
+            return self.original(hidden)
+        flat = hidden.reshape(-1, width)
+        normed = torch.empty_like(flat)
+        quantized = _ext.alignquant_rmsnorm_quantize_cuda(flat, weight, self.eps, normed=normed)
+        result = normed.reshape(hidden.shape)
+        result._alignquant_quantized = quantized
+        return result
+
+
+def _fuse_norms(model: nn.Module, runtimes: Mapping[str, "_ProjectionGroupRuntime"]) -> int:
+    """Replace the RMSNorm in front of every token-mode, identity-V projection group that follows one."""
+    preceding = {"self_attn": "input_layernorm", "mlp": "post_attention_layernorm"}
+    replaced = 0
+    for runtime in runtimes.values():
+        if runtime.scale_mode != "token" or runtime.v_metadata is not None or runtime.row_parallel:
+            continue
+        parts = runtime.members[0].split(".")  # ... layers.N.self_attn.q_proj
+        if len(parts) < 3 or parts[-2] not in preceding or parts[-1] not in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj"):
+            continue
+        try:
+            layer = model.get_submodule(".".join(parts[:-2]))
+        except AttributeError:
+            continue
+        norm = getattr(layer, preceding[parts[-2]], None)
+        weight = getattr(norm, "weight", None)
+        if (norm is None or isinstance(norm, AlignQuantRMSNorm) or weight is None or weight.dim() != 1
+                or int(weight.numel()) != runtime.n_k * 64 or "rmsnorm" not in type(norm).__name__.lower()):
+            continue
+        setattr(layer, preceding[parts[-2]], AlignQuantRMSNorm(norm))
+        replaced += 1
+    return replaced
+
+
 def install_alignquant(
     model: nn.Module,
     artifact: Mapping[str, Any] | str | Path,
@@ -353,6 +417,7 @@ def install_alignquant(
     tp_size: int = 1,
     process_group: Any = None,
     peer_allreduce: Any = None,
+    fuse_norms: bool = False,
 ) -> tuple[list[AlignQuantLinear], dict[str, Any]]:
     """Replace exactly the artifact-covered decoder projections of ``model``.
 
@@ -361,6 +426,8 @@ def install_alignquant(
     artifact holds the full layers; each rank keeps its tile-aligned shard.  ``peer_allreduce``
     (a ``kernels.cuda.allreduce.PeerAllReduce``) takes over the sum of the row-parallel
     partials for FP32 results that fit its buffer; larger ones go through ``dist.all_reduce``.
+    ``fuse_norms`` also replaces the RMSNorm in front of the q/k/v and gate/up groups by
+    ``AlignQuantRMSNorm`` (token scale mode, identity V only).
     Returns the installed modules and a metadata dict, like the reference
     (alignquant/quantization/model.py:419-539).
     """
@@ -435,7 +502,9 @@ def install_alignquant(
         successor = runtimes[chain[(position + 1) % len(chain)]]
         if successor.device == runtimes[group_id].device and len(chain) > 1:
             runtimes[group_id].next_weights = successor.weights
+    fused_norms = _fuse_norms(model, runtimes) if fuse_norms else 0
     metadata = {
+        "fused_norm_count": fused_norms,
         "module_count": len(installed),
         "projection_group_count": len(runtimes),
         "groups": {group: list(members) for group, members in groups.items()},

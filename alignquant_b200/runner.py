@@ -131,8 +131,9 @@ def run(args) -> dict:
         from alignquant_b200.kernels.cuda.allreduce import PeerAllReduce
 
         reducer = PeerAllReduce(64 * SHAPES[args.model][0], device)  # up to 64 rows of hidden-size partials
-    installed, _ = install_alignquant(model, artifact, device, scale_mode=args.scale_mode, tp_rank=rank, tp_size=world,
-                                      peer_allreduce=reducer)
+    installed, install_meta = install_alignquant(model, artifact, device, scale_mode=args.scale_mode, tp_rank=rank,
+                                                 tp_size=world, peer_allreduce=reducer,
+                                                 fuse_norms=not getattr(args, "stock_norms", False))
     del artifact
     torch.cuda.empty_cache()
 
@@ -203,7 +204,7 @@ def run(args) -> dict:
     return {
         "model": args.model, "layers": args.layers or SHAPES[args.model][2], "tp": world, "batch": args.batch,
         "prompt_len": args.prompt_len, "new_tokens": args.new_tokens, "scale_mode": args.scale_mode,
-        "quantized_modules": len(installed),
+        "quantized_modules": len(installed), "fused_norms": install_meta["fused_norm_count"],
         "prefill_tokens_per_s": args.batch * args.prompt_len / prefill_s,
         "decode_tokens_per_s": args.batch * decode_steps / decode_s, "decode_steps_timed": decode_steps,
         "decode_launch": decode_mode, "decode_ms_per_step": decode_s * 1e3 / max(decode_steps, 1),
@@ -232,6 +233,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=None, help="override the number of decoder layers")
     ap.add_argument("--scale-mode", choices=("tile", "token"), default="token")
     ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--stock-norms", action="store_true",
+                    help="keep the model's RMSNorm modules (default: norm + activation quantizer as one kernel)")
     ap.add_argument("--no-decode-graph", dest="decode_graph", action="store_false",
                     help="run every decode step eagerly instead of replaying a CUDA graph")
     result = run(ap.parse_args())

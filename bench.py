@@ -62,8 +62,9 @@ FALLBACK_HBM_GBS = 6650.0
 NOMINAL_INT8_TOPS = 4500.0
 PREFILL_ROWS = 2048
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the packed-GEMV kernel per projection
-# group at M = 1, one GPU, from an ncu capture of this sweep's four shapes run as a chain with the
-# look-ahead on (L2 not flushed between launches).  None until captured; N > 1 is not captured.
+# group at M = 1, one GPU, from an ncu capture of this sweep's four shapes with the L2 flushed before
+# every launch (the sweep's own condition: its 2 GB of weights per step never stay in the L2).
+# None until captured; N > 1 is not captured.
 NCU_DRAM_BYTES_PER_LAUNCH = {"qkv": None, "o": None, "gate_up": None, "down": None}
 
 
@@ -290,7 +291,7 @@ def generation_leg(world: int, tokens: int) -> dict:
         model, batch, prompt_len, full_tokens = "qwen3-14b", 32, 1024, 256
     record = generation_record(model, batch, prompt_len, tokens, warmup=1)
     keep = ("model", "layers", "tp", "batch", "prompt_len", "new_tokens", "prefill_tokens_per_s", "decode_tokens_per_s",
-            "decode_ms_per_step", "decode_launch", "decode_steps_timed", "quantized_modules")
+            "decode_ms_per_step", "decode_launch", "decode_steps_timed", "quantized_modules", "fused_norms")
     result = {key: record[key] for key in keep}
     result["note"] = (f"{tokens} generated tokens instead of the configuration's {full_tokens} (the decode step does not "
                       "depend on the count beyond the KV-cache length); random-init weights, random token ids")
@@ -583,7 +584,7 @@ def run_native(args) -> None:
     e2e_seconds = timed(e2e_run, max(1, min(args.steps, 5)), 1)
 
     traffic = None
-    if world == 1 and lookahead and all(v is not None for v in NCU_DRAM_BYTES_PER_LAUNCH.values()):
+    if world == 1 and not lookahead and all(v is not None for v in NCU_DRAM_BYTES_PER_LAUNCH.values()):
         traffic = sum(NCU_DRAM_BYTES_PER_LAUNCH.values()) / len(NCU_DRAM_BYTES_PER_LAUNCH)
     total_bytes = step_bytes * world  # every rank streams its own shard
     line = {
@@ -615,7 +616,8 @@ def run_native(args) -> None:
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "launch": e2e_mode},
         "gpu_launches": (2 * pairs_per_step + own_sum_launches) * args.steps,
         "roofline": {
-            "kernel": ("cluster_decode_kernel" if args.cluster_decode else "direct_decode_kernel") + " (packed W4/W8 GEMV, M<=16)",
+            "kernel": ("cluster_decode_kernel" if args.cluster_decode else "direct_decode_kernel + cluster_decode_kernel") +
+                      " (packed W4/W8 GEMV, M<=16; mean over the sweep's launches)",
             "bound": "hbm",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "peak_source": f"{peak_source} HBM copy bandwidth", "traffic": traffic,

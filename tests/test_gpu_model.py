@@ -89,3 +89,41 @@ def test_reference_built_artifact_installs_and_matches_reference_outputs(golden_
             assert got.dtype == torch.float16
             # fp16 result (2^-11 relative) on top of the rel 1e-3 / abs 1e-2 contract
             assert np.allclose(got.float().cpu().numpy(), want, rtol=2e-3, atol=1e-2), (index, short)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows", [1, 8, 40])
+def test_fused_norm_feeds_the_projection_group(rows, dtype):
+    """AlignQuantRMSNorm: the normalised tensor is the stock module's (to one rounding step of the
+    dtype, the sum of squares being taken in FP64), the int8 rows it leaves are exactly the
+    quantizer's for that tensor, and the projections give the same bits whether they take them or
+    quantize the tensor themselves."""
+    from alignquant_b200.kernels.cuda import extension as ext
+    from alignquant_b200.quantization.model import AlignQuantRMSNorm, install_alignquant, reset_alignquant_state
+
+    ext.load_extension()
+    artifact, _ = _artifact()
+    model = _Tiny(norms=True).cuda().to(dtype)
+    _, meta = install_alignquant(model, artifact, "cuda", scale_mode="token", fuse_norms=True)
+    assert meta["fused_norm_count"] == 2
+    layer = model.model.layers[0]
+    assert isinstance(layer.input_layernorm, AlignQuantRMSNorm)
+    gen = torch.Generator(device="cuda").manual_seed(rows)
+    x = (torch.randn((rows, 128), generator=gen, device="cuda") * 3).to(dtype)
+    for norm, members in ((layer.input_layernorm, (layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj)),
+                          (layer.post_attention_layernorm, (layer.mlp.gate_proj, layer.mlp.up_proj))):
+        reset_alignquant_state(model)
+        y = norm(x)
+        want = norm.original(x)
+        step = 2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7  # one unit in the last place, relative
+        assert torch.allclose(y.float(), want.float(), rtol=2 * step, atol=1e-6)
+        xq, scales = y._alignquant_quantized
+        ref_q, ref_s = ext.alignquant_activation_quantize_cuda(y, None, scale_mode="token")
+        assert torch.equal(xq, ref_q) and torch.equal(scales, ref_s)
+        fused = [m(y) for m in members]
+        ext.device_status()
+        fresh_input = y.clone()  # no int8 rows attached: the group launches its own quantizer
+        fresh = [m(fresh_input) for m in members]
+        ext.device_status()
+        for a, b in zip(fused, fresh):
+            assert torch.equal(a, b)

@@ -272,6 +272,31 @@ def test_reference_fixture_end_to_end(ext, golden_dir, name):
     assert np.allclose(out2.cpu().numpy(), g["y"], rtol=REL, atol=ABS)
 
 
+def test_reference_signature_caches_the_image_of_long_lived_tensors(ext, golden_dir, monkeypatch):
+    """The reference-signature call re-lays-out the weights once for tensors that stay alive, also
+    when one of them is not contiguous; a new tensor object is a new layer."""
+    g = dict(np.load(golden_dir / "linear_identity.npz"))
+    t = helpers.to_cuda({key[len("packed_"):]: v for key, v in g.items() if key.startswith("packed_")})
+    wide = torch.zeros(tuple(t["w8_payload"].shape[:-1]) + (128,), dtype=torch.int8, device="cuda")
+    wide[..., :64] = t["w8_payload"]
+    strided = wide[..., :64]  # same values, not contiguous, alive for the whole test
+    assert not strided.is_contiguous() or strided.numel() == 0
+    xq = torch.from_numpy(g["xq"]).cuda()
+    a_s = torch.from_numpy(np.ascontiguousarray(g["act_scales"][: (xq.shape[0] + 15) // 16])).cuda()
+    u_meta = torch.from_numpy(g["u_metadata"]).cuda()
+    builds = []
+    real = ext.prepare_weights
+    monkeypatch.setattr(ext, "prepare_weights", lambda *a, **k: (builds.append(1), real(*a, **k))[1])
+    outs = [ext.alignquant_linear_cuda(xq, a_s, t["state_bits"], t["w4_payload"], t["w4_scales"], strided, t["w8_scales"],
+                                       t["w4_row_offsets"], t["w8_row_offsets"], u_meta) for _ in range(3)]
+    ext.device_status()
+    assert len(builds) == 1 and torch.equal(outs[0], outs[2])
+    assert np.allclose(outs[0].cpu().numpy(), g["y"], rtol=REL, atol=ABS)
+    ext.alignquant_linear_cuda(xq, a_s, t["state_bits"], t["w4_payload"], t["w4_scales"], t["w8_payload"], t["w8_scales"],
+                               t["w4_row_offsets"], t["w8_row_offsets"], u_meta)
+    assert len(builds) == 2
+
+
 def test_argument_errors_raise(ext):
     packed, *_ = oc.synthetic_layer(64, 64, seed=1)
     weights, t = helpers.prepare_layer(packed, 1)

@@ -75,19 +75,37 @@ class _Mlp(nn.Module):
         self.down_proj = nn.Linear(inter_in, hidden, bias=False)
 
 
+class TinyRMSNorm(nn.Module):
+    """The arithmetic of the Llama / Qwen3 RMSNorm module."""
+
+    def __init__(self, hidden, eps=1e-5):
+        super().__init__()
+        self.weight = nn.Parameter(torch.linspace(0.5, 1.5, hidden))
+        self.variance_epsilon = eps
+
+    def forward(self, hidden_states):
+        dtype = hidden_states.dtype
+        x = hidden_states.to(torch.float32)
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.variance_epsilon)
+        return self.weight * x.to(dtype)
+
+
 class _Layer(nn.Module):
-    def __init__(self, hidden, q, kv, inter, tp):
+    def __init__(self, hidden, q, kv, inter, tp, norms=False):
         super().__init__()
         self.self_attn = _Attn(hidden, q // tp, kv // tp, q // tp)
         self.mlp = _Mlp(hidden, inter // tp, inter // tp)
+        if norms:
+            self.input_layernorm = TinyRMSNorm(hidden)
+            self.post_attention_layernorm = TinyRMSNorm(hidden)
 
 
 class _Tiny(nn.Module):
-    def __init__(self, tp=1, hidden=128, q=256, kv=128, inter=256, layers=1):
+    def __init__(self, tp=1, hidden=128, q=256, kv=128, inter=256, layers=1, norms=False):
         super().__init__()
         self.config = type("C", (), {"model_type": "llama"})()
         self.model = nn.Module()
-        self.model.layers = nn.ModuleList([_Layer(hidden, q, kv, inter, tp) for _ in range(layers)])
+        self.model.layers = nn.ModuleList([_Layer(hidden, q, kv, inter, tp, norms) for _ in range(layers)])
 
 
 FULL_SHAPES = {
@@ -162,6 +180,26 @@ def test_install_groups_caches_and_slices(monkeypatch):
     with pytest.raises(ValueError, match="coverage mismatch"):
         bad = dict(artifact, manifest={"modules": artifact["manifest"]["modules"][:-1]})
         glue.install_alignquant(_Tiny(), bad, "cpu")
+
+
+def test_fuse_norms_replaces_only_the_norms_in_front_of_projection_groups(monkeypatch):
+    _patch(monkeypatch)
+    artifact, _ = _artifact()
+    model = _Tiny(norms=True)
+    _, meta = glue.install_alignquant(model, artifact, "cpu", scale_mode="token", fuse_norms=True)
+    layer = model.model.layers[0]
+    assert meta["fused_norm_count"] == 2
+    assert isinstance(layer.input_layernorm, glue.AlignQuantRMSNorm)
+    assert isinstance(layer.post_attention_layernorm, glue.AlignQuantRMSNorm)
+    assert layer.input_layernorm.eps == 1e-5 and layer.input_layernorm.weight is layer.input_layernorm.original.weight
+    # a CPU tensor goes through the original module, and nothing is left on the result
+    x = torch.randn(3, 128)
+    y = layer.input_layernorm(x)
+    assert torch.equal(y, layer.input_layernorm.original(x)) and not hasattr(y, "_alignquant_quantized")
+    # tile scale mode (the reference's) keeps the stock norms
+    plain = _Tiny(norms=True)
+    _, meta = glue.install_alignquant(plain, artifact, "cpu", fuse_norms=True)
+    assert meta["fused_norm_count"] == 0 and isinstance(plain.model.layers[0].input_layernorm, TinyRMSNorm)
 
 
 def _tp_worker(rank, world, port, results):
