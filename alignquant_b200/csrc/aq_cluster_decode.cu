@@ -75,6 +75,7 @@ __device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
 
 constexpr int kGroupTiles = 8;  // tiles per ring slot
 constexpr int kSlots = 3;
+constexpr int kModePlain = 0, kModeTp = 1, kModeDump = 2;
 constexpr int kSlotBytes = kGroupTiles * kW8TileBytes;
 constexpr int kTileWorkers = 8;  // tiles in progress per CTA; WPT warps share one tile (16 rows each)
 constexpr int kMaxCount = 512;  // tiles of one CTA's K range
@@ -126,17 +127,24 @@ __device__ __forceinline__ void tile_products(const uint8_t* lane_base, int w4_s
 // split over a cluster.
 // For 17..32 rows two warps share every tile (WPT = 2): warp 2t takes rows 0..15 and warp
 // 2t+1 rows 16..31 of tile worker t, so the weights are still streamed once.
-// kTp: the epilogue also sums over the tensor-parallel ranks (a separate instantiation, so that
-// the single-GPU kernel keeps its register count).
-template <int NT, int WPT, bool kTp>
+// kMode: kModeTp -- the epilogue also sums over the tensor-parallel ranks; kModeDump -- the integer
+// tile sums are also written out (tests).  Separate instantiations keep both out of the plain
+// kernel's loop (its instructions should stay in the instruction cache) and register count.
+template <int NT, int WPT, int kMode>
 __global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) cluster_decode_kernel(const Params p) {
+  constexpr bool kTp = kMode == kModeTp;
+  constexpr bool kDump = kMode == kModeDump;
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kWarps = kTileWorkers * WPT;
   constexpr int kThreads = kWarps * 32;
   constexpr int kWarpRows = 8 * NT;      // rows one warp accumulates
   constexpr int kRows = kWarpRows * WPT;  // rows of the CTA
   constexpr int kReceivedRows = kRows + 7;  // split x ceil(rows / split) <= rows + split - 1, split <= 8
-  static_assert(kTileWorkers * kRows * kTile * 4 <= kSlots * kSlotBytes, "slabs must fit into the ring");
+  // Rows of a slab are 68 floats apart: lane (g, c) stores to rows 2c and 2c + 1, and 2c * 68 = 8c
+  // (mod 32 banks) keeps the four c of a column apart (64 would put them on one bank: 4-way conflicts,
+  // measured 0.3 us per launch at 16 rows).
+  constexpr int kSlabRow = kTile + 4;
+  static_assert(kTileWorkers * kRows * kSlabRow * 4 <= kSlots * kSlotBytes, "slabs must fit into the ring");
   uint8_t* ring = smem;
   float* slabs = reinterpret_cast<float*>(smem);
   float* received = reinterpret_cast<float*>(smem + kSlots * kSlotBytes);  // [source CTA][owned row][64]
@@ -216,7 +224,7 @@ __global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) clu
   const int c = lane & 3;
   const bool token_mode = p.scale_mode == AQ_SCALE_TOKEN;
   const float* const scale_global = p.act_scales;
-  int32_t* const dump_global = p.acc_dump;
+  int32_t* const dump_global = kDump ? p.acc_dump : nullptr;
   const int64_t k_bytes = static_cast<int64_t>(n_k) * kTile;
   const int8_t* x_lane[NT];
 #pragma unroll
@@ -331,7 +339,7 @@ __global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) clu
             acc[nt][q0 + q][2] = __fadd_rn(acc[nt][q0 + q][2], __fmul_rn(static_cast<float>(d[nt][q][2]), s0[nt]));
             acc[nt][q0 + q][3] = __fadd_rn(acc[nt][q0 + q][3], __fmul_rn(static_cast<float>(d[nt][q][3]), s1[nt]));
           }
-          if (dump_global != nullptr) {
+          if (kDump) {
             const int shift = is_w4 ? 4 : 0;
             const int tok = row0 + nt * 8 + 2 * c;
 #pragma unroll
@@ -355,19 +363,19 @@ __global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) clu
     }
     // ---- combine the eight warp sums in warp order -----------------------------------------
     __syncthreads();  // every warp has consumed its last tile: the ring becomes the slabs
-    float* slab = slabs + worker * kRows * kTile;
+    float* slab = slabs + worker * kRows * kSlabRow;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int tok = row0 + nt * 8 + 2 * c;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {  // only the rows that exist are combined and exchanged
         if (tok < rows) {
-          slab[tok * kTile + q * 16 + g] = acc[nt][q][0];
-          slab[tok * kTile + q * 16 + g + 8] = acc[nt][q][2];
+          slab[tok * kSlabRow + q * 16 + g] = acc[nt][q][0];
+          slab[tok * kSlabRow + q * 16 + g + 8] = acc[nt][q][2];
         }
         if (tok + 1 < rows) {
-          slab[(tok + 1) * kTile + q * 16 + g] = acc[nt][q][1];
-          slab[(tok + 1) * kTile + q * 16 + g + 8] = acc[nt][q][3];
+          slab[(tok + 1) * kSlabRow + q * 16 + g] = acc[nt][q][1];
+          slab[(tok + 1) * kSlabRow + q * 16 + g + 8] = acc[nt][q][3];
         }
       }
     }
@@ -376,10 +384,11 @@ __global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) clu
     // the place of this CTA's K range there: after ONE cluster barrier every CTA adds what it
     // received, in its own shared memory, and nobody has to stay for a peer that still reads.
     for (int e = threadIdx.x; e < rows * kTile; e += kThreads) {
-      float v = slabs[e];
-#pragma unroll
-      for (int w = 1; w < kTileWorkers; ++w) v = __fadd_rn(v, slabs[w * kRows * kTile + e]);
       const int row = e / kTile, col = e % kTile;
+      const float* sums = slabs + row * kSlabRow + col;
+      float v = sums[0];
+#pragma unroll
+      for (int w = 1; w < kTileWorkers; ++w) v = __fadd_rn(v, sums[w * kRows * kSlabRow]);
       const int owner = row % split_k, place = row / split_k;
       float* target = split_k > 1 ? cluster.map_shared_rank(received, owner) : received;
       target[(split * owned_rows + place) * kTile + col] = v;
@@ -503,15 +512,15 @@ struct Variant {
 Variant variant_for(int64_t m) { return m <= 8 ? Variant{1, 1} : m <= 16 ? Variant{2, 1} : Variant{2, 2}; }
 int variant_index(const Variant& v) { return v.wpt == 2 ? 2 : v.nt - 1; }
 int variant_threads(const Variant& v) { return 32 * kTileWorkers * v.wpt; }
-const void* variant_kernel(const Variant& v, bool tp = false) {
-  if (tp) {
-    if (v.wpt == 2) return reinterpret_cast<const void*>(cluster_decode_kernel<2, 2, true>);
-    return v.nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1, 1, true>)
-                     : reinterpret_cast<const void*>(cluster_decode_kernel<2, 1, true>);
-  }
-  if (v.wpt == 2) return reinterpret_cast<const void*>(cluster_decode_kernel<2, 2, false>);
-  return v.nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1, 1, false>)
-                   : reinterpret_cast<const void*>(cluster_decode_kernel<2, 1, false>);
+template <int kMode>
+const void* variant_kernel_of(const Variant& v) {
+  if (v.wpt == 2) return reinterpret_cast<const void*>(cluster_decode_kernel<2, 2, kMode>);
+  return v.nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1, 1, kMode>)
+                   : reinterpret_cast<const void*>(cluster_decode_kernel<2, 1, kMode>);
+}
+const void* variant_kernel(const Variant& v, int mode = kModePlain) {
+  return mode == kModeTp ? variant_kernel_of<kModeTp>(v) : mode == kModeDump ? variant_kernel_of<kModeDump>(v)
+                                                                              : variant_kernel_of<kModePlain>(v);
 }
 
 int smem_bytes(const Variant& v) {
@@ -520,14 +529,14 @@ int smem_bytes(const Variant& v) {
 }
 
 int launch_variant(const Variant& v, const Params& p, int split_k, cudaStream_t stream) {
-  static std::once_flag once[64][6];
+  static std::once_flag once[64][9];
   int device = 0;
   int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
   if (rc != AQ_OK) return rc;
-  const bool tp = p.tp_world > 1;
-  const void* kernel = variant_kernel(v, tp);
+  const int mode = p.tp_world > 1 ? kModeTp : p.acc_dump != nullptr ? kModeDump : kModePlain;
+  const void* kernel = variant_kernel(v, mode);
   cudaError_t attr_status = cudaSuccess;
-  std::call_once(once[device & 63][variant_index(v) + (tp ? 3 : 0)], [&] {
+  std::call_once(once[device & 63][variant_index(v) + 3 * mode], [&] {
     attr_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(v));
   });
   rc = check_cuda(attr_status, "cudaFuncSetAttribute(cluster_decode_kernel)");
