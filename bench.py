@@ -65,7 +65,7 @@ PREFILL_ROWS = 2048
 # group at M = 1, one GPU, from an ncu capture of this sweep's four shapes with the L2 flushed before
 # every launch (the sweep's own condition: its 2 GB of weights per step never stay in the L2).
 # None until captured; N > 1 is not captured.
-NCU_DRAM_BYTES_PER_LAUNCH = {"qkv": None, "o": None, "gate_up": None, "down": None}
+NCU_DRAM_BYTES_PER_LAUNCH = {"qkv": 11092736, "o": 6677248, "gate_up": 35363584, "down": 17704192}
 
 
 def parse_args():
@@ -621,6 +621,8 @@ def run_native(args) -> None:
             "bound": "hbm",
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "peak_source": f"{peak_source} HBM copy bandwidth", "traffic": traffic,
+            "traffic_how": ("dram__bytes_read.sum + dram__bytes_write.sum per launch, ncu capture of the four shapes at one "
+                            "row with the L2 flushed before each launch, mean over the shapes" if traffic is not None else None),
             "bytes_per_launch": linear_bytes / pairs_per_step, "us_per_launch": kernel_seconds * 1e6,
         },
     }
