@@ -11,6 +11,7 @@ AQ_OK = 0
 AQ_F16, AQ_BF16, AQ_F32 = 0, 1, 2
 AQ_SCALE_TILE, AQ_SCALE_TOKEN = 0, 1
 AQ_OPT_PEER_POLL_LIMIT, AQ_OPT_GEMM_ROUNDING, AQ_OPT_GEMM_TILE, AQ_OPT_GEMM_SPLIT, AQ_OPT_DECODE_KERNEL = 1, 2, 3, 4, 5
+AQ_OPT_QUANT_FUSION_TILES = 6
 AQ_DECODE_KERNEL_AUTO, AQ_DECODE_KERNEL_CLUSTER, AQ_DECODE_KERNEL_STREAMK = 0, 1, 2
 AQ_GEMM_ROUNDING_FUSED, AQ_GEMM_ROUNDING_SEPARATE = 0, 1
 GEMM_TILES = {"auto": 0, "paired": 1, "narrow": 2, "wide": 4}
@@ -39,6 +40,8 @@ SIGNATURES = {
     "aq_allreduce_buffer_bytes": (_I64, [_I32, _I64]),
     "aq_allreduce_f32": (_INT, [_P, _P, _I64, _I32, _I32, _P, _I64, _P]),
     "aq_linear_allreduce": (_INT, [_P, _P, _INT, _I64, _P, _I32, _I32, _P, _INT, _P, _I32, _I32, _P, _I64, _P, _I64, _P]),
+    "aq_quant_linear": (_INT, [_P, _INT, _I64, _P, _I32, _I32, _P, _INT, _P, _P, _P, _P, _I64, _I32, _I32, _P, _I64, _P, _I64, _P]),
+    "aq_quant_linear_fused": (_INT, [_I64, _I32, _I32]),
     "aq_measure_int8_peak": (_INT, [_I32, _P, _P]),
     "aq_device_status": (_INT, [_P]),
 }

@@ -58,11 +58,13 @@ bool use_dependent_launch() {
 
 namespace {
 constexpr int64_t kDefaultPeerPollLimit = 1LL << 22;
+constexpr int64_t kDefaultQuantFusionTiles = 2400;
 std::atomic<int64_t> g_peer_poll_limit{kDefaultPeerPollLimit};
 std::atomic<int64_t> g_gemm_rounding{0};
 std::atomic<int64_t> g_gemm_tile{0};
 std::atomic<int64_t> g_gemm_split{0};
 std::atomic<int64_t> g_decode_kernel{0};
+std::atomic<int64_t> g_quant_fusion_tiles{kDefaultQuantFusionTiles};
 }  // namespace
 
 uint32_t peer_poll_limit() { return static_cast<uint32_t>(g_peer_poll_limit.load(std::memory_order_relaxed)); }
@@ -70,6 +72,7 @@ bool gemm_separate_rounding() { return g_gemm_rounding.load(std::memory_order_re
 int gemm_tile_option() { return static_cast<int>(g_gemm_tile.load(std::memory_order_relaxed)); }
 int gemm_split_option() { return static_cast<int>(g_gemm_split.load(std::memory_order_relaxed)); }
 int decode_kernel_option() { return static_cast<int>(g_decode_kernel.load(std::memory_order_relaxed)); }
+int64_t quant_fusion_tiles() { return g_quant_fusion_tiles.load(std::memory_order_relaxed); }
 
 namespace {
 
@@ -135,6 +138,10 @@ int aq_set_option(int option, int64_t value) {
                  static_cast<long long>(value));
       g_decode_kernel.store(value, std::memory_order_relaxed);
       return AQ_OK;
+    case AQ_OPT_QUANT_FUSION_TILES:
+      AQ_REQUIRE(value >= 0, "AQ_OPT_QUANT_FUSION_TILES must not be negative, got %lld", static_cast<long long>(value));
+      g_quant_fusion_tiles.store(value, std::memory_order_relaxed);
+      return AQ_OK;
     case AQ_OPT_GEMM_SPLIT:
       AQ_REQUIRE(value >= 0 && value <= 8, "AQ_OPT_GEMM_SPLIT must be 0 (automatic) or 1..8, got %lld",
                  static_cast<long long>(value));
@@ -157,6 +164,8 @@ int64_t aq_get_option(int option) {
       return g_gemm_split.load(std::memory_order_relaxed);
     case AQ_OPT_DECODE_KERNEL:
       return g_decode_kernel.load(std::memory_order_relaxed);
+    case AQ_OPT_QUANT_FUSION_TILES:
+      return g_quant_fusion_tiles.load(std::memory_order_relaxed);
     default:
       fail(AQ_ERR_INVALID, "unknown option %d", option);
       return AQ_ERR_INVALID;
@@ -258,11 +267,17 @@ struct LookAhead {
   int64_t bytes;
 };
 
+// Activations that are still to be quantized (per-token scales): xq / act_scales of the call are outputs.
+struct RawActivation {
+  const void* x;
+  int dtype;
+};
+
 static int linear_impl(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,
                        const void* prepared, int32_t n_j, int32_t n_k, const int32_t* u_metadata,
                        int schedule, int decode_splits, int out_dtype, void* out, void* workspace,
                        int64_t workspace_bytes, int32_t* acc_dump, const TensorParallelSum* tp,
-                       const LookAhead* ahead, void* stream) {
+                       const LookAhead* ahead, void* stream, const RawActivation* raw = nullptr) {
   AQ_REQUIRE(xq != nullptr && act_scales != nullptr && prepared != nullptr && out != nullptr,
              "xq, act_scales, prepared and out must not be NULL");
   AQ_REQUIRE(m >= 1, "x_int8 must have at least one row");
@@ -322,6 +337,18 @@ static int linear_impl(const int8_t* xq, const float* act_scales, int scale_mode
     a.tp_world = tp->world;
     a.ar_max_count = tp->max_count;
   }
+  if (raw != nullptr) {
+    // One launch where the small-CTA decode kernel quantizes its own activations, else the
+    // quantizer kernel into xq / act_scales first.
+    if (kernel == 4 && (raw->dtype == AQ_F16 || raw->dtype == AQ_BF16) && direct_decode_quantizes(m, n_j, n_k)) {
+      a.raw_x = raw->x;
+      a.raw_dtype = raw->dtype;
+    } else {
+      const int rc = launch_quantize(raw->x, raw->dtype, m, static_cast<int64_t>(n_k) * 64, nullptr, AQ_SCALE_TOKEN,
+                                     const_cast<int8_t*>(xq), const_cast<float*>(act_scales), s);
+      if (rc != AQ_OK) return rc;
+    }
+  }
   if (kernel == 4) return launch_direct_decode(a, s);
   if (kernel == 3) return launch_cluster_decode(a, s);
   if (kernel == 0) {
@@ -378,6 +405,39 @@ int aq_linear_allreduce(const int8_t* xq, const float* act_scales, int scale_mod
   const LookAhead ahead = {next_prepared, next_bytes};
   return linear_impl(xq, act_scales, scale_mode, m, prepared, n_j, n_k, u_metadata, AQ_SCHEDULE_AUTO, 0, out_dtype, out,
                      nullptr, 0, nullptr, &tp, &ahead, stream);
+}
+
+int aq_quant_linear(const void* x, int x_dtype, int64_t m, const void* prepared, int32_t n_j, int32_t n_k,
+                    const int32_t* u_metadata, int out_dtype, void* out, int8_t* xq, float* act_scales, void* workspace,
+                    int64_t workspace_bytes, int32_t rank, int32_t world, void* const* peer_buffers, int64_t max_count,
+                    const void* next_prepared, int64_t next_bytes, void* stream) {
+  AQ_REQUIRE(x != nullptr && aligned(x, 16), "x must be a 16-byte aligned device pointer");
+  AQ_REQUIRE(x_dtype == AQ_F16 || x_dtype == AQ_BF16 || x_dtype == AQ_F32, "x_dtype must be AQ_F16, AQ_BF16 or AQ_F32, got %d", x_dtype);
+  AQ_REQUIRE(next_bytes >= 0, "next_bytes must not be negative");
+  const RawActivation raw = {x, x_dtype};
+  const LookAhead ahead = {next_prepared, next_bytes};
+  if (peer_buffers == nullptr) {
+    return linear_impl(xq, act_scales, AQ_SCALE_TOKEN, m, prepared, n_j, n_k, u_metadata, AQ_SCHEDULE_AUTO, 0, out_dtype, out,
+                       workspace, workspace_bytes, nullptr, nullptr, &ahead, stream, &raw);
+  }
+  AQ_REQUIRE(world >= 2 && world <= allreduce_max_ranks(), "world must be 2..%d, got %d", allreduce_max_ranks(), world);
+  AQ_REQUIRE(rank >= 0 && rank < world, "rank must be in [0, world)");
+  AQ_REQUIRE(max_count >= 4 && (max_count & 3) == 0, "max_count must be a positive multiple of 4");
+  AQ_REQUIRE(m >= 1 && n_j > 0 && m * static_cast<int64_t>(n_j) * 64 <= max_count,
+             "the output (m x N values) must fit the exchange buffers (max_count)");
+  for (int r = 0; r < world; ++r) {
+    AQ_REQUIRE(peer_buffers[r] != nullptr && aligned(peer_buffers[r], 16), "peer_buffers[%d] must be a 16-byte aligned device pointer", r);
+  }
+  const int kernel = (m >= 1 && n_j > 0 && n_k > 0) ? choose_kernel(m, n_j, n_k, AQ_SCHEDULE_AUTO, 0) : -1;
+  AQ_REQUIRE(kernel == 3 || kernel == 4, "the fused tensor-parallel sum is only available where aq_linear_plan reports kernel 3");
+  const TensorParallelSum tp = {rank, world, peer_buffers, max_count};
+  return linear_impl(xq, act_scales, AQ_SCALE_TOKEN, m, prepared, n_j, n_k, u_metadata, AQ_SCHEDULE_AUTO, 0, out_dtype, out,
+                     nullptr, 0, nullptr, &tp, &ahead, stream, &raw);
+}
+
+int aq_quant_linear_fused(int64_t m, int32_t n_j, int32_t n_k) {
+  if (m < 1 || n_j <= 0 || n_k <= 0) return 0;
+  return choose_kernel(m, n_j, n_k, AQ_SCHEDULE_AUTO, 0) == 4 && direct_decode_quantizes(m, n_j, n_k) ? 1 : 0;
 }
 
 int aq_linear_decode_static(const int8_t* xq, const float* act_scales, int scale_mode, int64_t m,

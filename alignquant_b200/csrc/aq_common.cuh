@@ -83,6 +83,10 @@ struct LinearArgs {
   // next) that the decode kernels ask the L2 cache to fetch while they run; nullptr: none.
   const void* prefetch = nullptr;
   int64_t prefetch_bytes = 0;
+  // Unquantized activations (fp16 / bf16 rows) for a kernel that quantizes them itself; xq and
+  // act_scales are then outputs.  nullptr: the activations are in xq / act_scales already.
+  const void* raw_x = nullptr;
+  int raw_dtype = 0;
 };
 
 // Layout of a peer exchange buffer (shared by aq_allreduce.cu and the fused decode epilogue):
@@ -109,6 +113,7 @@ int take_cluster_decode_status();
 int launch_direct_decode(const LinearArgs& a, cudaStream_t stream);
 bool direct_decode_supported(int64_t m, int n_j, int n_k);
 int direct_decode_workers(int64_t m, int n_j, int n_k);
+bool direct_decode_quantizes(int64_t m, int n_j, int n_k);
 int take_direct_decode_status();
 
 // Persistent stream-K kernel for m <= 16 (needs a zeroed, self-cleaning workspace).
@@ -145,6 +150,7 @@ bool gemm_separate_rounding();
 int gemm_tile_option();   // AQ_GEMM_TILE_*
 int gemm_split_option();  // 0 = automatic, 1..8 forced
 int decode_kernel_option();  // AQ_DECODE_KERNEL_*
+int64_t quant_fusion_tiles();  // AQ_OPT_QUANT_FUSION_TILES
 // Whether kernels are launched with programmatic stream serialization (dependent
 // launch); on by default, ALIGNQUANT_B200_PDL=0 turns it off.
 bool use_dependent_launch();

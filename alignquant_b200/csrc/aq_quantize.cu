@@ -10,6 +10,7 @@
 // All are bandwidth-bound: 128-bit loads and stores, warp-shuffle reductions.
 #include "aq_common.cuh"
 #include "aq_ptx.cuh"
+#include "aq_quantize_math.cuh"
 
 namespace aq {
 namespace {
@@ -55,27 +56,11 @@ __device__ __forceinline__ void load16<float>(const float* p, float (&v)[16]) {
   }
 }
 
-__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
-  return (static_cast<uint32_t>(a) & 0xffu) | ((static_cast<uint32_t>(b) & 0xffu) << 8) |
-         ((static_cast<uint32_t>(c) & 0xffu) << 16) | ((static_cast<uint32_t>(d) & 0xffu) << 24);
-}
-
 // ---------------------------------------------------------------------------
 // AQ_SCALE_TOKEN: one CTA walks rows; pass 1 finds the row absmax, pass 2 divides and
 // rounds.  Rows of up to 8192 values stay in registers between the passes (two 16-value
 // chunks per thread); longer rows are read again (they are still in L1/L2).
 // ---------------------------------------------------------------------------
-
-// rint(v / scale) with IEEE division semantics at the cost of a multiply: v * (1/scale)
-// differs from the correctly rounded quotient by less than 2^-22 * |quotient| < 4e-5 for
-// |quotient| <= 128, so both round to the same integer unless the product lies within 1e-4
-// of a rounding boundary; only then is the division evaluated.
-__device__ __forceinline__ int quantize_token_value(float v, float scale, float inv_scale) {
-  const float t = __fmul_rn(v, inv_scale);
-  int r = __float2int_rn(t);
-  if (fabsf(t - static_cast<float>(r)) > 0.5f - 1.0e-4f || fabsf(t) > 128.0f) r = __float2int_rn(__fdiv_rn(v, scale));
-  return max(-127, min(127, r));
-}
 
 __device__ __forceinline__ uint4 quantize_chunk(const float (&v)[16], float scale, float inv_scale) {
   int r[16];
@@ -132,7 +117,7 @@ __global__ void __launch_bounds__(256) quantize_token_kernel(const T* __restrict
     float block_max = warp_max[0];
 #pragma unroll
     for (int w = 1; w < 8; ++w) block_max = fmaxf(block_max, warp_max[w]);
-    const float scale = fmaxf(__fdiv_rn(block_max, 127.0f), 1.0e-12f);
+    const float scale = token_scale_of(block_max);
     const float inv_scale = __fdiv_rn(1.0f, scale);
     if (threadIdx.x == 0) scales[row] = scale;
     int8_t* qr = q + row * k;
@@ -282,7 +267,7 @@ __global__ void __launch_bounds__(256) rmsnorm_quantize_kernel(const T* __restri
     float block_max = warp_max[0];
 #pragma unroll
     for (int w = 1; w < 8; ++w) block_max = fmaxf(block_max, warp_max[w]);
-    const float scale = fmaxf(__fdiv_rn(block_max, 127.0f), 1.0e-12f);
+    const float scale = token_scale_of(block_max);
     const float inv_scale = __fdiv_rn(1.0f, scale);
     if (threadIdx.x == 0) scales[row] = scale;
     int8_t* qr = q + row * k;

@@ -397,6 +397,88 @@ def alignquant_linear_allreduce(
     return out
 
 
+def quant_linear_is_fused(m: int, n_j: int, n_k: int) -> bool:
+    """Whether ``alignquant_quant_linear`` runs this problem (fp16 / bf16 rows) as one launch."""
+    return bool(_lib.load().aq_quant_linear_fused(int(m), int(n_j), int(n_k)))
+
+
+def alignquant_quant_linear(
+    activation: torch.Tensor,
+    weights: PreparedWeights,
+    u_metadata: torch.Tensor | None,
+    *,
+    output_dtype: torch.dtype = torch.float32,
+    out: torch.Tensor | None = None,
+    quantized: tuple[torch.Tensor, torch.Tensor] | None = None,
+    reducer=None,
+    prefetch: PreparedWeights | None = None,
+) -> torch.Tensor | None:
+    """Per-token activation quantizer and projection in one call (``aq_quant_linear``).
+
+    ``activation`` is ``[M, K]`` in fp16 / bf16 / fp32 (no input transform).  Same bits as
+    ``alignquant_activation_quantize_cuda(x, None, scale_mode="token")`` followed by
+    ``alignquant_linear_prepared`` (or ``alignquant_linear_allreduce`` when ``reducer`` is
+    given); one launch instead of two where ``quant_linear_is_fused`` says so.  ``quantized``
+    (int8 ``[M, K]``, float32 ``[M]``) receives the quantized activations; allocated when not
+    passed.  With ``reducer``: returns ``None`` where the fused sum does not apply, exactly as
+    ``alignquant_linear_allreduce`` does, and nothing has been enqueued then.
+    """
+    if output_dtype not in _DTYPE_CODES:
+        raise ValueError("Projection output_dtype must be torch.float32, torch.bfloat16 or torch.float16.")
+    _require_cuda(activation, "x")
+    if activation.dtype not in _DTYPE_CODES:
+        raise RuntimeError("x must be bf16, fp16, or fp32")
+    n_j, n_k = weights.n_j, weights.n_k
+    if activation.dim() != 2 or int(activation.size(0)) < 1 or int(activation.size(1)) != n_k * 64:
+        raise RuntimeError("x must be [M,K] with positive M and the weights' K")
+    x = activation.contiguous()
+    m, k = int(x.size(0)), int(x.size(1))
+    device = x.device
+    if weights.device != device:
+        raise RuntimeError("all inputs must share one CUDA device")
+    if reducer is not None and (m * n_j * 64 > reducer.max_count or linear_plan(m, n_j, n_k)["kernel"] != 3):
+        return None
+    meta = None
+    if u_metadata is not None:
+        _require_cuda(u_metadata, "u_metadata")
+        if u_metadata.dtype != torch.int32 or tuple(u_metadata.shape) != (n_j, 4, 64) or u_metadata.device != device:
+            raise RuntimeError("u_metadata must be int32 [N/64,4,64] on x's device")
+        meta = u_metadata.contiguous()
+    lib = _lib.load()
+    with torch.cuda.device(device):
+        if quantized is not None:
+            q, scales = quantized
+            if (q.dtype != torch.int8 or tuple(q.shape) != (m, k) or not q.is_contiguous() or scales.dtype != torch.float32
+                    or tuple(scales.shape) != (m,) or not scales.is_contiguous() or q.device != device or scales.device != device):
+                raise RuntimeError("quantized must be (contiguous int8 [M,K], contiguous float32 [M]) on x's device")
+        else:
+            q = torch.empty((m, k), dtype=torch.int8, device=device)
+            scales = torch.empty((m,), dtype=torch.float32, device=device)
+        if out is None:
+            out = torch.empty((m, n_j * 64), dtype=output_dtype, device=device)
+        elif out.dtype != output_dtype or tuple(out.shape) != (m, n_j * 64) or not out.is_contiguous():
+            raise RuntimeError("out must be a contiguous [M,N] tensor of output_dtype")
+        ws_bytes, workspace = 0, None
+        if reducer is None:
+            ws_bytes = int(lib.aq_linear_workspace_bytes(m, n_j, n_k, _lib.SCHEDULE_CODES["auto"], 0))
+            if ws_bytes < 0:
+                _lib.check(ws_bytes)
+            workspace = _workspace(device, ws_bytes) if ws_bytes else None
+        if prefetch is not None and prefetch.device != device:
+            raise RuntimeError("prefetch must name weights on the device of this call")
+        _lib.check(
+            lib.aq_quant_linear(
+                _ptr(x), _DTYPE_CODES[x.dtype], m, _ptr(weights.image), n_j, n_k, _ptr(meta), _DTYPE_CODES[output_dtype],
+                _ptr(out), _ptr(q), _ptr(scales), _ptr(workspace), ws_bytes,
+                0 if reducer is None else reducer.rank, 1 if reducer is None else reducer.world,
+                None if reducer is None else reducer.peer_array_pointer(), 0 if reducer is None else reducer.max_count,
+                None if prefetch is None else _ptr(prefetch.image),
+                0 if prefetch is None else int(prefetch.image.numel()), _stream(device),
+            )
+        )
+    return out
+
+
 _WORKSPACES: dict[tuple, torch.Tensor] = {}
 
 
@@ -559,6 +641,12 @@ def set_decode_kernel(cluster_only: bool = False, stream_k: bool = False) -> Non
     stream-K kernel for everything of at most 16 rows (``AQ_OPT_DECODE_KERNEL``); neither: automatic."""
     value = _lib.AQ_DECODE_KERNEL_STREAMK if stream_k else _lib.AQ_DECODE_KERNEL_CLUSTER if cluster_only else _lib.AQ_DECODE_KERNEL_AUTO
     _lib.check(_lib.load().aq_set_option(_lib.AQ_OPT_DECODE_KERNEL, value))
+
+
+def set_quant_fusion_tiles(tiles: int = 2400) -> None:
+    """Largest layer (in 64 x 64 tiles) for which ``alignquant_quant_linear`` runs as one launch; 0: never
+    (``AQ_OPT_QUANT_FUSION_TILES``)."""
+    _lib.check(_lib.load().aq_set_option(_lib.AQ_OPT_QUANT_FUSION_TILES, int(tiles)))
 
 
 def set_gemm_split(split: int = 0) -> None:

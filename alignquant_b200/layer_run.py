@@ -41,6 +41,10 @@ def main() -> None:
     ap.add_argument("--gemm-separate-rounding", action="store_true",
                     help="GEMM adds a tile with a separately rounded multiply and add (the reference kernels' order)")
     ap.add_argument("--cluster-decode", action="store_true", help="keep the register-staged decode kernel off")
+    ap.add_argument("--one-call", action="store_true",
+                    help="with --layers: quantizer and projection through alignquant_quant_linear (one launch where it applies)")
+    ap.add_argument("--quant-fusion-tiles", type=int, default=None,
+                    help="largest layer in tiles for which --one-call runs as one launch (AQ_OPT_QUANT_FUSION_TILES)")
     ap.add_argument("--lookahead", action="store_true",
                     help="with --layers: every projection names the next layer's weights as its L2 look-ahead")
     args = ap.parse_args()
@@ -52,6 +56,8 @@ def main() -> None:
     ext.set_gemm_tile(args.gemm_tile)
     ext.set_gemm_rounding(args.gemm_separate_rounding)
     ext.set_decode_kernel(cluster_only=args.cluster_decode)
+    if args.quant_fusion_tiles is not None:
+        ext.set_quant_fusion_tiles(args.quant_fusion_tiles)
     device = torch.device("cuda", 0)
     row_counts = [int(v) for v in str(args.rows).split(",")]
     if args.layers > 1:
@@ -113,9 +119,12 @@ def chain(args, ext, device, row_counts, synthetic_module_tensors, synthetic_act
 
         def sweep() -> None:
             for index, weights in enumerate(layers):
+                ahead = layers[(index + 1) % len(layers)] if args.lookahead else None
+                if args.one_call:
+                    ext.alignquant_quant_linear(x, weights, None, output_dtype=out_dtype, out=out, quantized=(xq, scales), prefetch=ahead)
+                    continue
                 if args.with_quantizer:
                     ext.alignquant_activation_quantize_cuda(x, None, scale_mode=args.scale_mode, out=(xq, scales))
-                ahead = layers[(index + 1) % len(layers)] if args.lookahead else None
                 ext.alignquant_linear_prepared(xq, scales, weights, None, schedule=args.schedule, scale_mode=args.scale_mode,
                                                output_dtype=out_dtype, out=out, prefetch=ahead)
 
@@ -140,6 +149,7 @@ def chain(args, ext, device, row_counts, synthetic_module_tensors, synthetic_act
             "plan": ext.linear_plan(rows, args.n // 64, args.k // 64, schedule=args.schedule),
             "us_per_layer": seconds * 1e6, "weight_gbs": weight_bytes / args.layers / seconds / 1e9,
             "scale_mode": args.scale_mode, "out_dtype": args.out_dtype, "lookahead": bool(args.lookahead),
+            "one_call": bool(args.one_call), "one_launch": bool(args.one_call and ext.quant_linear_is_fused(rows, args.n // 64, args.k // 64)),
         }), flush=True)
 
 

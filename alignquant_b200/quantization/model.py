@@ -267,11 +267,9 @@ class _ProjectionGroupRuntime:
                 raise ValueError("Activation must contain at least one row.")
             flat = activation.reshape(rows, width)
             ready = getattr(activation, "_alignquant_quantized", None)  # left by AlignQuantRMSNorm
-            if (ready is not None and self.scale_mode == "token" and self.v_metadata is None
+            if not (ready is not None and self.scale_mode == "token" and self.v_metadata is None
                     and tuple(ready[0].shape) == (rows, width)):
-                qx, scales = ready
-            else:
-                qx, scales = _ext.alignquant_activation_quantize_cuda(flat, self.v_metadata, scale_mode=self.scale_mode)
+                ready = None
             # Low-precision kernel output only for bias-free groups, as in the reference
             # (model.py:343-349): with a bias the FP32 result is kept through the bias add and
             # rounded once at the end.  Row-parallel partials stay FP32 for the sum over ranks.
@@ -280,18 +278,34 @@ class _ProjectionGroupRuntime:
             combined = None
             self.sum_fused = False
             reducer = getattr(self, "peer_allreduce", None)
-            if self.row_parallel and reducer is not None:
-                # decode sizes: projection and the sum over the ranks in one kernel
-                combined = _ext.alignquant_linear_allreduce(
-                    qx, scales, self.weights, self.u_metadata, reducer, scale_mode=self.scale_mode, output_dtype=out_dtype,
-                    prefetch=self.next_weights,
-                )
-                self.sum_fused = combined is not None
-            if combined is None:
-                combined = _ext.alignquant_linear_prepared(
-                    qx, scales, self.weights, self.u_metadata, scale_mode=self.scale_mode, output_dtype=out_dtype,
-                    prefetch=self.next_weights,
-                )
+            one_call = ready is None and self.scale_mode == "token" and self.v_metadata is None
+            if one_call:
+                # quantizer and projection (and, at decode sizes, the sum over the ranks) as one call:
+                # one launch where the decode kernel quantizes its own rows, two otherwise
+                if self.row_parallel and reducer is not None:
+                    combined = _ext.alignquant_quant_linear(flat, self.weights, self.u_metadata, output_dtype=out_dtype,
+                                                            reducer=reducer, prefetch=self.next_weights)
+                    self.sum_fused = combined is not None
+                if combined is None:
+                    combined = _ext.alignquant_quant_linear(flat, self.weights, self.u_metadata, output_dtype=out_dtype,
+                                                            prefetch=self.next_weights)
+            else:
+                if ready is not None:
+                    qx, scales = ready
+                else:
+                    qx, scales = _ext.alignquant_activation_quantize_cuda(flat, self.v_metadata, scale_mode=self.scale_mode)
+                if self.row_parallel and reducer is not None:
+                    # decode sizes: projection and the sum over the ranks in one kernel
+                    combined = _ext.alignquant_linear_allreduce(
+                        qx, scales, self.weights, self.u_metadata, reducer, scale_mode=self.scale_mode, output_dtype=out_dtype,
+                        prefetch=self.next_weights,
+                    )
+                    self.sum_fused = combined is not None
+                if combined is None:
+                    combined = _ext.alignquant_linear_prepared(
+                        qx, scales, self.weights, self.u_metadata, scale_mode=self.scale_mode, output_dtype=out_dtype,
+                        prefetch=self.next_weights,
+                    )
             if tuple(combined.shape) != (rows, self.out_features):
                 raise RuntimeError(
                     f"Projection group {self.group_id} returned {tuple(combined.shape)}, "

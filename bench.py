@@ -380,6 +380,9 @@ def run_native(args) -> None:
         step_bytes += call_bytes(m, n, k, weight_bytes[(li, name)], out_bytes[name])
         linear_bytes += weight_bytes[(li, name)] + m * k + 4 * m + m * n * out_bytes[name]
     pairs_per_step = len(calls)
+    # pairs that run as ONE launch (the decode kernel quantizes its own rows)
+    one_launch_pairs = sum(1 for m, _, name in calls
+                           if ext.quant_linear_is_fused(m, local_shape[name][0] // 64, local_shape[name][1] // 64))
     allreduces_per_step = sum(1 for _, _, name in calls if GROUPS[name][2] == "k")
 
     separate_sums = [0]  # all-reduce kernels of our own launched by the last sweep (not fused ones, not NCCL's)
@@ -390,7 +393,20 @@ def run_native(args) -> None:
             axis = GROUPS[name][2]
             weights, ahead = layers[li][name], next_weights(position)
             if with_quantizer:
-                ext.alignquant_activation_quantize_cuda(acts[(m, name)], None, scale_mode="token", out=qbuf[(m, name)])
+                # quantizer + projection (+ sum over the ranks) through the one-call entry point: one launch
+                # where the decode kernel quantizes its own rows, the quantizer kernel and the projection otherwise
+                fused_sum = with_allreduce and reducer is not None and axis == "k"
+                y = ext.alignquant_quant_linear(acts[(m, name)], weights, None, output_dtype=out_dtype[name], out=outs[(m, name)],
+                                                quantized=qbuf[(m, name)], reducer=reducer if fused_sum else None, prefetch=ahead)
+                if y is None:  # the fused sum does not take this shape
+                    ext.alignquant_quant_linear(acts[(m, name)], weights, None, output_dtype=out_dtype[name],
+                                                out=outs[(m, name)], quantized=qbuf[(m, name)], prefetch=ahead)
+                    if with_allreduce and world > 1 and axis == "k":
+                        all_reduce(outs[(m, name)])
+                        separate_sums[0] += 1 if reducer is not None else 0
+                elif with_allreduce and world > 1 and axis == "k" and not fused_sum:
+                    all_reduce(outs[(m, name)])
+                continue
             xq, a_s = qbuf[(m, name)]
             if with_allreduce and reducer is not None and axis == "k" and ext.alignquant_linear_allreduce(
                     xq, a_s, weights, None, reducer, scale_mode="token", output_dtype=out_dtype[name], out=outs[(m, name)],
@@ -508,14 +524,11 @@ def run_native(args) -> None:
         m, li, name = calls[position]
         axis = GROUPS[name][2]
         weights, ahead = layers[li][name], next_weights(position)
-        xq, a_s = ext.alignquant_activation_quantize_cuda(x, None, scale_mode="token")
         y = None
         if reducer is not None and axis == "k":
-            y = ext.alignquant_linear_allreduce(xq, a_s, weights, None, reducer, scale_mode="token",
-                                                output_dtype=out_dtype[name], prefetch=ahead)
+            y = ext.alignquant_quant_linear(x, weights, None, output_dtype=out_dtype[name], reducer=reducer, prefetch=ahead)
         if y is None:
-            y = ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token", output_dtype=out_dtype[name],
-                                               prefetch=ahead)
+            y = ext.alignquant_quant_linear(x, weights, None, output_dtype=out_dtype[name], prefetch=ahead)
             if world > 1 and axis == "k":
                 all_reduce(y)
         return y
@@ -606,6 +619,8 @@ def run_native(args) -> None:
             "lookahead": ("every projection asks the L2 to fetch the next projection's image while it runs (aq_linear_ahead)"
                           if lookahead else "off"),
             "parallelism": f"tp{world}",
+            "pairs": (f"each quantizer + projection pair is one call of aq_quant_linear; {one_launch_pairs} of {pairs_per_step} "
+                      "pairs per step run as one launch (the decode kernel quantizes its own rows), the others as two"),
             "launch": launch_mode + ("" if world == 1 else
                                      f" + sum over ranks fused into the GEMV epilogue (peer memory; {own_sum_launches} of "
                                      f"{allreduces_per_step} sums per step as a separate peer-memory kernel)"
@@ -614,7 +629,7 @@ def run_native(args) -> None:
         "clocks": clocks.result,
         "e2e": {"value": total_bytes / e2e_seconds / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "launch": e2e_mode},
-        "gpu_launches": (2 * pairs_per_step + own_sum_launches) * args.steps,
+        "gpu_launches": (2 * pairs_per_step - one_launch_pairs + own_sum_launches) * args.steps,
         "roofline": {
             "kernel": ("cluster_decode_kernel" if args.cluster_decode else "direct_decode_kernel + cluster_decode_kernel") +
                       " (packed W4/W8 GEMV, M<=16; mean over the sweep's launches)",

@@ -80,6 +80,11 @@ AQ_API int aq_version(void);
  *                           kernel behind aq_linear_decode_static; the automatic choice no longer
  *                           takes it where another kernel applies).  For tests and measurements;
  *                           changes the FP32 summation order as aq_linear_plan reports.
+ *   AQ_OPT_QUANT_FUSION_TILES  aq_quant_linear runs as one launch only for layers of at most this
+ *                           many 64 x 64 tiles (0: never; default 2400).  While a separate quantizer
+ *                           runs, the projection that follows is already fetching its weights, so
+ *                           for a layer of several megabytes the two launches are the faster form;
+ *                           for a megabyte or two (shards under tensor parallelism) one launch is.
  * aq_set_option returns AQ_OK or AQ_ERR_INVALID; aq_get_option the value or AQ_ERR_INVALID.
  */
 #define AQ_OPT_PEER_POLL_LIMIT 1
@@ -87,6 +92,7 @@ AQ_API int aq_version(void);
 #define AQ_OPT_GEMM_TILE 3
 #define AQ_OPT_GEMM_SPLIT 4
 #define AQ_OPT_DECODE_KERNEL 5
+#define AQ_OPT_QUANT_FUSION_TILES 6
 #define AQ_DECODE_KERNEL_AUTO 0
 #define AQ_DECODE_KERNEL_CLUSTER 1
 #define AQ_DECODE_KERNEL_STREAMK 2
@@ -311,6 +317,37 @@ AQ_API int aq_linear_allreduce(const int8_t* xq, const float* act_scales, int sc
                                int64_t max_count, const void* next_prepared, int64_t next_bytes, void* stream);
 AQ_API int aq_allreduce_f32(const float* partial, float* out, int64_t count, int32_t rank, int32_t world,
                             void* const* peer_buffers, int64_t max_count, void* stream);
+
+/*
+ * The per-token activation quantizer and the projection as ONE call, optionally with the sum
+ * over the tensor-parallel ranks: what the reference's quantized module does per projection
+ * group with two extension calls (alignquant/quantization/model.py:329-350: quantizer, then
+ * linear).  Same results, bit for bit, as
+ *   aq_quantize_act(x, x_dtype, m, 64 * n_k, NULL, AQ_SCALE_TOKEN, xq, act_scales)  followed by
+ *   aq_linear_ahead(xq, act_scales, AQ_SCALE_TOKEN, ...)  or  aq_linear_allreduce(...),
+ * and xq / act_scales hold the quantized activations afterwards in either case.  Where the
+ * decode kernel of many small CTAs takes the problem and there is ONE row of fp16 / bf16
+ * activations (aq_quant_linear_fused returns 1), both run as one launch: every CTA of that kernel
+ * reads the whole row anyway, so it finds the row's maximum and rounds the row into its shared
+ * memory itself; a launch, its dependency latency and a round trip of the int8 row through the
+ * L2 go away.  (The rounding is then repeated on every SM, which at more rows costs more than
+ * the launch it saves.)  Everywhere else the call enqueues the quantizer kernel and then the
+ * projection.
+ *   x            x_dtype [m][64 * n_k] row-major, no input transform (identity V)
+ *   xq, act_scales  int8 [m][64 * n_k] and float [m]: outputs (and the projection's operands)
+ *   workspace    as for aq_linear (aq_linear_workspace_bytes with the automatic schedule)
+ *   peer_buffers NULL: no sum (rank / world / max_count ignored).  Otherwise as for
+ *                aq_linear_allreduce, with the same restriction (AQ_ERR_INVALID where
+ *                aq_linear_plan does not report kernel 3).
+ *   next_prepared / next_bytes  look-ahead as in aq_linear_ahead (NULL / 0: none)
+ */
+AQ_API int aq_quant_linear(const void* x, int x_dtype, int64_t m, const void* prepared, int32_t n_j, int32_t n_k,
+                           const int32_t* u_metadata, int out_dtype, void* out, int8_t* xq, float* act_scales,
+                           void* workspace, int64_t workspace_bytes, int32_t rank, int32_t world,
+                           void* const* peer_buffers, int64_t max_count, const void* next_prepared,
+                           int64_t next_bytes, void* stream);
+/* 1 if aq_quant_linear runs this problem (fp16 / bf16 activations) as one launch, else 0. */
+AQ_API int aq_quant_linear_fused(int64_t m, int32_t n_j, int32_t n_k);
 
 /*
  * Measurement aid: how fast this GPU's tensor cores execute tcgen05.mma kind::i8 when nothing

@@ -130,3 +130,36 @@ def test_fused_projection_and_rank_sum_with_a_played_peer(peers, m):
     out = torch.zeros((m, n), device="cuda")
     assert fused(out) == 0, _lib.last_error()
     assert lib.aq_device_status(ctypes.c_void_p(stream)) == -4 and "timed out" in _lib.last_error()
+
+
+@pytest.mark.parametrize("m", [1, 4, 7])
+def test_quantizer_projection_and_rank_sum_in_one_call_with_a_played_peer(peers, m):
+    """aq_quant_linear with exchange buffers: quantizer, projection and the sum over the ranks; one
+    launch for one row where the small-CTA kernel applies, two otherwise; same bits."""
+    from alignquant_b200 import _lib
+
+    lib, ext, buffers, array, max_count = peers
+    n, k = 3072, 1536  # a row-parallel shard: the small-CTA decode kernel carries epilogue and quantizer
+    n_j, n_k = n // 64, k // 64
+    assert ext.linear_plan(m, n_j, n_k)["kernel"] == 3 and ext.quant_linear_is_fused(m, n_j, n_k) == (m == 1)
+    packed, *_ = oc.synthetic_layer(n, k, seed=6)
+    weights, _ = helpers.prepare_layer(packed, n_k)
+    xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=m), torch.float16)
+    ref_q, ref_s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode="token")
+    own = ext.alignquant_linear_prepared(ref_q, ref_s, weights, None, scale_mode="token")
+    gen = torch.Generator(device="cuda").manual_seed(m)
+    stream = torch.cuda.current_stream().cuda_stream
+    q = torch.zeros((m, k), dtype=torch.int8, device="cuda")
+    s = torch.zeros((m,), device="cuda")
+    for call in (1, 2):
+        peer = torch.randn((m, n), generator=gen, device="cuda")
+        _play_peer(buffers[0], max_count, call, 1, peer)
+        out = torch.full((m, n), float("nan"), device="cuda")
+        status = lib.aq_quant_linear(
+            ctypes.c_void_p(xt.data_ptr()), _lib.AQ_F16, m, ctypes.c_void_p(weights.image.data_ptr()), n_j, n_k, None,
+            _lib.AQ_F32, ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(q.data_ptr()), ctypes.c_void_p(s.data_ptr()),
+            None, 0, 0, WORLD, ctypes.cast(array, ctypes.c_void_p), max_count, None, 0, ctypes.c_void_p(stream))
+        assert status == 0, _lib.last_error()
+        ext.device_status()
+        assert torch.equal(out, own + peer), f"call {call}"
+        assert torch.equal(q, ref_q) and torch.equal(s, ref_s)

@@ -272,6 +272,73 @@ def test_reference_fixture_end_to_end(ext, golden_dir, name):
     assert np.allclose(out2.cpu().numpy(), g["y"], rtol=REL, atol=ABS)
 
 
+@pytest.fixture
+def always_one_launch(ext):
+    """aq_quant_linear as one launch wherever the kernel can do it, whatever the layer's size."""
+    ext.set_quant_fusion_tiles(1 << 40)
+    yield
+    ext.set_quant_fusion_tiles()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,k,m", [(3072, 3072, 1), (5120, 3072, 1), (640, 3072, 1), (3072, 384, 1), (3072, 3072, 2),
+                                   (16384, 1024, 1), (3072, 8192, 4), (256, 512, 1), (5120, 3072, 40)])
+def test_quantizer_and_projection_in_one_call(ext, always_one_launch, n, k, m, dtype):
+    """alignquant_quant_linear: the bits of quantizer + projection, whether it runs as one launch (the
+    small-CTA decode kernel quantizing its own row: one fp16 / bf16 row) or as two."""
+    n_j, n_k = n // 64, k // 64
+    packed, _, tiles, scales = oc.synthetic_layer(n, k, seed=n + k)
+    weights, _ = helpers.prepare_layer(packed, n_k)
+    xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=m + n), dtype)
+    fused = ext.quant_linear_is_fused(m, n_j, n_k)
+    assert fused == (m == 1 and (n, k) in ((3072, 3072), (5120, 3072), (640, 3072), (3072, 384)))
+    ref_q, ref_s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode="token")
+    for out_dtype in (torch.float32, torch.float16):
+        want = ext.alignquant_linear_prepared(ref_q, ref_s, weights, None, scale_mode="token", output_dtype=out_dtype)
+        q = torch.full((m, k), 99, dtype=torch.int8, device="cuda")
+        s = torch.full((m,), float("nan"), device="cuda")
+        for _ in range(2):
+            got = ext.alignquant_quant_linear(xt, weights, None, output_dtype=out_dtype, quantized=(q, s), prefetch=weights)
+            ext.device_status()
+            assert torch.equal(got, want)
+            assert torch.equal(q, ref_q) and torch.equal(s, ref_s)
+    # the quantized rows against the oracle, the result against the FP64 reference
+    q_ref, s_ref = oc.a8_token_quantize(xt.float().cpu().numpy())
+    assert np.array_equal(ref_q.cpu().numpy(), q_ref) and np.array_equal(ref_s.cpu().numpy(), s_ref)
+    if m <= 8:
+        a_mk = oc.expand_act_scales(s_ref, m, n_k, "token")
+        y64 = oc.dequant_matmul_fp64(q_ref, a_mk, tiles, scales)
+        got = ext.alignquant_quant_linear(xt, weights, None)
+        assert np.allclose(got.cpu().numpy(), y64, rtol=REL, atol=ABS)
+
+
+def test_one_launch_only_for_layers_up_to_the_tile_limit(ext):
+    assert ext.quant_linear_is_fused(1, 48, 24) and ext.quant_linear_is_fused(1, 48, 48)  # 1152 and 2304 tiles
+    assert not ext.quant_linear_is_fused(1, 80, 48) and not ext.quant_linear_is_fused(2, 48, 24)  # 3840 tiles; two rows
+    ext.set_quant_fusion_tiles(0)
+    try:
+        assert not ext.quant_linear_is_fused(1, 48, 24)
+    finally:
+        ext.set_quant_fusion_tiles()
+
+
+def test_quantizer_and_projection_in_one_call_with_output_transform(ext):
+    from alignquant_b200.quantization.exact import metadata_stack
+
+    n, k, m = 3072, 3072, 1
+    n_j, n_k = n // 64, k // 64
+    packed, *_ = oc.synthetic_layer(n, k, seed=77)
+    weights, _ = helpers.prepare_layer(packed, n_k)
+    u_meta = metadata_stack([(j * 5) % 9 - 1 for j in range(n_j)], torch.device("cuda"))  # identity and non-identity rows
+    xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=9), torch.bfloat16)
+    assert ext.quant_linear_is_fused(m, n_j, n_k)
+    q, s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode="token")
+    want = ext.alignquant_linear_prepared(q, s, weights, u_meta, scale_mode="token")
+    got = ext.alignquant_quant_linear(xt, weights, u_meta)
+    ext.device_status()
+    assert torch.equal(got, want)
+
+
 def test_reference_signature_caches_the_image_of_long_lived_tensors(ext, golden_dir, monkeypatch):
     """The reference-signature call re-lays-out the weights once for tensors that stay alive, also
     when one of them is not contiguous; a new tensor object is a new layer."""

@@ -147,6 +147,12 @@ def _patch(monkeypatch):
         a = oc.expand_act_scales(scales.numpy(), xq.shape[0], weights.n_k, "token")
         return torch.from_numpy(oc.dequant_matmul_fp64(xq.numpy(), a, weights.tiles, weights.scales)).to(output_dtype)
 
+    def quant_linear(x, weights, u_metadata, *, output_dtype=torch.float32, reducer=None, **_):
+        if reducer is not None:
+            return None  # no peer-memory kernels on the CPU: the glue falls back to dist.all_reduce
+        return linear(*quantize(x, None), weights, u_metadata, output_dtype=output_dtype)
+
+    monkeypatch.setattr(glue._ext, "alignquant_quant_linear", quant_linear)
     monkeypatch.setattr(glue._ext, "prepare_weights", prepare)
     monkeypatch.setattr(glue._ext, "alignquant_activation_quantize_cuda", quantize)
     monkeypatch.setattr(glue._ext, "alignquant_linear_prepared", linear)
