@@ -75,10 +75,10 @@ def main() -> int:
             ok = False
             print(f"rank {rank}: fused projection + sum differs from the two-kernel path (m = {m})", file=sys.stderr)
     for m in (1, 4, 9):  # quantizer + projection + sum in one call (one launch at one row)
-        x = synthetic_activation(m, k, seed=300 + rank + m, device=device)
-        xq, a_s = ext.alignquant_activation_quantize_cuda(x, None, scale_mode="token")
-        separate = reducer(ext.alignquant_linear_prepared(xq, a_s, weights, None, scale_mode="token"))
-        one_call = ext.alignquant_quant_linear(x, weights, None, reducer=reducer)
+        raw = synthetic_activation(m, k, seed=300 + rank + m, device=device)
+        raw_q, raw_s = ext.alignquant_activation_quantize_cuda(raw, None, scale_mode="token")
+        separate = reducer(ext.alignquant_linear_prepared(raw_q, raw_s, weights, None, scale_mode="token"))
+        one_call = ext.alignquant_quant_linear(raw, weights, None, reducer=reducer)
         torch.cuda.synchronize()
         if one_call is None or not torch.equal(one_call, separate):
             ok = False

@@ -93,14 +93,26 @@ def test_peer_sum_gives_up_when_the_peer_never_arrives_and_recovers(peers):
         assert torch.equal(out, partial + peer), f"call {call}"  # rank order: own value first
 
 
+@pytest.fixture(params=["small-CTA kernel", "ring kernel"])
+def decode_kernel(request):
+    """Both decode kernels carry the fused epilogue; the ring kernel is forced through the option."""
+    from alignquant_b200.kernels.cuda import extension as ext
+
+    ext.load_extension()
+    ext.set_decode_kernel(cluster_only=request.param == "ring kernel")
+    yield request.param
+    ext.set_decode_kernel()
+
+
 @pytest.mark.parametrize("m", [1, 7, 16, 24])
-def test_fused_projection_and_rank_sum_with_a_played_peer(peers, m):
+def test_fused_projection_and_rank_sum_with_a_played_peer(peers, decode_kernel, m):
     from alignquant_b200 import _lib
 
     lib, ext, buffers, array, max_count = peers
-    n, k = 2048, 512  # enough tile rows for the cluster decode kernel that carries the fused epilogue
+    n, k = 2048, 512  # a row-parallel shard; both decode kernels take it
     n_j, n_k = n // 64, k // 64
-    assert ext.linear_plan(m, n_j, n_k)["kernel"] == 3
+    plan = ext.linear_plan(m, n_j, n_k)
+    assert plan["kernel"] == 3 and (plan["splits"] > 1) == (decode_kernel == "ring kernel")
     packed, _, tiles, scales = oc.synthetic_layer(n, k, seed=5)
     weights, _ = helpers.prepare_layer(packed, n_k)
     xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=m), torch.float16)
