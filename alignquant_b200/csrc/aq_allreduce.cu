@@ -87,32 +87,55 @@ __global__ void __launch_bounds__(kThreads) allreduce_push_kernel(const float* _
   float4* dst = reinterpret_cast<float4*>(out);
   for (int64_t i = g_begin + threadIdx.x; i < g_end; i += kThreads) {
     const float4 own = src[i];
-    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (int r = 0; r < world; ++r) {
-      float4 v = own;
-      if (r != rank) {
-        const uint4* unit = recv + r * rank_stride + 2 * i;
-        uint4 lo = ld_volatile_v4(unit);
-        uint4 hi = ld_volatile_v4(unit + 1);
-        uint32_t polls = 0;
-        while (lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch) {
-          if (++polls >= poll_limit) {
-            atomicCAS(&g_allreduce_status, 0, 1 + r);
-            break;
-          }
-          if (polls > 64) __nanosleep(100);
-          lo = ld_volatile_v4(unit);
-          hi = ld_volatile_v4(unit + 1);
-        }
-        v = make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z));
+    // the peers' units are requested together and re-requested only where a tag is still old
+    const uint4* const units = recv + 2 * i;
+    uint4 lo[kMaxRanks], hi[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      lo[r] = hi[r] = make_uint4(0u, epoch, 0u, epoch);
+      if (r < world && r != rank) {
+        lo[r] = ld_volatile_v4(units + r * rank_stride);
+        hi[r] = ld_volatile_v4(units + r * rank_stride + 1);
       }
-      if (r == 0) {
-        acc = v;
-      } else {
-        acc.x = __fadd_rn(acc.x, v.x);
-        acc.y = __fadd_rn(acc.y, v.y);
-        acc.z = __fadd_rn(acc.z, v.z);
-        acc.w = __fadd_rn(acc.w, v.w);
+    }
+    for (uint32_t polls = 0;;) {
+      bool complete = true;
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (lo[r].y != epoch || lo[r].w != epoch || hi[r].y != epoch || hi[r].w != epoch) {
+          complete = false;
+          lo[r] = ld_volatile_v4(units + r * rank_stride);
+          hi[r] = ld_volatile_v4(units + r * rank_stride + 1);
+        }
+      }
+      if (complete) break;
+      if (++polls >= poll_limit) {
+        int late = 0;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+          const bool old = lo[r].y != epoch || lo[r].w != epoch || hi[r].y != epoch || hi[r].w != epoch;
+          late = (old && late == 0) ? 1 + r : late;
+        }
+        if (late != 0) atomicCAS(&g_allreduce_status, 0, late);
+        break;
+      }
+      if (polls > 64) __nanosleep(100);
+    }
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      if (r < world) {
+        const float4 v = r == rank ? own
+                                   : make_float4(__uint_as_float(lo[r].x), __uint_as_float(lo[r].z), __uint_as_float(hi[r].x),
+                                                 __uint_as_float(hi[r].z));
+        if (r == 0) {
+          acc = v;
+        } else {
+          acc.x = __fadd_rn(acc.x, v.x);
+          acc.y = __fadd_rn(acc.y, v.y);
+          acc.z = __fadd_rn(acc.z, v.z);
+          acc.w = __fadd_rn(acc.w, v.w);
+        }
       }
     }
     dst[i] = acc;

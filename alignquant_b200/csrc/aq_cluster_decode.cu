@@ -463,28 +463,48 @@ __global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) clu
         const int row = split + split_k * (warp + it * kWarps);
         if (row < rows) {
           const int64_t e = static_cast<int64_t>(row) * n_cols + static_cast<int64_t>(j) * kTile + lane;
-          float lo = 0.0f, hi = 0.0f;
-          for (int r = 0; r < p.tp_world; ++r) {
-            float a = own_lo[it], b = own_hi[it];
-            if (r != p.tp_rank) {
-              const uint8_t* units = p.peers.buffer[p.tp_rank] + kArHeaderBytes + (area + r * p.ar_max_count + e) * 8;
-              uint2 ua = ld_volatile_v2(units);
-              uint2 ub = ld_volatile_v2(units + 32 * 8);
-              uint32_t polls = 0;
-              while (ua.y != epoch || ub.y != epoch) {
-                if (++polls >= p.ar_poll_limit) {
-                  atomicCAS(&g_cluster_decode_status, 0, 40 + r);
-                  break;
-                }
-                if (polls > 64) __nanosleep(100);
-                ua = ld_volatile_v2(units);
-                ub = ld_volatile_v2(units + 32 * 8);
-              }
-              a = __uint_as_float(ua.x);
-              b = __uint_as_float(ub.x);
+          // the peers' units are requested together and re-requested only where the tag is still
+          // old: one L2 round trip for all ranks that have delivered, not one per rank
+          const uint8_t* const mine = p.peers.buffer[p.tp_rank] + kArHeaderBytes + (area + e) * 8;
+          const int64_t rank_stride = p.ar_max_count * 8;
+          uint2 ua[kArMaxRanks], ub[kArMaxRanks];
+#pragma unroll
+          for (int r = 0; r < kArMaxRanks; ++r) {
+            ua[r] = ub[r] = make_uint2(0u, epoch);
+            if (r < p.tp_world && r != p.tp_rank) {
+              ua[r] = ld_volatile_v2(mine + r * rank_stride);
+              ub[r] = ld_volatile_v2(mine + r * rank_stride + 32 * 8);
             }
-            lo = r == 0 ? a : __fadd_rn(lo, a);
-            hi = r == 0 ? b : __fadd_rn(hi, b);
+          }
+          for (uint32_t polls = 0;;) {
+            bool complete = true;
+#pragma unroll
+            for (int r = 0; r < kArMaxRanks; ++r) {
+              if (ua[r].y != epoch || ub[r].y != epoch) {
+                complete = false;
+                ua[r] = ld_volatile_v2(mine + r * rank_stride);
+                ub[r] = ld_volatile_v2(mine + r * rank_stride + 32 * 8);
+              }
+            }
+            if (complete) break;
+            if (++polls >= p.ar_poll_limit) {
+              int late = 0;
+#pragma unroll
+              for (int r = 0; r < kArMaxRanks; ++r) late = ((ua[r].y != epoch || ub[r].y != epoch) && late == 0) ? 40 + r : late;
+              if (late != 0) atomicCAS(&g_cluster_decode_status, 0, late);
+              break;
+            }
+            if (polls > 64) __nanosleep(100);
+          }
+          float lo = 0.0f, hi = 0.0f;
+#pragma unroll
+          for (int r = 0; r < kArMaxRanks; ++r) {
+            if (r < p.tp_world) {
+              const float a = r == p.tp_rank ? own_lo[it] : __uint_as_float(ua[r].x);
+              const float b = r == p.tp_rank ? own_hi[it] : __uint_as_float(ub[r].x);
+              lo = r == 0 ? a : __fadd_rn(lo, a);
+              hi = r == 0 ? b : __fadd_rn(hi, b);
+            }
           }
           store_any(p.out, p.out_dtype, e, lo);
           store_any(p.out, p.out_dtype, e + 32, hi);

@@ -91,24 +91,43 @@ __device__ __forceinline__ float sum_over_ranks(const DirectParams& p, uint32_t 
     st_volatile_v2(p.peers.buffer[peer] + kArHeaderBytes + (area + p.tp_rank * p.ar_max_count + e) * 8,
                    __float_as_uint(own), epoch);
   }
-  float total = 0.0f;
-  for (int r = 0; r < p.tp_world; ++r) {
-    float v = own;
-    if (r != p.tp_rank) {
-      const uint8_t* unit = p.peers.buffer[p.tp_rank] + kArHeaderBytes + (area + r * p.ar_max_count + e) * 8;
-      uint2 u = ld_volatile_v2(unit);
-      uint32_t polls = 0;
-      while (u.y != epoch) {
-        if (++polls >= p.ar_poll_limit) {
-          atomicCAS(&g_direct_decode_status, 0, 40 + r);
-          break;
-        }
-        if (polls > 64) __nanosleep(100);
-        u = ld_volatile_v2(unit);
+  // The peers' units are requested together and re-requested only where the tag is still old: one
+  // L2 round trip for all ranks that have delivered, not one per rank (measured: the sum cost
+  // about 0.85 us per rank when the loads were issued one after the other).
+  const uint8_t* const mine = p.peers.buffer[p.tp_rank] + kArHeaderBytes + (area + e) * 8;
+  const int64_t rank_stride = p.ar_max_count * 8;
+  uint2 unit[kArMaxRanks];
+#pragma unroll
+  for (int r = 0; r < kArMaxRanks; ++r) {
+    unit[r] = make_uint2(0u, epoch);
+    if (r < p.tp_world && r != p.tp_rank) unit[r] = ld_volatile_v2(mine + r * rank_stride);
+  }
+  for (uint32_t polls = 0;;) {
+    bool complete = true;
+#pragma unroll
+    for (int r = 0; r < kArMaxRanks; ++r) {
+      if (unit[r].y != epoch) {
+        complete = false;
+        unit[r] = ld_volatile_v2(mine + r * rank_stride);
       }
-      v = __uint_as_float(u.x);
     }
-    total = r == 0 ? v : __fadd_rn(total, v);
+    if (complete) break;
+    if (++polls >= p.ar_poll_limit) {
+      int late = 0;
+#pragma unroll
+      for (int r = 0; r < kArMaxRanks; ++r) late = (unit[r].y != epoch && late == 0) ? 40 + r : late;
+      if (late != 0) atomicCAS(&g_direct_decode_status, 0, late);
+      break;
+    }
+    if (polls > 64) __nanosleep(100);
+  }
+  float total = 0.0f;
+#pragma unroll
+  for (int r = 0; r < kArMaxRanks; ++r) {
+    if (r < p.tp_world) {
+      const float v = r == p.tp_rank ? own : __uint_as_float(unit[r].x);
+      total = r == 0 ? v : __fadd_rn(total, v);
+    }
   }
   return total;
 }
