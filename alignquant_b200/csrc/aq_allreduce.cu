@@ -38,14 +38,17 @@ static_assert(kBlocks * 4 <= kHeaderBytes, "header too small");
 
 using Peers = ArPeers;
 
+// Two exchange units {value, call number} per 16-byte access, as a vector of two 64-bit scalars:
+// each unit is single-copy atomic, so a reader never sees a new tag with an old value.
 __device__ __forceinline__ void st_volatile_v4(uint4* p, const uint4& v) {
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-               : "memory");
+  const uint64_t a = static_cast<uint64_t>(v.x) | (static_cast<uint64_t>(v.y) << 32);
+  const uint64_t b = static_cast<uint64_t>(v.z) | (static_cast<uint64_t>(v.w) << 32);
+  asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
 __device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
+  uint64_t a, b;
+  asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+  return make_uint4(static_cast<uint32_t>(a), static_cast<uint32_t>(a >> 32), static_cast<uint32_t>(b), static_cast<uint32_t>(b >> 32));
 }
 
 __global__ void __launch_bounds__(kThreads) allreduce_push_kernel(const float* __restrict__ partial,

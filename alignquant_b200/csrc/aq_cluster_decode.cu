@@ -64,13 +64,17 @@ struct Params {
   uint32_t ar_poll_limit;
 };
 
+// One exchange unit {value, call number} as ONE 64-bit scalar access: a 64-bit access is
+// single-copy atomic, so a reader never sees a new tag with an old value (a two-element vector
+// access would be two scalar accesses in unspecified order by the memory model).
 __device__ __forceinline__ void st_volatile_v2(void* p, uint32_t a, uint32_t b) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+  const uint64_t unit = static_cast<uint64_t>(a) | (static_cast<uint64_t>(b) << 32);
+  asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(unit) : "memory");
 }
 __device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
-  uint2 v;
-  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
+  uint64_t unit;
+  asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(unit) : "l"(p) : "memory");
+  return make_uint2(static_cast<uint32_t>(unit), static_cast<uint32_t>(unit >> 32));
 }
 
 constexpr int kGroupTiles = 8;  // tiles per ring slot
