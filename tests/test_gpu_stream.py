@@ -272,6 +272,66 @@ def test_reference_fixture_end_to_end(ext, golden_dir, name):
     assert np.allclose(out2.cpu().numpy(), g["y"], rtol=REL, atol=ABS)
 
 
+@pytest.mark.parametrize("kernel", ["auto", "cluster", "streamk"])
+@pytest.mark.parametrize("m", [1, 9, 24, 40, 200])
+def test_output_transform_through_every_kernel(ext, kernel, m):
+    """Non-identity output (U) transforms on most tile rows, identity on the others, through the
+    small-CTA kernel (cluster exchange of its column groups), the ring kernel (also its 17-32-row
+    variant), the stream-K kernel and the GEMM: against the FP64 dequantize-and-matmul with the
+    inverse transform, and the same bits from every call."""
+    from alignquant_b200.quantization.exact import metadata_stack
+
+    if kernel == "streamk" and m > 16:
+        pytest.skip("the stream-K kernel takes at most 16 rows")
+    n, k = 3072, 512
+    n_j, n_k = n // 64, k // 64
+    packed, _, tiles, scales = oc.synthetic_layer(n, k, seed=91)
+    weights, _ = helpers.prepare_layer(packed, n_k)
+    seeds = [(j * 7) % 11 - 1 for j in range(n_j)]  # -1 (identity) on every eleventh row
+    u_meta = metadata_stack(seeds, torch.device("cuda"))
+    xt = helpers.torch_activation(oc.synthetic_activation(m, k, seed=m), torch.float16)
+    ext.set_decode_kernel(cluster_only=kernel == "cluster", stream_k=kernel == "streamk")
+    try:
+        for scale_mode in ("token", "tile"):
+            xq, a_s = ext.alignquant_activation_quantize_cuda(xt, None, scale_mode=scale_mode)
+            outs = [ext.alignquant_linear_prepared(xq, a_s, weights, u_meta, scale_mode=scale_mode) for _ in range(2)]
+            ext.device_status()
+            assert torch.equal(outs[0], outs[1])
+            if scale_mode == "token":
+                a_mk = oc.expand_act_scales(a_s.cpu().numpy(), m, n_k, "token")
+            else:
+                a_mk = np.repeat(a_s.cpu().numpy().reshape(-1, n_k), 16, axis=0)[:m]
+            y64 = oc.dequant_matmul_fp64(xq.cpu().numpy(), a_mk, tiles, scales, u_meta.cpu().numpy())
+            assert np.allclose(outs[0].cpu().numpy(), y64, rtol=REL, atol=ABS), scale_mode
+            # and the transform really acts: without it the result is a different one
+            plain = oc.dequant_matmul_fp64(xq.cpu().numpy(), a_mk, tiles, scales)
+            assert not np.allclose(outs[0].cpu().numpy(), plain, rtol=REL, atol=ABS)
+    finally:
+        ext.set_decode_kernel()
+
+
+@pytest.mark.parametrize("m,k", [(16, 3072), (5, 8192), (40, 2560)])
+def test_tile_quantizer_with_input_transform_at_layer_sizes(ext, m, k):
+    """The V-transform quantizer on rows as long as the benchmark layers' K (48, 128 and 40 tiles, every
+    seventh an identity): scales to float32 rounding of the oracle's FP64 matmul, codes equal except for
+    at most one step on less than one in a thousand (the kernel's butterfly and the matmul differ in the
+    last bits of FP64)."""
+    from alignquant_b200.quantization.exact import metadata_stack
+
+    n_k = k // 64
+    seeds = [(t * 5) % 7 - 1 for t in range(n_k)]
+    meta = metadata_stack(seeds, torch.device("cuda"))
+    x = oc.synthetic_activation(m, k, seed=k + m)
+    xt = helpers.torch_activation(x, torch.float16)
+    q, s = ext.alignquant_activation_quantize_cuda(xt, meta)
+    pad = np.zeros((16 * ((m + 15) // 16), k))
+    pad[:m] = xt.float().cpu().numpy()
+    q_ref, s_ref = oc.a8_tile_quantize(oc.transform_activation(pad, meta.cpu().numpy()))
+    assert np.allclose(s.cpu().numpy().reshape(-1, n_k), s_ref, rtol=1e-6, atol=0)
+    diff = np.abs(q.cpu().numpy().astype(np.int32) - q_ref[:m].astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 1e-3
+
+
 @pytest.fixture
 def always_one_launch(ext):
     """aq_quant_linear as one launch wherever the kernel can do it, whatever the layer's size."""
