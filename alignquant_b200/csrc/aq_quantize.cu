@@ -74,6 +74,51 @@ __device__ __forceinline__ uint4 quantize_chunk(const float (&v)[16], float scal
   return o;
 }
 
+// Sixteen values as they come from memory (two 16-byte vectors of 16-bit values, four of floats):
+// a row that waits in registers for its turn costs half the registers this way.
+template <typename T>
+struct Raw16 {
+  uint4 part[sizeof(T) == 2 ? 2 : 4];
+};
+
+template <typename T>
+__device__ __forceinline__ Raw16<T> load_raw16(const T* p) {
+  Raw16<T> r;
+#pragma unroll
+  for (int i = 0; i < static_cast<int>(sizeof(r.part) / sizeof(uint4)); ++i) r.part[i] = __ldg(reinterpret_cast<const uint4*>(p) + i);
+  return r;
+}
+
+__device__ __forceinline__ void raw_to_float(const Raw16<__half>& r, float (&v)[16]) {
+  const uint32_t w[8] = {r.part[0].x, r.part[0].y, r.part[0].z, r.part[0].w, r.part[1].x, r.part[1].y, r.part[1].z, r.part[1].w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void raw_to_float(const Raw16<__nv_bfloat16>& r, float (&v)[16]) {
+  const uint32_t w[8] = {r.part[0].x, r.part[0].y, r.part[0].z, r.part[0].w, r.part[1].x, r.part[1].y, r.part[1].z, r.part[1].w};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ void raw_to_float(const Raw16<float>& r, float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[4 * i] = __uint_as_float(r.part[i].x);
+    v[4 * i + 1] = __uint_as_float(r.part[i].y);
+    v[4 * i + 2] = __uint_as_float(r.part[i].z);
+    v[4 * i + 3] = __uint_as_float(r.part[i].w);
+  }
+}
+
+// Rows of up to 8192 values are read ONCE and wait in registers, as loaded, between the maximum
+// and the rounding; the row a CTA takes next is requested before the current one is reduced, so
+// that a CTA always has a row on its way from HBM (a CTA walks rows blockIdx.x, + gridDim.x, ...).
 template <typename T>
 __global__ void __launch_bounds__(256) quantize_token_kernel(const T* __restrict__ x,
                                                              int8_t* __restrict__ q,
@@ -86,21 +131,36 @@ __global__ void __launch_bounds__(256) quantize_token_kernel(const T* __restrict
   const int warp = threadIdx.x >> 5;
   const int chunks = k / 16;
   const bool in_registers = chunks <= 512;
+  const int c0 = threadIdx.x, c1 = threadIdx.x + 256;
+  Raw16<T> next0, next1;
+  if (in_registers && blockIdx.x < m) {
+    const T* first = x + static_cast<int64_t>(blockIdx.x) * k;
+    if (c0 < chunks) next0 = load_raw16(first + c0 * 16);
+    if (c1 < chunks) next1 = load_raw16(first + c1 * 16);
+  }
   for (int64_t row = blockIdx.x; row < m; row += gridDim.x) {
     const T* xr = x + row * k;
     float amax = 0.0f;
-    float v0[16], v1[16];
-    const int c0 = threadIdx.x, c1 = threadIdx.x + 256;
+    Raw16<T> r0, r1;
     if (in_registers) {
+      r0 = next0;
+      r1 = next1;
+      const int64_t following = row + gridDim.x;
+      if (following < m) {
+        const T* xn = x + following * k;
+        if (c0 < chunks) next0 = load_raw16(xn + c0 * 16);
+        if (c1 < chunks) next1 = load_raw16(xn + c1 * 16);
+      }
+      float v[16];
       if (c0 < chunks) {
-        load16(xr + c0 * 16, v0);
+        raw_to_float(r0, v);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v0[i]));
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
       }
       if (c1 < chunks) {
-        load16(xr + c1 * 16, v1);
+        raw_to_float(r1, v);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v1[i]));
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
       }
     } else {
       for (int c = threadIdx.x; c < chunks; c += 256) {
@@ -122,8 +182,15 @@ __global__ void __launch_bounds__(256) quantize_token_kernel(const T* __restrict
     if (threadIdx.x == 0) scales[row] = scale;
     int8_t* qr = q + row * k;
     if (in_registers) {
-      if (c0 < chunks) *reinterpret_cast<uint4*>(qr + c0 * 16) = quantize_chunk(v0, scale, inv_scale);
-      if (c1 < chunks) *reinterpret_cast<uint4*>(qr + c1 * 16) = quantize_chunk(v1, scale, inv_scale);
+      float v[16];
+      if (c0 < chunks) {
+        raw_to_float(r0, v);
+        *reinterpret_cast<uint4*>(qr + c0 * 16) = quantize_chunk(v, scale, inv_scale);
+      }
+      if (c1 < chunks) {
+        raw_to_float(r1, v);
+        *reinterpret_cast<uint4*>(qr + c1 * 16) = quantize_chunk(v, scale, inv_scale);
+      }
     } else {
       for (int c = threadIdx.x; c < chunks; c += 256) {
         float v[16];

@@ -268,9 +268,31 @@ def prefill_leg(ext, device, steps: int) -> dict:
         total_seconds += seconds
         del weights, out, xq, a_s, x
     ext.device_status(device)
+    # The activation quantizer at prefill sizes is a plain streaming kernel: bf16 rows in, int8 rows and a
+    # scale per row out.  Eight distinct inputs of 134 MB each (more than the L2) are walked round robin.
+    q_rows, q_k, q_buffers = 8192, 8192, 8
+    xs = [synthetic_activation(q_rows, q_k, seed=970 + i, dtype=torch.bfloat16, device=device) for i in range(q_buffers)]
+    q_out = (torch.empty((q_rows, q_k), dtype=torch.int8, device=device), torch.empty((q_rows,), dtype=torch.float32, device=device))
+    for i in range(3):
+        ext.alignquant_activation_quantize_cuda(xs[i % q_buffers], None, scale_mode="token", out=q_out)
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    begin.record()
+    for i in range(2 * q_buffers):
+        ext.alignquant_activation_quantize_cuda(xs[i % q_buffers], None, scale_mode="token", out=q_out)
+    end.record()
+    torch.cuda.synchronize()
+    q_seconds = begin.elapsed_time(end) / 1e3 / (2 * q_buffers)
+    q_bytes = q_rows * q_k * 2 + q_rows * q_k + 4 * q_rows
+    peak, peak_source = hbm_peak()
+    quantizer = {"rows": q_rows, "k": q_k, "us": q_seconds * 1e6, "gbs": q_bytes / q_seconds / 1e9,
+                 "frac_of_hbm_peak": q_bytes / q_seconds / 1e9 / peak, "hbm_peak_gbs": peak, "peak_source": peak_source,
+                 "bytes": q_bytes, "kernel": "quantize_token_kernel<bf16> (per-token scales)"}
+    del xs, q_out
     measured_peak = ext.measure_int8_peak(4096, device)
     tops = total_ops / total_seconds / 1e12
     return {
+        "quantizer": quantizer,
         "workload": f"llama-3.2-3b prefill: (qkv, o, gate_up, down) at M = {PREFILL_ROWS}, bf16 activations, bf16 results, 60% W4",
         "metric": "prefill_gemm_int8_tops", "value": tops, "unit": "TOPS", "shapes": shapes,
         "frac_of_nominal_peak": tops / NOMINAL_INT8_TOPS, "nominal_peak_tops": NOMINAL_INT8_TOPS,
