@@ -38,6 +38,7 @@ def main() -> None:
     ap.add_argument("--schedule", default="auto")
     ap.add_argument("--flush-l2", action="store_true", help="overwrite a 512 MB buffer before every launch")
     ap.add_argument("--gemm-tile", choices=("auto", "paired", "narrow", "wide"), default="auto", help="CTA tile of the GEMM")
+    ap.add_argument("--gemm-split", type=int, default=0, help="K ranges of the GEMM (1..8), 0 = automatic")
     ap.add_argument("--gemm-separate-rounding", action="store_true",
                     help="GEMM adds a tile with a separately rounded multiply and add (the reference kernels' order)")
     ap.add_argument("--cluster-decode", action="store_true", help="keep the register-staged decode kernel off")
@@ -55,6 +56,7 @@ def main() -> None:
     ext.load_extension()
     ext.set_gemm_tile(args.gemm_tile)
     ext.set_gemm_rounding(args.gemm_separate_rounding)
+    ext.set_gemm_split(args.gemm_split)
     ext.set_decode_kernel(cluster_only=args.cluster_decode)
     if args.quant_fusion_tiles is not None:
         ext.set_quant_fusion_tiles(args.quant_fusion_tiles)

@@ -161,3 +161,12 @@ def test_config4_qwen3_14b_decode_batch32(ext, group):
 def test_config4_qwen3_14b_tp8_shards(ext, group):
     n, k = QWEN3_14B_TP8[group]
     _check(ext, n, k, 32, torch.bfloat16)
+
+
+@pytest.mark.parametrize("m", [1, 16])
+def test_ring_kernel_with_more_than_256_tiles_per_cta(ext, m):
+    """150 tile rows (no K split: one CTA per row) of 257 tiles: a warp of the ring kernel takes 33
+    tiles, one more than the 32 whose records its lanes hold at a time."""
+    plan = ext.linear_plan(m, 150, 257)
+    assert plan["kernel"] == 3 and plan["splits"] == 1
+    _check(ext, 9600, 16448, m, torch.float16)
