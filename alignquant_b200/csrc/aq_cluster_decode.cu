@@ -78,12 +78,12 @@ __device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
 }
 
 constexpr int kGroupTiles = 8;  // tiles per ring slot
-constexpr int kSlots = 3;
+constexpr int kMaxSlots = 3;  // ring slots: 3, or 2 for the layers that are split over a cluster (see Variant)
 constexpr int kModePlain = 0, kModeTp = 1, kModeDump = 2;
 constexpr int kSlotBytes = kGroupTiles * kW8TileBytes;
 constexpr int kTileWorkers = 8;  // tiles in progress per CTA; WPT warps share one tile (16 rows each)
 constexpr int kMaxCount = 512;  // tiles of one CTA's K range
-constexpr int kNumBars = kSlots;  // one "slot filled" barrier per ring slot
+constexpr int kNumBars = kMaxSlots;  // one "slot filled" barrier per ring slot
 
 // Counts a warp's arrival on a ring slot; release for the warp's reads of the slot, acquire for the
 // one that sees the last arrival and refills it.
@@ -134,7 +134,7 @@ __device__ __forceinline__ void tile_products(const uint8_t* lane_base, int w4_s
 // kMode: kModeTp -- the epilogue also sums over the tensor-parallel ranks; kModeDump -- the integer
 // tile sums are also written out (tests).  Separate instantiations keep both out of the plain
 // kernel's loop (its instructions should stay in the instruction cache) and register count.
-template <int NT, int WPT, int kMode>
+template <int NT, int WPT, int kMode, int kSlots>
 __global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) cluster_decode_kernel(const Params p) {
   constexpr bool kTp = kMode == kModeTp;
   constexpr bool kDump = kMode == kModeDump;
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) clu
   TileRecord* recs = reinterpret_cast<TileRecord*>(received + kReceivedRows * kTile);
   uint64_t* bars = reinterpret_cast<uint64_t*>(recs + kMaxCount);
   uint32_t* consumed = reinterpret_cast<uint32_t*>(bars + kNumBars);  // warps that are done with the slot's current tiles
-  volatile uint32_t* abort_flag = consumed + kSlots;
+  volatile uint32_t* abort_flag = consumed + kMaxSlots;
 
   cg::cluster_group cluster = cg::this_cluster();
   const int split_k = static_cast<int>(cluster.num_blocks());
@@ -528,19 +528,31 @@ __global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) clu
   }
 }
 
-// Kernel variants by row count: up to 8 rows <1,1>, up to 16 <2,1>, up to 32 <2,2>.
+// Kernel variants by row count: up to 8 rows <1,1>, up to 16 <2,1>, up to 32 <2,2>; and by ring
+// depth: layers that are split over a cluster have short K ranges per CTA (their first two slots
+// are most or all of it), so they run with two slots and leave 32 KiB per CTA to the CTAs of the
+// next launch; unsplit layers stream a whole tile row through three.
 struct Variant {
   int nt;
   int wpt;
+  int slots;
 };
-Variant variant_for(int64_t m) { return m <= 8 ? Variant{1, 1} : m <= 16 ? Variant{2, 1} : Variant{2, 2}; }
-int variant_index(const Variant& v) { return v.wpt == 2 ? 2 : v.nt - 1; }
+Variant variant_for(int64_t m, int split) {
+  const int slots = (split > 1 && m <= 16) ? 2 : 3;  // the 32-row variant's warp sums need the third slot
+  return m <= 8 ? Variant{1, 1, slots} : m <= 16 ? Variant{2, 1, slots} : Variant{2, 2, 3};
+}
+int variant_index(const Variant& v) { return (v.wpt == 2 ? 2 : v.nt - 1) + (v.slots == 2 ? 3 : 0); }  // 0..4
+constexpr int kVariants = 5;
 int variant_threads(const Variant& v) { return 32 * kTileWorkers * v.wpt; }
 template <int kMode>
 const void* variant_kernel_of(const Variant& v) {
-  if (v.wpt == 2) return reinterpret_cast<const void*>(cluster_decode_kernel<2, 2, kMode>);
-  return v.nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1, 1, kMode>)
-                   : reinterpret_cast<const void*>(cluster_decode_kernel<2, 1, kMode>);
+  if (v.wpt == 2) return reinterpret_cast<const void*>(cluster_decode_kernel<2, 2, kMode, 3>);
+  if (v.slots == 2) {
+    return v.nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1, 1, kMode, 2>)
+                     : reinterpret_cast<const void*>(cluster_decode_kernel<2, 1, kMode, 2>);
+  }
+  return v.nt == 1 ? reinterpret_cast<const void*>(cluster_decode_kernel<1, 1, kMode, 3>)
+                   : reinterpret_cast<const void*>(cluster_decode_kernel<2, 1, kMode, 3>);
 }
 const void* variant_kernel(const Variant& v, int mode = kModePlain) {
   return mode == kModeTp ? variant_kernel_of<kModeTp>(v) : mode == kModeDump ? variant_kernel_of<kModeDump>(v)
@@ -549,18 +561,18 @@ const void* variant_kernel(const Variant& v, int mode = kModePlain) {
 
 int smem_bytes(const Variant& v) {
   const int rows = 8 * v.nt * v.wpt;  // the slabs live in the ring
-  return kSlots * kSlotBytes + (rows + 7) * kTile * 4 + kMaxCount * 8 + kNumBars * 8 + kSlots * 4 + 16;
+  return v.slots * kSlotBytes + (rows + 7) * kTile * 4 + kMaxCount * 8 + kNumBars * 8 + kMaxSlots * 4 + 16;
 }
 
 int launch_variant(const Variant& v, const Params& p, int split_k, cudaStream_t stream) {
-  static std::once_flag once[64][9];
+  static std::once_flag once[64][3 * kVariants];
   int device = 0;
   int rc = check_cuda(cudaGetDevice(&device), "cudaGetDevice");
   if (rc != AQ_OK) return rc;
   const int mode = p.tp_world > 1 ? kModeTp : p.acc_dump != nullptr ? kModeDump : kModePlain;
   const void* kernel = variant_kernel(v, mode);
   cudaError_t attr_status = cudaSuccess;
-  std::call_once(once[device & 63][variant_index(v) + 3 * mode], [&] {
+  std::call_once(once[device & 63][variant_index(v) + kVariants * mode], [&] {
     attr_status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(v));
   });
   rc = check_cuda(attr_status, "cudaFuncSetAttribute(cluster_decode_kernel)");
@@ -592,7 +604,7 @@ namespace {
 // device (0 when the query fails); cached per device.
 int max_active_clusters(const Variant& v, int split) {
   static std::mutex mutex;
-  static int cache[64][3][9];  // [device][variant][split], 0 = not queried yet, -1 = failed
+  static int cache[64][kVariants][9];  // [device][variant][split], 0 = not queried yet, -1 = failed
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
   std::lock_guard<std::mutex> lock(mutex);
@@ -626,7 +638,7 @@ int max_active_clusters(const Variant& v, int split) {
 // that every CTA streams from the start; never shorter than one tile per CTA and never longer
 // than the record buffer.
 int cluster_decode_split(int64_t m, int n_j, int n_k) {
-  const Variant v = variant_for(m);
+  const Variant v = variant_for(m, 2);  // what a split layer runs
   static int sm_count[64] = {0};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) device = 0;
@@ -672,7 +684,7 @@ int launch_cluster_decode(const LinearArgs& a, cudaStream_t stream) {
     p.peers.buffer[r] = (a.peer_buffers != nullptr && r < a.tp_world) ? static_cast<uint8_t*>(a.peer_buffers[r]) : nullptr;
   }
   const int split = cluster_decode_split(a.m, a.n_j, a.n_k);
-  return launch_variant(variant_for(a.m), p, split, stream);
+  return launch_variant(variant_for(a.m, split), p, split, stream);
 }
 
 int take_cluster_decode_status() {
