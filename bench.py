@@ -682,16 +682,18 @@ def run_native(args) -> None:
         pass
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
-    if "prefill" in legs and world == 1:
-        try:
-            line["prefill"] = prefill_leg(ext, device, max(3, min(args.steps, 10)))
-        except Exception as error:  # the headline line is still reported
-            line["prefill"] = {"error": f"{type(error).__name__}: {error}"}
     if "generation" in legs:
         try:
             line["generation"] = generation_leg(world, args.gen_tokens)
         except Exception as error:
             line["generation"] = {"error": f"{type(error).__name__}: {error}"}
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    if "prefill" in legs and world == 1:
+        try:
+            line["prefill"] = prefill_leg(ext, device, max(3, min(args.steps, 10)))
+        except Exception as error:  # the headline line is still reported
+            line["prefill"] = {"error": f"{type(error).__name__}: {error}"}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
