@@ -146,6 +146,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_push_kernel(const float* _
   // the last CTA to finish advances the call counter (the next launch starts after this one ends)
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence();
     if (atomicAdd(&counters[1], 1u) == static_cast<uint32_t>(blocks - 1)) {
       counters[1] = 0;
       counters[0] = epoch;

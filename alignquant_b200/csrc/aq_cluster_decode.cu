@@ -520,6 +520,7 @@ __global__ void __launch_bounds__(32 * kTileWorkers * WPT, WPT == 1 ? 2 : 1) clu
   if (kTp && threadIdx.x == 0) {
     // the last CTA of the grid advances the call counter (the next launch starts after this one ends)
     uint32_t* counters = reinterpret_cast<uint32_t*>(p.peers.buffer[p.tp_rank]);
+    __threadfence();
     if (atomicAdd(&counters[1], 1u) == gridDim.x * gridDim.y - 1) {
       counters[1] = 0;
       counters[0] = ar_epoch_shared;

@@ -507,6 +507,7 @@ __global__ void __launch_bounds__(32 * WARPS, NG == 1 ? 3 : 2) direct_decode_ker
     __syncthreads();
     if (threadIdx.x == 0) {
       uint32_t* counters = reinterpret_cast<uint32_t*>(p.peers.buffer[p.tp_rank]);
+      __threadfence();
       if (atomicAdd(&counters[1], 1u) == gridDim.x * gridDim.y - 1) {
         counters[1] = 0;
         counters[0] = epoch;
