@@ -79,7 +79,7 @@ def parse_args():
     ap.add_argument("--gen-tokens", type=int, default=32, help="generated tokens of the generation leg")
     ap.add_argument("--lookahead", action="store_true",
                     help="every projection of the sweep names the next one's weights as its L2 look-ahead (off by default: "
-                         "between back-to-back projections it was measured to cost about 2 %)")
+                         "between back-to-back projections it was measured to cost about 2 %%)")
     ap.add_argument("--cluster-decode", action="store_true",
                     help="keep the register-staged decode kernel off (AQ_DECODE_KERNEL_CLUSTER), for comparison")
     return ap.parse_args()
