@@ -77,6 +77,9 @@ def parse_args():
     ap.add_argument("--legs", default="decode,prefill,generation",
                     help="comma-separated legs besides the decode sweep: prefill, generation")
     ap.add_argument("--gen-tokens", type=int, default=32, help="generated tokens of the generation leg")
+    ap.add_argument("--watchdog", type=int, default=300,
+                    help="multi-GPU runs only: seconds after which a run without a result ends itself with a diagnostic "
+                         "line (0: never)")
     ap.add_argument("--lookahead", action="store_true",
                     help="every projection of the sweep names the next one's weights as its L2 look-ahead (off by default: "
                          "between back-to-back projections it was measured to cost about 2 %%)")
@@ -320,6 +323,36 @@ def generation_leg(world: int, tokens: int) -> dict:
     return result
 
 
+class Watchdog:
+    """Ends a multi-GPU run that has produced no result in time, naming the stage every rank was in.
+
+    Every device-side wait of the library is bounded, so the GPUs stay usable whatever happens; what
+    this guards against is a host-side stall (a collective that one rank never joins, a rendezvous
+    that never completes) holding a whole node until an outer limit kills the job without a word.
+    """
+
+    def __init__(self, seconds: int, rank: int, world: int):
+        import threading
+
+        self.stage, self.rank, self.world, self.seconds = "start", rank, world, seconds
+        self.timer = None
+        if seconds > 0 and world > 1:
+            self.timer = threading.Timer(seconds, self.fire)
+            self.timer.daemon = True
+            self.timer.start()
+
+    def fire(self) -> None:
+        print(f"[bench] rank {self.rank}: no result after {self.seconds} s, stage '{self.stage}'", file=sys.stderr, flush=True)
+        if self.rank == 0:
+            print(json.dumps({"metric": "decode_gemv_hbm_gbs", "n_gpus": self.world,
+                              "error": f"no result after {self.seconds} s; rank 0 was in stage '{self.stage}'"}), flush=True)
+        os._exit(5)
+
+    def cancel(self) -> None:
+        if self.timer is not None:
+            self.timer.cancel()
+
+
 def run_native(args) -> None:
     import torch
     import torch.distributed as dist
@@ -333,11 +366,14 @@ def run_native(args) -> None:
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
     legs = {leg.strip() for leg in args.legs.split(",") if leg.strip()}
+    watchdog = Watchdog(args.watchdog, rank, world)
+    watchdog.stage = "process group"
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     ext.load_extension()
+    watchdog.stage = "exchange buffers"
     ext.set_decode_kernel(cluster_only=args.cluster_decode)
     reducer = None
     if world > 1 and os.environ.get("ALIGNQUANT_B200_ALLREDUCE", "peer") == "peer":
@@ -351,6 +387,7 @@ def run_native(args) -> None:
         else:
             dist.all_reduce(tensor)
 
+    watchdog.stage = "weights"
     # ---- build the sharded model: prepared weight images only (raw arenas are freed)
     layers = []
     weight_bytes = {}
@@ -464,6 +501,7 @@ def run_native(args) -> None:
         return seconds
 
     # ---- N > 1: the fused projection + rank sum against projection, then NCCL all-reduce
+    watchdog.stage = "tp_check"
     tp_check = None
     if world > 1:
         worst = 0.0
@@ -513,6 +551,7 @@ def run_native(args) -> None:
             os._exit(3)
 
     # ---- device-resident step: one CUDA graph per rank (kernels and, for N > 1, the all-reduces)
+    watchdog.stage = "first sweep (eager)"
     sweep(True, True)
     own_sum_launches = separate_sums[0]
     barrier()
@@ -529,6 +568,7 @@ def run_native(args) -> None:
         launch_mode = "eager"
         torch.cuda.synchronize()
         step = lambda: sweep(True, True)  # noqa: E731
+    watchdog.stage = "timed sweep"
     with ClockSampler(local_rank) as clocks:
         seconds = timed(step, args.steps, max(args.warmup, 3))
         # keep the same step running until nvidia-smi (100 ms period) has had time to sample it
@@ -538,6 +578,7 @@ def run_native(args) -> None:
             torch.cuda.synchronize()
     ext.device_status(device)
 
+    watchdog.stage = "GEMV-only sweep"
     # ---- the packed-GEMV kernel alone (roofline of the dominant kernel)
     kernel_graph = torch.cuda.CUDAGraph()
     with torch.cuda.graph(kernel_graph):
@@ -546,6 +587,7 @@ def run_native(args) -> None:
     peak, peak_source = hbm_peak()
     achieved = linear_bytes / pairs_per_step / kernel_seconds / 1e9
 
+    watchdog.stage = "end-to-end sweep"
     # ---- end to end through the public API from pinned host buffers
     host_x = {key: x.cpu().pin_memory() for key, x in acts.items()}
     host_out = {key: torch.empty(o.shape, dtype=o.dtype).pin_memory() for key, o in outs.items()}
@@ -694,6 +736,7 @@ def run_native(args) -> None:
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
     if "generation" in legs:
+        watchdog.stage = "generation leg"
         try:
             line["generation"] = generation_leg(world, args.gen_tokens)
         except Exception as error:
@@ -705,6 +748,7 @@ def run_native(args) -> None:
             line["prefill"] = prefill_leg(ext, device, max(3, min(args.steps, 10)))
         except Exception as error:  # the headline line is still reported
             line["prefill"] = {"error": f"{type(error).__name__}: {error}"}
+    watchdog.cancel()
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
