@@ -41,3 +41,18 @@ def test_native_arm_has_no_cpu_path():
     done = _run("--steps", "1", "--warmup", "1")
     assert done.returncode != 0
     assert not [line for line in done.stdout.splitlines() if line.startswith("{")]
+
+
+def test_watchdog_ends_a_stalled_multi_gpu_run_with_a_diagnostic_line():
+    """The watchdog of multi-GPU runs (a host-side stall must not hold a node without a word): it
+    prints which stage the rank was in, rank 0 prints a JSON line with an error, exit code 5; a
+    single-GPU run gets no timer."""
+    stalled = "import bench, time; w = bench.Watchdog(1, 0, 2); w.stage = 'tp_check'; time.sleep(20)"
+    done = subprocess.run([sys.executable, "-c", stalled], cwd=ROOT, capture_output=True, text=True, timeout=60)
+    assert done.returncode == 5
+    line = json.loads(done.stdout.strip())
+    assert line["n_gpus"] == 2 and "tp_check" in line["error"] and "tp_check" in done.stderr
+    single = "import bench, time; w = bench.Watchdog(1, 0, 1); time.sleep(2); w.cancel(); print('done')"
+    done = subprocess.run([sys.executable, "-c", single], cwd=ROOT, capture_output=True, text=True, timeout=60)
+    assert done.returncode == 0 and done.stdout.strip() == "done"
+
