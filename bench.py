@@ -536,12 +536,12 @@ def run_native(args) -> None:
                 worst = max(worst, float((got - want).abs().max()))
         try:
             ext.device_status(device)
-        except RuntimeError as error:  # a bounded device-side wait ran out: every rank still reaches the verdict
+        except RuntimeError as error:  # a bounded device-side wait ran out: every rank still reaches the common result
             ok = False
             print(f"[bench] rank {rank}: {error}", file=sys.stderr)
-        verdict = torch.tensor([0 if ok else 1], device=device, dtype=torch.int32)
-        dist.all_reduce(verdict, op=dist.ReduceOp.MAX)
-        tp_check = "ok" if int(verdict.item()) == 0 else "mismatch"
+        failed = torch.tensor([0 if ok else 1], device=device, dtype=torch.int32)
+        dist.all_reduce(failed, op=dist.ReduceOp.MAX)
+        tp_check = "ok" if int(failed.item()) == 0 else "mismatch"
         if tp_check != "ok":
             if rank == 0:
                 print(json.dumps({"metric": "decode_gemv_hbm_gbs", "n_gpus": world, "tp_check": tp_check,
