@@ -9,8 +9,9 @@ over ~2 GB of distinct weights (larger than L2, so no flush is needed between st
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
 
 With N > 1 (launched under torch.distributed.run) every layer is sharded
-tensor-parallel: column shards of qkv/gate_up, row shards of o/down followed by an
-NCCL all-reduce of the [M, 3072] partial; total work is fixed ("strong" scaling).
+tensor-parallel: column shards of qkv/gate_up, row shards of o/down whose [M, 3072]
+partials are summed over the ranks through peer memory inside the GEMV kernel (with
+ALIGNQUANT_B200_ALLREDUCE=nccl: by an NCCL all-reduce); total work is fixed ("strong" scaling).
 
 Rank 0 prints one JSON line.  `value` is algorithmic bytes per second with every
 input resident in HBM (CUDA-graph replay, CUDA-event timing, max over ranks); `e2e`
@@ -19,9 +20,11 @@ copies included; `roofline` times the packed-GEMV kernel alone; `cpu_baseline` t
 the CPU oracle (the reference's dequantize-and-matmul recipe) on a bounded sample.
 `--impl reference` runs only that CPU arm.
 
-Every projection hands the weights of the projection that runs after it to the decode
-kernel as a look-ahead (`aq_linear_ahead`), exactly as the quantized modules of an installed
-model do: the L2 cache fetches the next image while the current kernel runs.
+Every quantizer + projection pair is one call of `aq_quant_linear` (one launch where the
+quantizer runs inside the GEMV kernel, two otherwise).  With `--lookahead` every projection also
+names the weights of the projection that runs after it (`next_prepared`), as the quantized
+modules of an installed model do; between back-to-back projections that measured slower, so
+it is off here.
 
 The line also carries the other two legs of the metric (`--legs` selects them):
 `prefill` -- the same four Llama-3.2-3B shapes at M = 2048 with bf16 activations through the
@@ -30,7 +33,9 @@ back-to-back `tcgen05.mma kind::i8` rate (`aq_measure_int8_peak`); `generation` 
 generated tokens per second of a random-init Qwen3-4B-shaped model on one GPU, or of the
 tensor-parallel Qwen3-14B-shaped model on N > 1 GPUs, with a shortened, stated token count.
 With N > 1 the fused projection + rank sum is first checked against the two-step path
-(`tp_check`); a mismatch ends the run with a non-zero exit code.
+(`tp_check`); a mismatch ends the run with a non-zero exit code.  `tp_one_call_bits` says whether the
+one-call form gave the bits of quantizer + fused projection.  A multi-GPU run without a result
+after `--watchdog` seconds ends itself with a line that names the stage it was in.
 """
 
 from __future__ import annotations
@@ -505,7 +510,7 @@ def run_native(args) -> None:
     tp_check = None
     if world > 1:
         worst = 0.0
-        ok = True
+        ok = same_bits = True
         for m in ROW_COUNTS:
             for name, (_, _, axis) in GROUPS.items():
                 if axis != "k":
@@ -529,7 +534,8 @@ def run_native(args) -> None:
                                                            reducer=reducer)
                 torch.cuda.synchronize()
                 if one_call is not None:
-                    ok = ok and torch.equal(one_call, got)
+                    ok = ok and bool(torch.isclose(one_call, want, rtol=1e-5, atol=1e-5).all())
+                    same_bits = same_bits and torch.equal(one_call, got)
                 # NCCL's summation order differs from the rank order of the fused sum
                 close = torch.isclose(got, want, rtol=1e-5, atol=1e-5)
                 ok = ok and bool(close.all())
@@ -539,9 +545,11 @@ def run_native(args) -> None:
         except RuntimeError as error:  # a bounded device-side wait ran out: every rank still reaches the common result
             ok = False
             print(f"[bench] rank {rank}: {error}", file=sys.stderr)
-        failed = torch.tensor([0 if ok else 1], device=device, dtype=torch.int32)
+        failed = torch.tensor([0 if ok else 1, 0 if same_bits else 1], device=device, dtype=torch.int32)
         dist.all_reduce(failed, op=dist.ReduceOp.MAX)
-        tp_check = "ok" if int(failed.item()) == 0 else "mismatch"
+        failed = failed.tolist()
+        tp_check = "ok" if failed[0] == 0 else "mismatch"
+        one_call_bits = None if reducer is None else ("same" if failed[1] == 0 else "differ")
         if tp_check != "ok":
             if rank == 0:
                 print(json.dumps({"metric": "decode_gemv_hbm_gbs", "n_gpus": world, "tp_check": tp_check,
@@ -718,6 +726,7 @@ def run_native(args) -> None:
     }
     if tp_check is not None:
         line["tp_check"] = tp_check
+        line["tp_one_call_bits"] = one_call_bits  # one-call form against quantizer + fused projection, bit for bit
     if rank == 0 and world == 1:
         sample = CpuSample()
         sample.run()
