@@ -55,6 +55,32 @@ def test_shard_is_an_exact_sub_selection(rows, cols):
     assert np.array_equal(s_scales, scales[j0:j1, k0:k1])
 
 
+@pytest.mark.parametrize("tp", [1, 2, 4, 8])
+def test_tensor_parallel_ranges_of_the_qwen3_14b_shape(tp):
+    """Head groups and MLP width of the 14B shape split on tile borders at every rank count the
+    multi-GPU configuration names: the ranks' ranges are disjoint, in order and cover everything."""
+    hidden, inter, heads, kv_heads, head_dim = 5120, 17408, 40, 8, 128
+    totals = {"q_proj rows": heads * head_dim // 64, "k_proj rows": kv_heads * head_dim // 64,
+              "gate_proj rows": inter // 64, "o_proj k": heads * head_dim // 64, "down_proj k": inter // 64}
+    for what, total in totals.items():
+        ranges = [glue.tensor_parallel_range(total, rank, tp, what) for rank in range(tp)]
+        assert ranges[0][0] == 0 and ranges[-1][1] == total
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+        assert {hi - lo for lo, hi in ranges} == {total // tp}
+    if tp == 8:  # 5 query heads, 1 KV head, 2176 MLP columns per rank
+        assert glue.tensor_parallel_range(totals["q_proj rows"], 3, 8, "q") == (30, 40)
+        assert glue.tensor_parallel_range(totals["k_proj rows"], 3, 8, "k") == (6, 8)
+        assert glue.tensor_parallel_range(totals["down_proj k"], 7, 8, "down") == (238, 272)
+    assert hidden % 64 == 0
+
+
+def test_tensor_parallel_range_rejects_uneven_and_invalid_ranks():
+    with pytest.raises(ValueError, match="cannot be split evenly"):
+        glue.tensor_parallel_range(272, 0, 3, "down_proj k")
+    with pytest.raises(ValueError, match="Invalid tensor-parallel rank"):
+        glue.tensor_parallel_range(272, 8, 8, "down_proj k")
+
+
 # ---- a tiny decoder and a CPU stand-in for the three extension calls -------------------------
 
 
